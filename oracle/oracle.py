@@ -1,0 +1,214 @@
+"""ctypes front end to the CPU oracle (``oracle/liboracle.so``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by ``__graft_entry__.smoke()``
+and by ``bench.py``'s CPU-baseline / reference legs.  The shipped package never
+imports it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import build_oracle
+
+_LIB = None
+
+
+def _fp(a: np.ndarray):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def lib():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = build_oracle.ORACLE_SO
+    if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(
+            os.path.join(build_oracle.HERE, "shainet_oracle.cpp")):
+        build_oracle.build_oracle(force=True)
+    L = C.CDLL(path)
+    P, F, I, D = C.c_void_p, C.POINTER(C.c_float), C.c_int, C.c_double
+    L.oracle_block_create.restype = P
+    L.oracle_block_create.argtypes = [I, I, I, D, D]
+    L.oracle_block_destroy.argtypes = [P]
+    L.oracle_block_set_rope_freqs.argtypes = [P, F]
+    L.oracle_block_set_qk_norm.argtypes = [P, F, F]
+    L.oracle_block_set_bias.argtypes = [P, F, F, F]
+    L.oracle_block_clear.argtypes = [P]
+    L.oracle_block_len.argtypes = [P]
+    L.oracle_block_len.restype = I
+    L.oracle_inv_freq.argtypes = [P, F]
+    L.oracle_block_import.argtypes = [P, F, F, I]
+    L.oracle_block_export.argtypes = [P, F, F]
+    L.oracle_block_attend_cached.argtypes = [P, F, F, F, I, F, I, I]
+    L.oracle_block_attend_only.argtypes = [P, F, I, I, F, I, I]
+    L.oracle_block_attend_full.argtypes = [P, F, F, F, I, F]
+    L.oracle_rope_apply.argtypes = [F, I, I, I, D, F]
+    L.oracle_llama3_rope_freqs.argtypes = [D, I, D, D, D, D, F]
+    L.oracle_matmul.argtypes = [F, F, I, I, I, F]
+    L.oracle_rmsnorm.argtypes = [F, I, I, F, D, F]
+    L.oracle_swiglu.argtypes = [F, I, I, I, F, F, F, F]
+    L.oracle_add.argtypes = [F, F, C.c_size_t, F]
+    L.oracle_max_threads.restype = I
+    _LIB = L
+    return L
+
+
+class OracleAttention:
+    """The attention state of the reference's ``LlamaBlock`` (per-kv-head growing
+    K/V arrays and ``cache_len``; src/shainet/transformer/llama_block.cr:45-48)
+    with its cached and uncached attention between the projections and o_proj."""
+
+    def __init__(self, num_heads, num_kv_heads, head_dim, rope_theta=10000.0, eps=1e-6,
+                 rope_freqs=None, q_norm=None, k_norm=None, b_q=None, b_k=None, b_v=None):
+        self.L = lib()
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.q_dim, self.kv_dim = num_heads * head_dim, num_kv_heads * head_dim
+        self.h = self.L.oracle_block_create(num_heads, num_kv_heads, head_dim, rope_theta, eps)
+        if not self.h:
+            raise ValueError("bad head configuration")
+        self._keep = []
+        if rope_freqs is not None:
+            f = _f32(rope_freqs)
+            self.L.oracle_block_set_rope_freqs(self.h, _fp(f))
+        if q_norm is not None or k_norm is not None:
+            qn = _f32(q_norm) if q_norm is not None else None
+            kn = _f32(k_norm) if k_norm is not None else None
+            self.L.oracle_block_set_qk_norm(self.h, _fp(qn) if qn is not None else None,
+                                            _fp(kn) if kn is not None else None)
+        if b_q is not None or b_k is not None or b_v is not None:
+            bs = [(_f32(b) if b is not None else None) for b in (b_q, b_k, b_v)]
+            self.L.oracle_block_set_bias(self.h, *[(_fp(b) if b is not None else None) for b in bs])
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.L.oracle_block_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    def clear_cache(self):
+        self.L.oracle_block_clear(self.h)
+
+    @property
+    def cache_len(self) -> int:
+        return self.L.oracle_block_len(self.h)
+
+    def inv_freq(self) -> np.ndarray:
+        out = np.empty(self.head_dim // 2, np.float32)
+        self.L.oracle_inv_freq(self.h, _fp(out))
+        return out
+
+    def import_cache(self, k, v):
+        k, v = _f32(k), _f32(v)
+        assert k.shape == v.shape and k.shape[0] == self.num_kv_heads and k.shape[2] == self.head_dim
+        self.L.oracle_block_import(self.h, _fp(k), _fp(v), k.shape[1])
+
+    def export_cache(self):
+        n = self.cache_len
+        k = np.empty((self.num_kv_heads, n, self.head_dim), np.float32)
+        v = np.empty_like(k)
+        self.L.oracle_block_export(self.h, _fp(k), _fp(v))
+        return k, v
+
+    def attend_cached(self, q, k_new, v_new, threads=1, mode=0) -> np.ndarray:
+        q, k_new, v_new = _f32(q), _f32(k_new), _f32(v_new)
+        T = q.shape[0]
+        assert q.shape == (T, self.q_dim) and k_new.shape == (T, self.kv_dim) and v_new.shape == k_new.shape
+        out = np.empty((T, self.q_dim), np.float32)
+        self.L.oracle_block_attend_cached(self.h, _fp(q), _fp(k_new), _fp(v_new), T, _fp(out), threads, mode)
+        return out
+
+    def attend_only(self, q, start_pos, threads=1, mode=0) -> np.ndarray:
+        q = _f32(q)
+        T = q.shape[0]
+        out = np.empty((T, self.q_dim), np.float32)
+        self.L.oracle_block_attend_only(self.h, _fp(q), T, start_pos, _fp(out), threads, mode)
+        return out
+
+    def attend_full(self, q, k, v) -> np.ndarray:
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        S = q.shape[0]
+        out = np.empty((S, self.q_dim), np.float32)
+        self.L.oracle_block_attend_full(self.h, _fp(q), _fp(k), _fp(v), S, _fp(out))
+        return out
+
+
+def rope_apply(x, start_pos=0, theta=10000.0) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().oracle_rope_apply(_fp(x), x.shape[0], x.shape[1], start_pos, theta, _fp(out))
+    return out
+
+
+def llama3_rope_freqs(theta, head_dim, factor, low_freq_factor, high_freq_factor, old_ctx) -> np.ndarray:
+    out = np.empty(head_dim // 2, np.float32)
+    lib().oracle_llama3_rope_freqs(theta, head_dim, factor, low_freq_factor, high_freq_factor, old_ctx, _fp(out))
+    return out
+
+
+def matmul(a, b) -> np.ndarray:
+    a, b = _f32(a), _f32(b)
+    out = np.empty((a.shape[0], b.shape[1]), np.float32)
+    lib().oracle_matmul(_fp(a), _fp(b), a.shape[0], a.shape[1], b.shape[1], _fp(out))
+    return out
+
+
+def rmsnorm(x, gamma, eps) -> np.ndarray:
+    x, gamma = _f32(x), _f32(gamma)
+    out = np.empty_like(x)
+    lib().oracle_rmsnorm(_fp(x), x.shape[0], x.shape[1], _fp(gamma), eps, _fp(out))
+    return out
+
+
+def swiglu(x, gate_w, up_w, down_w) -> np.ndarray:
+    x, gate_w, up_w, down_w = _f32(x), _f32(gate_w), _f32(up_w), _f32(down_w)
+    out = np.empty((x.shape[0], down_w.shape[1]), np.float32)
+    lib().oracle_swiglu(_fp(x), x.shape[0], x.shape[1], gate_w.shape[1], _fp(gate_w), _fp(up_w), _fp(down_w), _fp(out))
+    return out
+
+
+def add(a, b) -> np.ndarray:
+    a, b = _f32(a), _f32(b)
+    out = np.empty_like(a)
+    lib().oracle_add(_fp(a), _fp(b), a.size, _fp(out))
+    return out
+
+
+def max_threads() -> int:
+    return lib().oracle_max_threads()
+
+
+class OracleLlamaBlock:
+    """Whole decoder block on the host (norm1 -> attention -> residual -> norm2 ->
+    SwiGLU -> residual; src/shainet/transformer/llama_block.cr:179-196), used only
+    to replay the reference's cache-consistency spec.  Weights are [in, out]."""
+
+    def __init__(self, d_model, num_heads, num_kv_heads, head_dim, eps, rope_theta, w):
+        self.attn = OracleAttention(num_heads, num_kv_heads, head_dim, rope_theta, eps)
+        self.eps, self.w = eps, w
+
+    def _wrap(self, x, attn_fn):
+        w = self.w
+        normed = rmsnorm(x, w["norm1"], self.eps)
+        q, k, v = matmul(normed, w["w_q"]), matmul(normed, w["w_k"]), matmul(normed, w["w_v"])
+        a = matmul(attn_fn(q, k, v), w["w_o"])
+        h = add(x, a)
+        n2 = rmsnorm(h, w["norm2"], self.eps)
+        return add(h, swiglu(n2, w["gate"], w["up"], w["down"]))
+
+    def forward(self, x):
+        return self._wrap(x, self.attn.attend_full)
+
+    def forward_cached(self, x):
+        return self._wrap(x, self.attn.attend_cached)
+
+    def clear_cache(self):
+        self.attn.clear_cache()

@@ -1,0 +1,461 @@
+// CPU oracle for the SHAInet LLaMA/Qwen attention hot path.
+//
+// TEST INFRASTRUCTURE ONLY.  This file restates, operation by operation and in
+// the same floating-point order, what the reference's Crystal host code
+// computes for RoPE, per-head QK-norm, KV-cache append and grouped-query causal
+// attention.  It exists so that the CUDA library can be checked against it and
+// so that a CPU baseline can be timed; nothing in the shipped library may link
+// or call it.
+//
+// Parity status: the reference's host language (Crystal) has no compiler in
+// this build environment, so the Crystal code itself cannot be executed.  The
+// oracle is pinned instead by (1) the reference's two RoPE known-answer specs,
+// (2) the reference's cached-vs-uncached consistency relation on its
+// tiny-llama fixture, (3) its nil-bias == zero-bias relation, and (4) a
+// GPU-side comparison with the reference's own CUDA attention kernel compiled
+// unmodified from its source (see oracle/build_oracle.py, tests/test_reference_kernel.py).
+// Behaviours the reference's specs never exercise (QK-norm, head_dim 64/128,
+// theta 5e5/1e6, LLaMA-3 scaled frequencies) are "parity unpinned": the source
+// lines cited below are their only specification.
+//
+// Build: g++ -O2 -ffp-contract=off -fopenmp (no -ffast-math) so that the
+// sequential fp32 sums are neither reassociated nor fused, as in an LLVM
+// release build of the Crystal source.
+//
+// Citations are paths inside the reference project.
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+#include <algorithm>
+#include <limits>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+struct Block {
+    int num_heads = 0;
+    int num_kv_heads = 0;
+    int head_dim = 0;
+    double rope_theta = 10000.0;
+    double eps = 1e-6;
+    bool has_freqs = false;
+    std::vector<float> rope_freqs;           // head_dim/2, overrides theta formula
+    bool has_qn = false, has_kn = false;
+    std::vector<float> q_norm, k_norm;       // head_dim each
+    bool has_bq = false, has_bk = false, has_bv = false;
+    std::vector<float> b_q, b_k, b_v;
+    // src/shainet/transformer/llama_block.cr:45-48 — one growing array per kv head
+    std::vector<std::vector<float>> k_cache, v_cache;
+    int cache_len = 0;
+
+    int q_dim() const { return num_heads * head_dim; }
+    int kv_dim() const { return num_kv_heads * head_dim; }
+
+    // src/shainet/transformer/llama_block.cr:669-675
+    float inv_freq(int i) const {
+        if (has_freqs) return rope_freqs[i];
+        double e = 2.0 * (double)i / (double)head_dim;
+        return (float)(1.0 / std::pow(rope_theta, e));
+    }
+};
+
+// src/shainet/transformer/llama_block.cr:585-601
+void add_bias(float* m, int rows, int cols, const float* b) {
+    for (int r = 0; r < rows; ++r) {
+        float* row = m + (size_t)r * cols;
+        for (int c = 0; c < cols; ++c) row[c] += b[c];
+    }
+}
+
+// src/shainet/transformer/llama_block.cr:615-641
+void head_rmsnorm(float* m, int rows, int cols, int nheads, int hd, const float* w, double eps) {
+    for (int r = 0; r < rows; ++r) {
+        for (int h = 0; h < nheads; ++h) {
+            float* p = m + (size_t)r * cols + (size_t)h * hd;
+            float ss = 0.0f;
+            for (int d = 0; d < hd; ++d) {
+                float v = p[d];
+                ss += v * v;
+            }
+            float mean = ss / (float)hd;                      // Float32 / Int32 -> Float32
+            float inv = (float)(1.0 / std::sqrt((double)mean + eps));
+            for (int d = 0; d < hd; ++d) p[d] = p[d] * inv * w[d];
+        }
+    }
+}
+
+// Rotation used for both K (llama_block.cr:266-286) and Q (:332-344).
+inline void rope_row(const Block& b, const float* x, int pos, float* out) {
+    int half = b.head_dim / 2;
+    for (int i = 0; i < half; ++i) {
+        float freq = b.inv_freq(i);
+        float angle = (float)pos * freq;
+        float c = cosf(angle);
+        float s = sinf(angle);
+        float x0 = x[i];
+        float x1 = x[i + half];
+        out[i] = x0 * c - x1 * s;
+        out[i + half] = x1 * c + x0 * s;
+    }
+}
+
+// src/shainet/transformer/llama_block.cr:302-401 for one query head.
+// mode 0: the reference's fp32 sequential arithmetic.
+// mode 1: the same visible set with every sum carried in f64 ("truth" for
+//         judging summation error; not a reference behaviour).
+void attend_head(const Block& b, int h, const float* q_full, float* output, int new_tokens,
+                 int start_pos, int total_len, float scale, int mode) {
+    const int hd = b.head_dim;
+    const int heads_per_kv = b.num_heads / b.num_kv_heads;
+    const int dm = b.q_dim();
+    const int q_col = h * hd;
+    const int kv_h = h / heads_per_kv;
+    const float* kptr = b.k_cache[kv_h].data();
+    const float* vptr = b.v_cache[kv_h].data();
+    std::vector<float> q_rot(hd, 0.0f), scores(total_len, 0.0f), out(hd, 0.0f);
+    std::vector<double> sd, od;
+    if (mode == 1) { sd.assign(total_len, 0.0); od.assign(hd, 0.0); }
+
+    for (int i = 0; i < new_tokens; ++i) {
+        int pos = start_pos + i;
+        const float* qrow = q_full + (size_t)i * dm + q_col;
+        rope_row(b, qrow, pos, q_rot.data());
+        int visible = start_pos + i + 1;
+        if (mode == 0) {
+            float max_val = -std::numeric_limits<float>::infinity();
+            for (int j = 0; j < visible; ++j) {
+                const float* kr = kptr + (size_t)j * hd;
+                float dot = 0.0f;
+                for (int d = 0; d < hd; ++d) dot += q_rot[d] * kr[d];
+                float sv = dot * scale;
+                scores[j] = sv;
+                if (sv > max_val) max_val = sv;
+            }
+            float exp_sum = 0.0f;
+            for (int j = 0; j < visible; ++j) {
+                float e = (float)std::exp((double)(scores[j] - max_val));
+                scores[j] = e;
+                exp_sum += e;
+            }
+            float inv_sum = 1.0f / exp_sum;
+            for (int d = 0; d < hd; ++d) out[d] = 0.0f;
+            for (int j = 0; j < visible; ++j) {
+                float w = scores[j] * inv_sum;
+                const float* vr = vptr + (size_t)j * hd;
+                for (int d = 0; d < hd; ++d) out[d] += w * vr[d];
+            }
+            float* orow = output + (size_t)i * dm + q_col;
+            for (int d = 0; d < hd; ++d) orow[d] = out[d];
+        } else {
+            double max_val = -std::numeric_limits<double>::infinity();
+            for (int j = 0; j < visible; ++j) {
+                const float* kr = kptr + (size_t)j * hd;
+                double dot = 0.0;
+                for (int d = 0; d < hd; ++d) dot += (double)q_rot[d] * (double)kr[d];
+                double sv = dot * (double)scale;
+                sd[j] = sv;
+                if (sv > max_val) max_val = sv;
+            }
+            double exp_sum = 0.0;
+            for (int j = 0; j < visible; ++j) { sd[j] = std::exp(sd[j] - max_val); exp_sum += sd[j]; }
+            for (int d = 0; d < hd; ++d) od[d] = 0.0;
+            for (int j = 0; j < visible; ++j) {
+                double w = sd[j] / exp_sum;
+                const float* vr = vptr + (size_t)j * hd;
+                for (int d = 0; d < hd; ++d) od[d] += w * (double)vr[d];
+            }
+            float* orow = output + (size_t)i * dm + q_col;
+            for (int d = 0; d < hd; ++d) orow[d] = (float)od[d];
+        }
+    }
+}
+
+// src/shainet/math/simple_matrix.cr:61-74 — f64 accumulate, fp32 store.
+void matmul_f64acc(const float* a, const float* b, int M, int K, int N, float* out) {
+    for (int i = 0; i < M; ++i)
+        for (int j = 0; j < N; ++j) {
+            double sum = 0.0;
+            for (int k = 0; k < K; ++k) sum += (double)a[(size_t)i * K + k] * (double)b[(size_t)k * N + j];
+            out[(size_t)i * N + j] = (float)sum;
+        }
+}
+
+}  // namespace
+
+extern "C" {
+
+void* oracle_block_create(int num_heads, int num_kv_heads, int head_dim, double rope_theta, double eps) {
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || head_dim <= 0) return nullptr;
+    Block* b = new Block();
+    b->num_heads = num_heads;
+    b->num_kv_heads = num_kv_heads;
+    b->head_dim = head_dim;
+    b->rope_theta = rope_theta;
+    b->eps = eps;
+    b->k_cache.resize(num_kv_heads);
+    b->v_cache.resize(num_kv_heads);
+    return b;
+}
+
+void oracle_block_destroy(void* p) { delete (Block*)p; }
+
+void oracle_block_set_rope_freqs(void* p, const float* f) {
+    Block* b = (Block*)p;
+    b->has_freqs = f != nullptr;
+    if (f) b->rope_freqs.assign(f, f + b->head_dim / 2);
+}
+
+void oracle_block_set_qk_norm(void* p, const float* qw, const float* kw) {
+    Block* b = (Block*)p;
+    b->has_qn = qw != nullptr;
+    b->has_kn = kw != nullptr;
+    if (qw) b->q_norm.assign(qw, qw + b->head_dim);
+    if (kw) b->k_norm.assign(kw, kw + b->head_dim);
+}
+
+void oracle_block_set_bias(void* p, const float* bq, const float* bk, const float* bv) {
+    Block* b = (Block*)p;
+    b->has_bq = bq != nullptr; b->has_bk = bk != nullptr; b->has_bv = bv != nullptr;
+    if (bq) b->b_q.assign(bq, bq + b->q_dim());
+    if (bk) b->b_k.assign(bk, bk + b->kv_dim());
+    if (bv) b->b_v.assign(bv, bv + b->kv_dim());
+}
+
+// src/shainet/transformer/llama_block.cr:116-122
+void oracle_block_clear(void* p) {
+    Block* b = (Block*)p;
+    for (auto& v : b->k_cache) v.clear();
+    for (auto& v : b->v_cache) v.clear();
+    b->cache_len = 0;
+}
+
+int oracle_block_len(void* p) { return ((Block*)p)->cache_len; }
+
+void oracle_inv_freq(void* p, float* out) {
+    Block* b = (Block*)p;
+    for (int i = 0; i < b->head_dim / 2; ++i) out[i] = b->inv_freq(i);
+}
+
+// Fill the caches directly (already-rotated K rows), layout [KV][len][hd].
+// Used to stand in for a long prefill when only decode is under test.
+void oracle_block_import(void* p, const float* k, const float* v, int len) {
+    Block* b = (Block*)p;
+    size_t per = (size_t)len * b->head_dim;
+    for (int h = 0; h < b->num_kv_heads; ++h) {
+        b->k_cache[h].assign(k + h * per, k + (h + 1) * per);
+        b->v_cache[h].assign(v + h * per, v + (h + 1) * per);
+    }
+    b->cache_len = len;
+}
+
+void oracle_block_export(void* p, float* k, float* v) {
+    Block* b = (Block*)p;
+    size_t per = (size_t)b->cache_len * b->head_dim;
+    for (int h = 0; h < b->num_kv_heads; ++h) {
+        std::memcpy(k + h * per, b->k_cache[h].data(), per * sizeof(float));
+        std::memcpy(v + h * per, b->v_cache[h].data(), per * sizeof(float));
+    }
+}
+
+// The part of attention_cached_cpu between the projections and o_proj
+// (src/shainet/transformer/llama_block.cr:256-296): bias, QK-norm, K RoPE +
+// append, then the per-head loop.  q_full [T, q_dim], k_new/v_new [T, kv_dim]
+// are the raw projection outputs and are left untouched; out is [T, q_dim].
+// threads > 1 runs the (independent) query heads under OpenMP; results are
+// identical because each head's arithmetic is unchanged.
+void oracle_block_attend_cached(void* p, const float* q_in, const float* k_in, const float* v_in,
+                                int new_tokens, float* out, int threads, int mode) {
+    Block* b = (Block*)p;
+    const int hd = b->head_dim, qd = b->q_dim(), kvd = b->kv_dim();
+    const float scale = (float)(1.0 / std::sqrt((double)hd));
+    const int start_pos = b->cache_len;
+    std::vector<float> q(q_in, q_in + (size_t)new_tokens * qd);
+    std::vector<float> k(k_in, k_in + (size_t)new_tokens * kvd);
+    std::vector<float> v(v_in, v_in + (size_t)new_tokens * kvd);
+    if (b->has_bq) add_bias(q.data(), new_tokens, qd, b->b_q.data());
+    if (b->has_bk) add_bias(k.data(), new_tokens, kvd, b->b_k.data());
+    if (b->has_bv) add_bias(v.data(), new_tokens, kvd, b->b_v.data());
+    if (b->has_qn) head_rmsnorm(q.data(), new_tokens, qd, b->num_heads, hd, b->q_norm.data(), b->eps);
+    if (b->has_kn) head_rmsnorm(k.data(), new_tokens, kvd, b->num_kv_heads, hd, b->k_norm.data(), b->eps);
+
+    std::vector<float> rotated(hd, 0.0f);
+    for (int kv_h = 0; kv_h < b->num_kv_heads; ++kv_h) {
+        int kv_col = kv_h * hd;
+        for (int t = 0; t < new_tokens; ++t) {
+            std::fill(rotated.begin(), rotated.end(), 0.0f);
+            rope_row(*b, k.data() + (size_t)t * kvd + kv_col, start_pos + t, rotated.data());
+            b->k_cache[kv_h].insert(b->k_cache[kv_h].end(), rotated.begin(), rotated.end());
+            const float* vr = v.data() + (size_t)t * kvd + kv_col;
+            b->v_cache[kv_h].insert(b->v_cache[kv_h].end(), vr, vr + hd);
+        }
+    }
+    const int total_len = b->cache_len + new_tokens;
+    b->cache_len = total_len;
+
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : 1;
+#pragma omp parallel for num_threads(nt) schedule(dynamic, 1)
+#endif
+    for (int h = 0; h < b->num_heads; ++h)
+        attend_head(*b, h, q.data(), out, new_tokens, start_pos, total_len, scale, mode);
+}
+
+// Attention only, over the caches as they stand, with q rows that are already
+// biased/normalised but NOT rotated (attention_heads_cpu itself,
+// llama_block.cr:302-401).  Used for the timed CPU baseline.
+void oracle_block_attend_only(void* p, const float* q, int new_tokens, int start_pos, float* out,
+                              int threads, int mode) {
+    Block* b = (Block*)p;
+    const float scale = (float)(1.0 / std::sqrt((double)b->head_dim));
+    const int total_len = start_pos + new_tokens;
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : 1;
+#pragma omp parallel for num_threads(nt) schedule(dynamic, 1)
+#endif
+    for (int h = 0; h < b->num_heads; ++h)
+        attend_head(*b, h, q, out, new_tokens, start_pos, total_len, scale, mode);
+}
+
+// attention_full_cpu between the projections and o_proj
+// (src/shainet/transformer/llama_block.cr:217-240, :678-716): no cache,
+// positions start at 0, dense S x S scores through the f64-accumulating matmul.
+void oracle_block_attend_full(void* p, const float* q_in, const float* k_in, const float* v_in,
+                              int seq_len, float* out) {
+    Block* b = (Block*)p;
+    const int hd = b->head_dim, qd = b->q_dim(), kvd = b->kv_dim();
+    const float scale = (float)(1.0 / std::sqrt((double)hd));
+    const int heads_per_kv = b->num_heads / b->num_kv_heads;
+    std::vector<float> q(q_in, q_in + (size_t)seq_len * qd);
+    std::vector<float> k(k_in, k_in + (size_t)seq_len * kvd);
+    std::vector<float> v(v_in, v_in + (size_t)seq_len * kvd);
+    if (b->has_bq) add_bias(q.data(), seq_len, qd, b->b_q.data());
+    if (b->has_bk) add_bias(k.data(), seq_len, kvd, b->b_k.data());
+    if (b->has_bv) add_bias(v.data(), seq_len, kvd, b->b_v.data());
+    if (b->has_qn) head_rmsnorm(q.data(), seq_len, qd, b->num_heads, hd, b->q_norm.data(), b->eps);
+    if (b->has_kn) head_rmsnorm(k.data(), seq_len, kvd, b->num_kv_heads, hd, b->k_norm.data(), b->eps);
+
+    std::vector<float> q_h((size_t)seq_len * hd), k_h((size_t)seq_len * hd), v_h((size_t)seq_len * hd);
+    std::vector<float> k_t((size_t)seq_len * hd), scores((size_t)seq_len * seq_len);
+    std::vector<float> weights((size_t)seq_len * seq_len), attn_out((size_t)seq_len * hd), tmp(hd);
+    for (int h = 0; h < b->num_heads; ++h) {
+        int q_col = h * hd, kv_col = (h / heads_per_kv) * hd;
+        for (int s = 0; s < seq_len; ++s) {
+            // extract_head then apply_rope!(…, 0): llama_block.cr:662-666, :678-693
+            rope_row(*b, q.data() + (size_t)s * qd + q_col, s, tmp.data());
+            if (hd % 2) tmp[hd - 1] = q[(size_t)s * qd + q_col + hd - 1];
+            std::memcpy(&q_h[(size_t)s * hd], tmp.data(), hd * sizeof(float));
+            rope_row(*b, k.data() + (size_t)s * kvd + kv_col, s, tmp.data());
+            if (hd % 2) tmp[hd - 1] = k[(size_t)s * kvd + kv_col + hd - 1];
+            std::memcpy(&k_h[(size_t)s * hd], tmp.data(), hd * sizeof(float));
+            std::memcpy(&v_h[(size_t)s * hd], v.data() + (size_t)s * kvd + kv_col, hd * sizeof(float));
+        }
+        for (int s = 0; s < seq_len; ++s)
+            for (int d = 0; d < hd; ++d) k_t[(size_t)d * seq_len + s] = k_h[(size_t)s * hd + d];
+        matmul_f64acc(q_h.data(), k_t.data(), seq_len, hd, seq_len, scores.data());
+        std::fill(weights.begin(), weights.end(), 0.0f);
+        for (int i = 0; i < seq_len; ++i) {
+            float max_val = -std::numeric_limits<float>::infinity();
+            for (int j = 0; j <= i; ++j) {
+                float sv = scores[(size_t)i * seq_len + j] * scale;
+                if (sv > max_val) max_val = sv;
+            }
+            float exp_sum = 0.0f;
+            for (int j = 0; j <= i; ++j) {
+                float e = (float)std::exp((double)(scores[(size_t)i * seq_len + j] * scale - max_val));
+                weights[(size_t)i * seq_len + j] = e;
+                exp_sum += e;
+            }
+            for (int j = 0; j <= i; ++j) weights[(size_t)i * seq_len + j] = weights[(size_t)i * seq_len + j] / exp_sum;
+        }
+        matmul_f64acc(weights.data(), v_h.data(), seq_len, seq_len, hd, attn_out.data());
+        for (int s = 0; s < seq_len; ++s)
+            for (int d = 0; d < hd; ++d) out[(size_t)s * qd + q_col + d] = attn_out[(size_t)s * hd + d];
+    }
+}
+
+// src/shainet/transformer/rope.cr:7-33 — the free-standing RoPE module, all in f64.
+void oracle_rope_apply(const float* x, int seq_len, int head_dim, int start_pos, double theta, float* out) {
+    int half = head_dim / 2;
+    for (int pos = 0; pos < seq_len; ++pos) {
+        int actual = pos + start_pos;
+        for (int i = 0; i < half; ++i) {
+            double freq = 1.0 / std::pow(theta, 2.0 * (double)i / (double)head_dim);
+            double angle = (double)actual * freq;
+            double c = std::cos(angle), s = std::sin(angle);
+            double x0 = x[(size_t)pos * head_dim + i];
+            double x1 = x[(size_t)pos * head_dim + i + half];
+            out[(size_t)pos * head_dim + i] = (float)(x0 * c - x1 * s);
+            out[(size_t)pos * head_dim + i + half] = (float)(x1 * c + x0 * s);
+        }
+        if (head_dim % 2) out[(size_t)pos * head_dim + head_dim - 1] = x[(size_t)pos * head_dim + head_dim - 1];
+    }
+}
+
+// src/shainet/hf_loader.cr:235-265 — LLaMA-3 "llama3" rope_scaling table.
+void oracle_llama3_rope_freqs(double theta, int head_dim, double factor, double low_freq_factor,
+                              double high_freq_factor, double old_ctx, float* out) {
+    double low_wl = old_ctx / low_freq_factor;
+    double high_wl = old_ctx / high_freq_factor;
+    for (int i = 0; i < head_dim / 2; ++i) {
+        double inv = 1.0 / std::pow(theta, 2.0 * (double)i / (double)head_dim);
+        double wavelen = 2.0 * M_PI / inv;
+        double ni;
+        if (wavelen < high_wl) ni = inv;
+        else if (wavelen > low_wl) ni = inv / factor;
+        else {
+            double smooth = (old_ctx / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor);
+            ni = (1.0 - smooth) * inv / factor + smooth * inv;
+        }
+        out[i] = (float)ni;
+    }
+}
+
+// ---- block-level pieces needed only to replay the reference's tiny-llama
+// ---- cache-consistency spec (spec/rope_kv_cache_spec.cr:30-59).
+
+void oracle_matmul(const float* a, const float* b, int M, int K, int N, float* out) {
+    matmul_f64acc(a, b, M, K, N, out);
+}
+
+// src/shainet/transformer/rms_norm.cr:18-37
+void oracle_rmsnorm(const float* x, int rows, int cols, const float* gamma, double eps, float* out) {
+    for (int i = 0; i < rows; ++i) {
+        double sq = 0.0;
+        for (int j = 0; j < cols; ++j) { double v = x[(size_t)i * cols + j]; sq += v * v; }
+        double rms = std::sqrt(sq / (double)cols + eps);
+        for (int j = 0; j < cols; ++j)
+            out[(size_t)i * cols + j] = (float)(((double)x[(size_t)i * cols + j] / rms) * (double)gamma[j]);
+    }
+}
+
+// src/shainet/transformer/swiglu_ff.cr:76-91 (gate/up/down are [in, out] row-major)
+void oracle_swiglu(const float* x, int rows, int d_model, int hidden, const float* gate_w,
+                   const float* up_w, const float* down_w, float* out) {
+    std::vector<float> gate((size_t)rows * hidden), up((size_t)rows * hidden), hid((size_t)rows * hidden);
+    matmul_f64acc(x, gate_w, rows, d_model, hidden, gate.data());
+    matmul_f64acc(x, up_w, rows, d_model, hidden, up.data());
+    for (size_t i = 0; i < hid.size(); ++i) {
+        double g = gate[i];
+        hid[i] = (float)((g / (1.0 + std::exp(-g))) * (double)up[i]);
+    }
+    matmul_f64acc(hid.data(), down_w, rows, hidden, d_model, out);
+}
+
+// src/shainet/math/simple_matrix.cr:39-48
+void oracle_add(const float* a, const float* b, size_t n, float* out) {
+    for (size_t i = 0; i < n; ++i) out[i] = (float)((double)a[i] + (double)b[i]);
+}
+
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+}  // extern "C"

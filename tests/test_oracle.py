@@ -1,0 +1,174 @@
+"""Pins the CPU oracle to what the reference's own specs assert for this path."""
+import math
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_rope_identity_at_position_zero():
+    # spec/rope_kv_cache_spec.cr:5-10
+    m = np.arange(1, 9, dtype=np.float32)[None, :]
+    out = O.rope_apply(m, 0, 10000.0)
+    assert np.allclose(out, m, atol=1e-5)
+
+
+def test_rope_half_split_pairing():
+    # spec/rope_kv_cache_spec.cr:12-26 — head_dim 4, position 1, unit vector
+    m = np.array([[1.0, 0.0, 0.0, 0.0]], np.float32)
+    out = O.rope_apply(m, 1, 10000.0)
+    assert abs(out[0, 0] - math.cos(1.0)) < 1e-4
+    assert abs(out[0, 2] - math.sin(1.0)) < 1e-4
+    assert out[0, 1] == 0.0 and out[0, 3] == 0.0
+
+
+def test_block_rope_matches_module_rope():
+    # LlamaBlock's private fp32 rotation (llama_block.cr:678-693) and the f64
+    # RoPE module (rope.cr:7-33) describe the same rotation.
+    rng = np.random.default_rng(0)
+    hd, S = 8, 5
+    a = O.OracleAttention(1, 1, hd, 10000.0)
+    k = rng.standard_normal((S, hd)).astype(np.float32)
+    a.attend_cached(np.zeros((S, hd), np.float32), k, k)
+    kc, _ = a.export_cache()
+    assert np.allclose(kc[0], O.rope_apply(k, 0, 10000.0), atol=2e-6)
+
+
+def _tiny_llama():
+    z = np.load(os.path.join(GOLDEN, "tiny_llama_slice.npz"))
+    d, H, KV = int(z["hidden_size"]), int(z["num_heads"]), int(z["num_kv_heads"])
+    blocks = []
+    for l in range(int(z["num_layers"])):
+        w = {k: z[f"l{l}.{k}"] for k in ("w_q", "w_k", "w_v", "w_o", "gate", "up", "down", "norm1", "norm2")}
+        blocks.append(O.OracleLlamaBlock(d, H, KV, d // H, float(z["eps"]), float(z["rope_theta"]), w))
+    return z["embed_rows"], blocks
+
+
+def test_tiny_llama_cache_consistency():
+    # spec/rope_kv_cache_spec.cr:30-59: uncached forward of tokens [1,42,100,7]
+    # vs prefill of 3 + one cached step; last rows agree within 1e-3.
+    emb, blocks = _tiny_llama()
+    full = emb.copy()
+    for b in blocks:
+        full = b.forward(full)
+    for b in blocks:
+        b.clear_cache()
+    pre = emb[:3].copy()
+    for b in blocks:
+        pre = b.forward_cached(pre)
+    inc = emb[3:4].copy()
+    for b in blocks:
+        inc = b.forward_cached(inc)
+    assert np.all(np.isfinite(inc)) and np.abs(inc).max() > 0
+    assert np.abs(inc[0] - full[-1]).max() < 1e-3
+    # the oracle is far inside the spec's tolerance
+    assert np.abs(inc[0] - full[-1]).max() < 1e-5
+
+
+def test_cached_equals_uncached_gqa():
+    # Shapes of spec/llama_attention_gpu_spec.cr:17-66: 8 heads / 4 KV heads, head_dim 8
+    rng = np.random.default_rng(42)
+    H, KV, hd = 8, 4, 8
+    q = rng.uniform(-1, 1, (9, H * hd)).astype(np.float32)
+    k = rng.uniform(-1, 1, (9, KV * hd)).astype(np.float32)
+    v = rng.uniform(-1, 1, (9, KV * hd)).astype(np.float32)
+    a = O.OracleAttention(H, KV, hd)
+    full = a.attend_full(q, k, v)
+    outs = [a.attend_cached(q[:6], k[:6], v[:6])]
+    for t in range(6, 9):
+        outs.append(a.attend_cached(q[t:t + 1], k[t:t + 1], v[t:t + 1]))
+    assert np.abs(np.concatenate(outs) - full).max() < 1e-5
+    assert a.cache_len == 9
+
+
+def test_nil_bias_equals_zero_bias():
+    # spec/llama_qkv_bias_spec.cr:8-40 (1e-6) and :42-72 (a real bias moves the output)
+    rng = np.random.default_rng(3)
+    H, KV, hd, T = 4, 2, 8, 5
+    q = rng.standard_normal((T, H * hd)).astype(np.float32)
+    k = rng.standard_normal((T, KV * hd)).astype(np.float32)
+    v = rng.standard_normal((T, KV * hd)).astype(np.float32)
+    a = O.OracleAttention(H, KV, hd).attend_cached(q, k, v)
+    z = O.OracleAttention(H, KV, hd, b_q=np.zeros(H * hd), b_k=np.zeros(KV * hd), b_v=np.zeros(KV * hd)).attend_cached(q, k, v)
+    assert np.abs(a - z).max() <= 1e-6
+    nz = O.OracleAttention(H, KV, hd, b_q=np.full(H * hd, 0.5), b_k=np.full(KV * hd, -0.3),
+                           b_v=np.full(KV * hd, 0.2)).attend_cached(q, k, v)
+    assert np.abs(a - nz).sum() > 0.01
+
+
+def test_clear_cache_and_growth_replay():
+    # spec/llama_attention_gpu_spec.cr:68-104: 290-token prefill + 10 steps, twice after clear
+    rng = np.random.default_rng(7)
+    H, KV, hd = 4, 2, 8
+    a = O.OracleAttention(H, KV, hd)
+    seq = [(rng.uniform(-1, 1, (n, H * hd)), rng.uniform(-1, 1, (n, KV * hd)), rng.uniform(-1, 1, (n, KV * hd)))
+           for n in [290] + [1] * 10]
+    first = [a.attend_cached(*s) for s in seq]
+    assert a.cache_len == 300
+    a.clear_cache()
+    assert a.cache_len == 0
+    second = [a.attend_cached(*s) for s in seq]
+    for x, y in zip(first, second):
+        assert np.array_equal(x, y)
+
+
+def test_threads_do_not_change_results():
+    rng = np.random.default_rng(5)
+    H, KV, hd, T = 8, 2, 16, 33
+    q = rng.standard_normal((T, H * hd)); k = rng.standard_normal((T, KV * hd)); v = rng.standard_normal((T, KV * hd))
+    x = O.OracleAttention(H, KV, hd).attend_cached(q, k, v, threads=1)
+    y = O.OracleAttention(H, KV, hd).attend_cached(q, k, v, threads=4)
+    assert np.array_equal(x, y)
+
+
+def test_f64_truth_close_to_fp32_path():
+    rng = np.random.default_rng(11)
+    H, KV, hd, L = 8, 2, 64, 2048
+    kc = rng.standard_normal((KV, L, hd)).astype(np.float32)
+    vc = rng.standard_normal((KV, L, hd)).astype(np.float32)
+    a = O.OracleAttention(H, KV, hd, 500000.0)
+    a.import_cache(kc, vc)
+    q = rng.standard_normal((1, H * hd)).astype(np.float32)
+    x = a.attend_only(q, L - 1, mode=0)
+    y = a.attend_only(q, L - 1, mode=1)
+    assert np.abs(x - y).max() / np.abs(y).max() < 1e-5
+
+
+def test_qk_norm_formula():
+    # llama_block.cr:615-641: v * f32(1/sqrt(f64(ss/hd)+eps)) * w, before RoPE
+    rng = np.random.default_rng(13)
+    hd = 16
+    w = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    k = rng.standard_normal((1, hd)).astype(np.float32)
+    a = O.OracleAttention(1, 1, hd, 1e6, 1e-6, q_norm=w, k_norm=w)
+    a.attend_cached(k, k, k)
+    kc, vc = a.export_cache()
+    ss = np.float32(0)
+    for d in range(hd):
+        ss = np.float32(ss + np.float32(k[0, d] * k[0, d]))
+    inv = np.float32(1.0 / math.sqrt(float(np.float32(ss / np.float32(hd))) + 1e-6))
+    expect = (k[0] * inv) * w          # position 0: rotation is the identity
+    assert np.array_equal(kc[0, 0], expect.astype(np.float32))
+    assert np.array_equal(vc[0, 0], k[0])  # V is neither normalised nor rotated
+
+
+def test_llama3_scaled_freqs():
+    # hf_loader.cr:235-265 with Llama-3.2 parameters
+    hd, theta = 64, 500000.0
+    f = O.llama3_rope_freqs(theta, hd, 32.0, 1.0, 4.0, 8192.0)
+    base = np.array([1.0 / theta ** (2.0 * i / hd) for i in range(hd // 2)])
+    assert f[0] == np.float32(base[0])                       # short wavelengths untouched
+    assert np.isclose(f[-1], base[-1] / 32.0, rtol=1e-6)     # long wavelengths divided by factor
+    assert np.all(np.diff(f) < 0)
+    a = O.OracleAttention(4, 2, hd, theta, rope_freqs=f)
+    assert np.array_equal(a.inv_freq(), f)
+
+
+def test_bad_head_split_rejected():
+    # llama_block.cr:80
+    with pytest.raises(ValueError):
+        O.OracleAttention(6, 4, 8)
