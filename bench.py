@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path (RoPE + KV append + GQA decode attention).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload cfg5]
+
+One "step" is one decode token through every layer's attention (fused
+bias/QK-norm/RoPE/append kernel, split-K decode kernel, split merge) over
+synthetic N(0,1) KV caches of the named shape.  The headline `value` is decode
+tokens/s with inputs resident in HBM; `e2e` is the same metric through the
+host-pointer C-ABI entry (pinned host inputs, H2D and D2H inside the timed
+region); `roofline` is the attention kernel's algorithmic HBM bytes over its
+device time against the measured copy bandwidth; `cpu_baseline` is the CPU
+oracle (a port of the reference's Crystal host path) timed on this host.
+
+`--impl reference` times that CPU port alone (the reference's host language has
+no compiler on this image, so its own binary cannot be run).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE config 5: Qwen3-30B-A3B-shaped long-context decode attention
+    "cfg5": dict(name="cfg5: Qwen3-30B-A3B attention, 48 layers, batch 1, fp32 KV cache ctx 32768, decode",
+                 H=32, KV=4, hd=128, theta=1e6, qk_norm=True, layers=48, ctx=32768),
+    # BASELINE config 2 (attention part): LLaMA-3.2-1B, 16 layers, ctx 4096
+    "cfg2": dict(name="cfg2: LLaMA-3.2-1B attention, 16 layers, batch 1, fp32 KV cache ctx 4096, decode",
+                 H=32, KV=8, hd=64, theta=5e5, qk_norm=False, layers=16, ctx=4096),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def decode_bytes(wl, L, kv_heads=None):
+    """Algorithmic HBM bytes of one layer-step at visible length L: K and V read
+    once, the new row written, q read and out written."""
+    KV = wl["KV"] if kv_heads is None else kv_heads
+    H = wl["H"] * KV // wl["KV"]
+    return 2 * KV * L * wl["hd"] * 4 + 2 * KV * wl["hd"] * 4 + 2 * H * wl["hd"] * 4
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t is not None:
+            self._t.join()
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_port_rate(wl, threads, layers_sampled, steps, seed=5001):
+    """Decode tokens/s of the CPU oracle: `steps` steps of `layers_sampled` layers at
+    the workload's context, scaled to the full layer count."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(seed)
+    H, KV, hd = wl["H"], wl["KV"], wl["hd"]
+    kw = {}
+    if wl["qk_norm"]:
+        kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
+                  k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
+    o = O.OracleAttention(H, KV, hd, wl["theta"], 1e-6, **kw)
+    kc = rng.standard_normal((KV, wl["ctx"], hd), dtype=np.float32)
+    vc = rng.standard_normal((KV, wl["ctx"], hd), dtype=np.float32)
+    o.import_cache(kc, vc)
+    q = rng.standard_normal((1, H * hd)).astype(np.float32)
+    k = rng.standard_normal((1, KV * hd)).astype(np.float32)
+    v = rng.standard_normal((1, KV * hd)).astype(np.float32)
+    per_step = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        for _ in range(layers_sampled):
+            o.attend_cached(q, k, v, threads=threads)
+        per_step.append(time.perf_counter() - t0)
+    return per_step
+
+
+def run_reference(args, wl, rank, world):
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    threads = O.max_threads()
+    layers_sampled = 1
+    cpu_port_rate(wl, threads, 1, max(1, min(args.warmup, 2)))            # warm-up (page in, thread pool)
+    t0 = time.perf_counter()
+    per_step = cpu_port_rate(wl, threads, layers_sampled, args.steps)
+    wall = time.perf_counter() - t0
+    sec_per_token = float(np.sum(per_step)) / args.steps * wl["layers"] / layers_sampled
+    value = 1.0 / sec_per_token
+    sample = (f"{args.steps} decode steps x {layers_sampled} of {wl['layers']} layers at ctx {wl['ctx']}, "
+              f"scaled to all layers; OpenMP over query heads")
+    line = {
+        "impl": "reference", "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_token * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl["name"], "timed": "CPU port of the reference's Crystal attention path "
+                   "(no Crystal compiler on this image)", "wall_s": wall},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, wl, rank, world, local_rank):
+    import torch
+    import shainet_b200 as S
+    from shainet_b200 import build
+    build.build()
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+    H, KV, hd, layers, ctx_len = wl["H"], wl["KV"], wl["hd"], wl["layers"], wl["ctx"]
+    if KV % world != 0:
+        raise SystemExit(f"{world} ranks do not divide {KV} kv heads (sequence-split sharding is not built yet)")
+    KVl, Hl = KV // world, H // world      # this rank's kv-head group(s) and their query heads
+    qd, kd = Hl * hd, KVl * hd
+    K, W = args.steps, args.warmup
+    K_roof = min(K, 32)
+    K_e2e, W_e2e = min(K, 64), 3
+
+    rng = np.random.default_rng(5000 + rank)
+    ctx = S.AttnContext(local_rank)
+    cap = ctx_len + max(K, W, K_roof, K_e2e + W_e2e) + 8
+    blocks = []
+    for l in range(layers):
+        kw = {}
+        if wl["qk_norm"]:
+            kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
+                      k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
+        b = S.LlamaAttention(ctx, Hl, KVl, hd, wl["theta"], 1e-6, initial_capacity=cap, **kw)
+        b.cache.fill_normal(ctx_len, 5001 + 1000 * rank + l)
+        blocks.append(b)
+
+    NV = 4  # input variants cycled over steps
+    g = torch.Generator(device=dev)
+    g.manual_seed(5002 + rank)
+    q_d = torch.randn(NV, layers, qd, device=dev, generator=g)
+    k_d = torch.randn(NV, layers, kd, device=dev, generator=g)
+    v_d = torch.randn(NV, layers, kd, device=dev, generator=g)
+    out_d = torch.empty(layers, qd, device=dev)
+    gathered = torch.empty(layers, world, qd, device=dev) if world > 1 else None
+    stream = torch.cuda.current_stream().cuda_stream
+    esz = q_d.element_size()
+
+    def reset():
+        for b in blocks:
+            b.cache.truncate(ctx_len)
+
+    def step(i):
+        vi = i % NV
+        for l, b in enumerate(blocks):
+            b.forward_cached_dev(q_d[vi, l].data_ptr(), k_d[vi, l].data_ptr(), v_d[vi, l].data_ptr(),
+                                 out_d[l].data_ptr(), 1, stream)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])   # head outputs before o_proj
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    for i in range(max(W, 3)):
+        step(i)
+    barrier()
+    sampler.start()
+    reset()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    ctx.sync()
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- roofline pass: the attention kernels alone, bracketed by events inside the library ----
+    reset()
+    ctx.timing_enable(True)
+    for i in range(K_roof):
+        step(i)
+    barrier()
+    kernel_ms, launches = ctx.timing_read()
+    ctx.timing_enable(False)
+    clocks = sampler.stop()
+
+    # ---- end to end: host-pointer C-ABI entry, pinned host inputs, blocking ----
+    reset()
+    hq = torch.randn(NV, layers, qd).pin_memory()
+    hk = torch.randn(NV, layers, kd).pin_memory()
+    hv = torch.randn(NV, layers, kd).pin_memory()
+    ho = torch.empty(layers, qd).pin_memory()
+    fwd_host = ctx.L.shainet_attn_forward_host
+    FP = C.POINTER(C.c_float)
+
+    def host_step(i):
+        vi = i % NV
+        for l, b in enumerate(blocks):
+            rc = fwd_host(ctx.h, b.cache.h, C.cast(hq[vi, l].data_ptr(), FP), C.cast(hk[vi, l].data_ptr(), FP),
+                          C.cast(hv[vi, l].data_ptr(), FP), C.cast(ho[l].data_ptr(), FP), 1, b.scale, 0)
+            if rc:
+                S.check(rc)
+            if world > 1:
+                out_d[l].copy_(ho[l], non_blocking=True)
+                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
+    for i in range(W_e2e):
+        host_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K_e2e):
+        host_step(i)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        L_avg = ctx_len + (K_roof + 1) / 2.0
+        bytes_per_launch = decode_bytes(wl, L_avg, KVl)
+        avg_kernel_s = kernel_ms / 1e3 / max(launches, 1)
+        achieved = bytes_per_launch / avg_kernel_s / 1e9
+        line = {
+            "metric": "decode_attn_tokens_per_s", "value": K / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl["name"], "layers": layers, "num_heads": H, "num_kv_heads": KV, "head_dim": hd,
+                       "ctx": ctx_len, "sharding": f"kv-head groups over {world} rank(s)",
+                       "l2": "working set per step (all layers' K/V) is far larger than L2; no flush needed",
+                       "hbm_gbs_whole_step": decode_bytes(wl, ctx_len + (K + 1) / 2.0, KVl) * layers / (ms / K / 1e3) / 1e9},
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "attn_splitk_kernel (+ split merge)", "achieved": achieved,
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "bytes_per_launch": bytes_per_launch,
+                         "avg_launch_us": avg_kernel_s * 1e6, "launches_timed": launches},
+            "e2e": {"value": K_e2e / e2e_s, "unit": "tokens/s", "steps": K_e2e,
+                    "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz, "d2h_bytes_per_step": layers * qd * esz},
+            "gpu_launches": 3 * layers * K,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle as O
+            threads = O.max_threads()
+            cpu_port_rate(wl, threads, 1, 1)
+            per_step = cpu_port_rate(wl, threads, 2, 4)
+            spt = float(np.mean(per_step)) * layers / 2
+            one = cpu_port_rate(wl, 1, 1, 1)
+            line["cpu_baseline"] = {"value": 1.0 / spt, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": f"4 decode steps x 2 of {layers} layers at ctx {ctx_len}, scaled to all "
+                                              "layers; OpenMP over query heads",
+                                    "single_thread_value": 1.0 / (float(one[0]) * layers)}
+        print(json.dumps(line), flush=True)
+    for b in blocks:
+        b.close()
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging / profiling)")
+    ap.add_argument("--ctx", type=int, default=None, help="override the context length (debugging / profiling)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = dict(WORKLOADS[args.workload])
+    if args.layers:
+        wl["layers"] = args.layers
+        wl["name"] += f" [layers={args.layers}]"
+    if args.ctx:
+        wl["ctx"] = args.ctx
+        wl["name"] += f" [ctx={args.ctx}]"
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+    else:
+        run_ours(args, wl, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+/* libshainet_attn — C ABI of the B200 (sm_100a) attention path for SHAInet's
+ * LLaMA/Qwen decoder block: (bias +) per-head RMSNorm + RoPE + KV-cache append +
+ * grouped-query causal attention over the cache, for prefill and decode.
+ *
+ * Plain C, plain pointers and sizes.  Every function returns an int status
+ * (0 = ok, negative = error, see SHAINET_ATTN_E_*) and never prints or aborts;
+ * shainet_attn_last_error() gives the message of the calling thread's last
+ * failure.  File:line citations name the reference code each entry replaces
+ * (paths inside the SHAInet project).
+ *
+ * Threading: a context and the caches created from it are used by one host
+ * thread at a time (the contract of the reference's mutex-serialised Network).
+ * There is no CPU fallback: without a CUDA device every call fails.
+ */
+#ifndef SHAINET_ATTN_H
+#define SHAINET_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SHAINET_ATTN_VERSION 100
+
+#define SHAINET_ATTN_OK 0
+#define SHAINET_ATTN_E_INVALID (-1)      /* bad argument / shape / null pointer / misaligned pointer */
+#define SHAINET_ATTN_E_CUDA (-2)         /* a CUDA runtime call failed */
+#define SHAINET_ATTN_E_NOMEM (-3)        /* device or pinned allocation failed */
+#define SHAINET_ATTN_E_UNSUPPORTED (-4)  /* shape outside what the kernels cover */
+#define SHAINET_ATTN_E_DEVICE_WAIT (-5)  /* a kernel gave up on a bounded wait */
+#define SHAINET_ATTN_E_STATE (-6)        /* call sequence error (e.g. import past capacity) */
+
+/* forward flags */
+#define SHAINET_ATTN_F_GENERIC 1u  /* force the shape-agnostic kernel */
+#define SHAINET_ATTN_F_SPLITK 2u   /* force the split-K decode kernel (error if unsupported) */
+#define SHAINET_ATTN_F_TENSOR 4u   /* force the tcgen05 prefill kernel (error if unsupported) */
+
+typedef struct shainet_attn_ctx shainet_attn_ctx;
+typedef struct shainet_attn_kv shainet_attn_kv;
+
+/* ---- probing: replaces CUDA.fully_available? in LlamaBlock#gpu_attention?
+ * (src/shainet/transformer/llama_block.cr:484-492, src/shainet/cuda.cr:778-780). */
+int shainet_attn_version(void);
+int shainet_attn_device_count(void);
+const char* shainet_attn_last_error(void);
+
+/* ---- context: owns the stream used by the host-pointer entry, the rotated-q
+ * buffer, the split-K partials, pinned staging and the device status word.
+ * Replaces the class-level @@gpu_staging/@@gpu_attn_out/@@gpu_attn_ws/
+ * @@staging_host scratch (src/shainet/transformer/llama_block.cr:57-68, 421-429). */
+int shainet_attn_ctx_create(shainet_attn_ctx** out, int device);
+int shainet_attn_ctx_destroy(shainet_attn_ctx* ctx);
+/* Waits for the context's stream and reports a kernel-side bounded-wait failure. */
+int shainet_attn_ctx_sync(shainet_attn_ctx* ctx);
+/* Bytes of device memory the context's scratch currently holds. */
+size_t shainet_attn_ctx_scratch_bytes(shainet_attn_ctx* ctx);
+/* Kernel timing for roofline reports: while enabled, every forward call
+ * brackets its attention kernel(s) (not the RoPE/append kernel) with CUDA
+ * events on the launching stream.  _read waits for them, returns the summed
+ * device time and the number of bracketed launches since _enable(1), and
+ * clears the record.  The reference only has wall-clock prints
+ * (examples/prof.cr:19-37). */
+int shainet_attn_ctx_timing_enable(shainet_attn_ctx* ctx, int enable);
+int shainet_attn_ctx_timing_read(shainet_attn_ctx* ctx, double* total_ms, int* launches);
+
+/* ---- KV cache of one block: two device buffers [num_kv_heads, capacity,
+ * head_dim] fp32 (the layout of src/shainet/native/cuda_kernels.cu:689-694),
+ * grown x2 (min 256) device-to-device.  Replaces @k_cache/@v_cache/@cache_len,
+ * the device mirror and ensure_gpu_cache! (llama_block.cr:45-56, 497-520),
+ * clear_cache! (:116-122) and finalize (:124-130).  num_heads/num_kv_heads are
+ * the heads THIS cache serves (a rank's slice when kv-head groups are sharded).
+ * RoPE defaults to theta = 10000 as LlamaBlock.new does (:74). */
+int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                           int head_dim, int initial_capacity);
+int shainet_attn_kv_destroy(shainet_attn_kv* kv);
+int shainet_attn_kv_reset(shainet_attn_kv* kv);              /* clear_cache!: length 0, buffers kept */
+int shainet_attn_kv_len(const shainet_attn_kv* kv);          /* @cache_len, or negative status */
+int shainet_attn_kv_capacity(const shainet_attn_kv* kv);     /* @gpu_cache_cap */
+int shainet_attn_kv_reserve(shainet_attn_kv* kv, int total_len);
+/* Drops the newest positions: the length becomes len (<= current length).
+ * clear_cache! (llama_block.cr:116-122) is the len = 0 case; a partial
+ * roll-back lets a caller replay or discard speculative rows. */
+int shainet_attn_kv_truncate(shainet_attn_kv* kv, int len);
+
+/* inv_freq(i) = f32(1 / theta^(2i/head_dim)) computed in double on the host
+ * exactly as llama_block.cr:669-675 does. */
+int shainet_attn_kv_set_rope_theta(shainet_attn_kv* kv, double theta);
+/* Explicit table of head_dim/2 inverse frequencies (LlamaBlock#rope_freqs,
+ * llama_block.cr:25-28; LLaMA-3 scaling from hf_loader.cr:235-265). */
+int shainet_attn_kv_set_rope(shainet_attn_kv* kv, const float* inv_freq_host, int half);
+/* Qwen3 per-head RMSNorm weights (head_dim floats each, either may be NULL)
+ * and its epsilon (LlamaBlock#q_norm/#k_norm, llama_block.cr:19-23, 615-641). */
+int shainet_attn_kv_set_qk_norm(shainet_attn_kv* kv, const float* q_weight_host, const float* k_weight_host,
+                                double eps);
+/* Qwen2 projection biases, sizes num_heads*head_dim, num_kv_heads*head_dim x2;
+ * any may be NULL (LlamaBlock#b_q/#b_k/#b_v, llama_block.cr:35-43, 585-601). */
+int shainet_attn_kv_set_bias(shainet_attn_kv* kv, const float* b_q_host, const float* b_k_host,
+                             const float* b_v_host);
+
+/* Cache contents to/from host arrays laid out [num_kv_heads, len, head_dim]
+ * (K rows are stored rotated, as the reference stores them).  Import sets the
+ * length to len. */
+int shainet_attn_kv_export(shainet_attn_kv* kv, float* k_host, float* v_host, int len);
+int shainet_attn_kv_import(shainet_attn_kv* kv, const float* k_host, const float* v_host, int len);
+/* Fills len positions of K and V with N(0,1) values generated on the device
+ * from seed and sets the length (synthetic long contexts for benchmarks). */
+int shainet_attn_kv_fill_normal(shainet_attn_kv* kv, int len, uint64_t seed);
+/* Raw device pointers of the current buffers (invalidated by growth). */
+int shainet_attn_kv_device_ptrs(shainet_attn_kv* kv, float** k_dev, float** v_dev);
+
+/* ---- the drop-in for attention_heads_gpu (llama_block.cr:407-479) and the
+ * host K-RoPE/append loop before it (:266-286): q [new_tokens, num_heads*head_dim],
+ * k_new/v_new [new_tokens, num_kv_heads*head_dim] are the projection outputs on
+ * the host, NOT yet biased, normalised or rotated; out [new_tokens,
+ * num_heads*head_dim] receives the attention output (input of o_proj).
+ * Positions start at the cache's current length, which grows by new_tokens.
+ * scale is LlamaBlock's f32(1/sqrt(head_dim)) (:249).  Blocking. */
+int shainet_attn_forward_host(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                              const float* v_new, float* out, int new_tokens, float scale, unsigned flags);
+
+/* Same with device pointers (16-byte aligned) on a caller stream (a
+ * cudaStream_t passed as void*; NULL = the context's stream).  Asynchronous. */
+int shainet_attn_forward_dev(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q_dev, const float* k_new_dev,
+                             const float* v_new_dev, float* out_dev, int new_tokens, float scale, unsigned flags,
+                             void* stream);
+
+/* One decode token for each of `batch` sequences in lock step, one launch:
+ * q [batch, q_dim], k_new/v_new [batch, kv_dim], out [batch, q_dim] on the
+ * device.  All caches share one head shape, RoPE table and norm weights (those
+ * of kvs[0]).  The reference has no batched entry (Network#run is batch 1,
+ * src/shainet/basic/network_run.cr:294-315); this serves ragged batched decode. */
+int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* const* kvs, int batch,
+                                     const float* q_dev, const float* k_new_dev, const float* v_new_dev,
+                                     float* out_dev, float scale, unsigned flags, void* stream);
+
+/* ---- symbol-compatible replacements for the two kernels the reference loads
+ * with dlsym from libshainet_cuda_kernels.so (src/shainet/cuda.cr:838-891;
+ * definitions src/shainet/native/cuda_kernels.cu:713-726 and :808-825).  Same
+ * names, argument order and meaning: device pointers, legacy default stream,
+ * q already rotated, ws a scratch of num_heads*new_tokens*(start_pos+new_tokens)
+ * floats.  Errors are printed like the reference does. */
+void kv_cache_append_f32(const float* staging, float* kc, float* vc, int new_tokens, int start_pos,
+                         int num_kv_heads, int head_dim, int capacity);
+void attention_kv_f32(const float* q, const float* kc, const float* vc, float* out, float* ws, int new_tokens,
+                      int start_pos, int num_heads, int heads_per_kv, int head_dim, int capacity, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHAINET_ATTN_H */

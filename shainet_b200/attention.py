@@ -1,0 +1,197 @@
+"""Host-side mirror of the attention state and calls of SHAInet's ``LlamaBlock``
+(src/shainet/transformer/llama_block.cr) over the libshainet_attn C ABI.
+
+``AttnContext`` stands for the class-level scratch of the reference block,
+``KVCache`` for one block's ``@k_cache/@v_cache/@cache_len`` and device mirror,
+``LlamaAttention`` for the slice of ``attention_cached_cpu`` between the q/k/v
+projections and ``o_proj`` (bias, QK-norm, RoPE, append, attention).  Method
+names follow the reference (``forward_cached``, ``clear_cache``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+
+from . import _lib
+from ._lib import F_GENERIC, F_SPLITK, F_TENSOR, ShainetAttnError, check  # noqa: F401
+
+
+def _fp(a: np.ndarray):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _opt(a):
+    return (None, None) if a is None else (lambda x: (x, _fp(x)))(_f32(a))
+
+
+def device_count() -> int:
+    return _lib.load().shainet_attn_device_count()
+
+
+def default_scale(head_dim: int) -> float:
+    """f32(1/sqrt(head_dim)) as llama_block.cr:249 computes it."""
+    return float(np.float32(1.0 / math.sqrt(float(head_dim))))
+
+
+class AttnContext:
+    def __init__(self, device: int = 0):
+        self.L = _lib.load()
+        h = C.c_void_p()
+        check(self.L.shainet_attn_ctx_create(C.byref(h), device))
+        self.h = h
+        self.device = device
+
+    def sync(self):
+        check(self.L.shainet_attn_ctx_sync(self.h))
+
+    def scratch_bytes(self) -> int:
+        return self.L.shainet_attn_ctx_scratch_bytes(self.h)
+
+    def timing_enable(self, on: bool):
+        check(self.L.shainet_attn_ctx_timing_enable(self.h, int(on)))
+
+    def timing_read(self):
+        """(summed device ms of the bracketed attention launches, their count); clears the record."""
+        ms, n = C.c_double(), C.c_int()
+        check(self.L.shainet_attn_ctx_timing_read(self.h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def close(self):
+        if getattr(self, "h", None):
+            check(self.L.shainet_attn_ctx_destroy(self.h))
+            self.h = None
+
+
+class KVCache:
+    def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int, head_dim: int, initial_capacity: int = 0):
+        self.ctx, self.L = ctx, ctx.L
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.q_dim, self.kv_dim = num_heads * head_dim, num_kv_heads * head_dim
+        h = C.c_void_p()
+        check(self.L.shainet_attn_kv_create(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim, initial_capacity))
+        self.h = h
+
+    def close(self):
+        if getattr(self, "h", None):
+            check(self.L.shainet_attn_kv_destroy(self.h))
+            self.h = None
+
+    def __len__(self) -> int:
+        return check(self.L.shainet_attn_kv_len(self.h))
+
+    @property
+    def capacity(self) -> int:
+        return check(self.L.shainet_attn_kv_capacity(self.h))
+
+    def reset(self):
+        check(self.L.shainet_attn_kv_reset(self.h))
+
+    def truncate(self, n: int):
+        check(self.L.shainet_attn_kv_truncate(self.h, n))
+
+    def reserve(self, total_len: int):
+        check(self.L.shainet_attn_kv_reserve(self.h, total_len))
+
+    def set_rope_theta(self, theta: float):
+        check(self.L.shainet_attn_kv_set_rope_theta(self.h, theta))
+
+    def set_rope(self, inv_freq):
+        f = _f32(inv_freq)
+        check(self.L.shainet_attn_kv_set_rope(self.h, _fp(f), f.size))
+
+    def set_qk_norm(self, q_weight, k_weight, eps: float):
+        q, qp = _opt(q_weight)
+        k, kp = _opt(k_weight)
+        check(self.L.shainet_attn_kv_set_qk_norm(self.h, qp, kp, eps))
+
+    def set_bias(self, b_q, b_k, b_v):
+        (q, qp), (k, kp), (v, vp) = _opt(b_q), _opt(b_k), _opt(b_v)
+        check(self.L.shainet_attn_kv_set_bias(self.h, qp, kp, vp))
+
+    def export(self, n: int | None = None):
+        n = len(self) if n is None else n
+        k = np.empty((self.num_kv_heads, n, self.head_dim), np.float32)
+        v = np.empty_like(k)
+        check(self.L.shainet_attn_kv_export(self.h, _fp(k), _fp(v), n))
+        return k, v
+
+    def import_(self, k, v):
+        k, v = _f32(k), _f32(v)
+        if k.shape != v.shape or k.ndim != 3 or k.shape[0] != self.num_kv_heads or k.shape[2] != self.head_dim:
+            raise ValueError("cache arrays must be [num_kv_heads, len, head_dim]")
+        check(self.L.shainet_attn_kv_import(self.h, _fp(k), _fp(v), k.shape[1]))
+
+    def fill_normal(self, n: int, seed: int):
+        check(self.L.shainet_attn_kv_fill_normal(self.h, n, seed))
+
+    def device_ptrs(self):
+        k, v = C.c_void_p(), C.c_void_p()
+        check(self.L.shainet_attn_kv_device_ptrs(self.h, C.byref(k), C.byref(v)))
+        return k.value, v.value
+
+
+class LlamaAttention:
+    """Attention part of ``LlamaBlock``: same constructor meaning for
+    ``num_heads, num_kv_heads, head_dim, rope_theta, eps`` (llama_block.cr:73-92),
+    same optional ``rope_freqs``, ``q_norm/k_norm`` and ``b_q/b_k/b_v`` properties,
+    ``forward_cached`` taking the projection outputs where the reference calls
+    ``attention_heads_gpu`` (:292-296), ``clear_cache`` for ``clear_cache!``."""
+
+    def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int | None = None, head_dim: int = 64,
+                 rope_theta: float = 10000.0, eps: float = 1e-6, rope_freqs=None, q_norm=None, k_norm=None,
+                 b_q=None, b_k=None, b_v=None, initial_capacity: int = 0):
+        num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
+        self.ctx = ctx
+        self.cache = KVCache(ctx, num_heads, num_kv_heads, head_dim, initial_capacity)
+        self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
+        self.q_dim, self.kv_dim = self.cache.q_dim, self.cache.kv_dim
+        self.scale = default_scale(head_dim)
+        if rope_freqs is not None:
+            self.cache.set_rope(rope_freqs)
+        else:
+            self.cache.set_rope_theta(rope_theta)
+        if q_norm is not None or k_norm is not None:
+            self.cache.set_qk_norm(q_norm, k_norm, eps)
+        if b_q is not None or b_k is not None or b_v is not None:
+            self.cache.set_bias(b_q, b_k, b_v)
+
+    @property
+    def cache_len(self) -> int:
+        return len(self.cache)
+
+    def clear_cache(self):
+        self.cache.reset()
+
+    def forward_cached(self, q, k_new, v_new, flags: int = 0) -> np.ndarray:
+        """Host arrays in, host array out (the reference's SimpleMatrix path)."""
+        q, k_new, v_new = _f32(q), _f32(k_new), _f32(v_new)
+        T = q.shape[0]
+        if q.shape != (T, self.q_dim) or k_new.shape != (T, self.kv_dim) or v_new.shape != (T, self.kv_dim):
+            raise ValueError("q must be [T, num_heads*head_dim]; k_new, v_new [T, num_kv_heads*head_dim]")
+        out = np.empty((T, self.q_dim), np.float32)
+        check(self.ctx.L.shainet_attn_forward_host(self.ctx.h, self.cache.h, _fp(q), _fp(k_new), _fp(v_new), _fp(out),
+                                                   T, self.scale, flags))
+        return out
+
+    def forward_cached_dev(self, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, new_tokens: int, stream: int = 0,
+                           flags: int = 0):
+        """Device pointers (ints) on a caller stream; asynchronous."""
+        check(self.ctx.L.shainet_attn_forward_dev(self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, new_tokens,
+                                                  self.scale, flags, stream or None))
+
+    def close(self):
+        self.cache.close()
+
+
+def forward_batched_dev(ctx: AttnContext, caches, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, scale: float,
+                        stream: int = 0, flags: int = 0):
+    """One decode token for every cache in ``caches`` (lock step), one launch set."""
+    arr = (C.c_void_p * len(caches))(*[c.h for c in caches])
+    check(ctx.L.shainet_attn_forward_batched_dev(ctx.h, arr, len(caches), q_ptr, k_ptr, v_ptr, out_ptr, scale, flags,
+                                                 stream or None))

@@ -1,0 +1,790 @@
+// Host side of libshainet_attn: contexts, KV caches, kernel selection and the
+// C ABI declared in include/shainet_attn.h.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/shainet_attn.h"
+#include "kernels.h"
+
+using namespace shainet;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+    const int code = (e == cudaErrorMemoryAllocation) ? SHAINET_ATTN_E_NOMEM : SHAINET_ATTN_E_CUDA;
+    cudaGetLastError();  // clear the sticky-free error state
+    return fail(code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define CU(call)                                              \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
+    } while (0)
+
+constexpr int SEQ_RING = 8;           // in-flight descriptor uploads of batched decode
+constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
+constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
+
+struct DevBuf {
+    float* p = nullptr;
+    size_t cap = 0;  // floats
+};
+
+}  // namespace
+
+struct shainet_attn_ctx {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    DevBuf q_rot, part, dev_in, dev_out;
+    float* pin_in = nullptr;
+    size_t pin_in_cap = 0;
+    float* pin_out = nullptr;
+    size_t pin_out_cap = 0;
+    AttnStatus* status_host = nullptr;  // mapped pinned; kernels write through status_dev
+    AttnStatus* status_dev = nullptr;
+    SeqDesc* seq_host = nullptr;        // [SEQ_RING][seq_cap] pinned
+    SeqDesc* seq_dev = nullptr;         // [SEQ_RING][seq_cap]
+    int seq_cap = 0;
+    int seq_slot = 0;
+    cudaEvent_t seq_ev[SEQ_RING] = {};
+    int live_caches = 0;
+    bool timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool;  // reusable pairs
+};
+
+struct shainet_attn_kv {
+    shainet_attn_ctx* ctx = nullptr;
+    HeadShape hs{};
+    float* k = nullptr;
+    float* v = nullptr;
+    int cap = 0;
+    int len = 0;
+    float* inv_freq = nullptr;  // device, head_dim/2
+    float* q_norm = nullptr;    // device, nullable
+    float* k_norm = nullptr;
+    float* b_q = nullptr;
+    float* b_k = nullptr;
+    float* b_v = nullptr;
+    double eps = 1e-6;
+};
+
+namespace {
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+int grow(DevBuf& b, size_t floats, cudaStream_t s) {
+    if (b.cap >= floats && b.p) return SHAINET_ATTN_OK;
+    if (b.p) {
+        CU(cudaStreamSynchronize(s));
+        CU(cudaFree(b.p));
+        b.p = nullptr;
+        b.cap = 0;
+    }
+    size_t want = std::max(floats, b.cap * 2);
+    want = (want + 63) & ~(size_t)63;
+    CU(cudaMalloc(&b.p, want * sizeof(float)));
+    b.cap = want;
+    return SHAINET_ATTN_OK;
+}
+
+int grow_pinned(float*& p, size_t& cap, size_t floats) {
+    if (cap >= floats && p) return SHAINET_ATTN_OK;
+    if (p) CU(cudaFreeHost(p));
+    p = nullptr;
+    cap = 0;
+    size_t want = std::max(floats, (size_t)4096);
+    CU(cudaMallocHost(&p, want * sizeof(float)));
+    cap = want;
+    return SHAINET_ATTN_OK;
+}
+
+int upload_vec(float*& dst, const float* host, size_t n) {
+    if (!host) {
+        if (dst) CU(cudaFree(dst));
+        dst = nullptr;
+        return SHAINET_ATTN_OK;
+    }
+    if (!dst) CU(cudaMalloc(&dst, n * sizeof(float)));
+    CU(cudaMemcpy(dst, host, n * sizeof(float), cudaMemcpyHostToDevice));
+    return SHAINET_ATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Capacity policy of ensure_gpu_cache! (llama_block.cr:500): max(256, need, 2*old),
+// but the live rows move device-to-device instead of being re-uploaded.
+int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
+    if (kv->cap >= total_len && kv->k) return SHAINET_ATTN_OK;
+    const long long want = std::max<long long>(256, std::max<long long>(total_len, 2ll * kv->cap));
+    if (want > 0x7fffffffll) return fail(SHAINET_ATTN_E_INVALID, "cache capacity overflow");
+    const int new_cap = (int)want;
+    const size_t bytes = (size_t)kv->hs.num_kv_heads * new_cap * kv->hs.head_dim * sizeof(float);
+    float *nk = nullptr, *nv = nullptr;
+    cudaError_t e = cudaMalloc(&nk, bytes);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMalloc(k cache)");
+    e = cudaMalloc(&nv, bytes);
+    if (e != cudaSuccess) {
+        cudaFree(nk);
+        return fail_cuda(e, "cudaMalloc(v cache)");
+    }
+    if (kv->k && kv->len > 0) {
+        const size_t row_bytes = (size_t)kv->len * kv->hs.head_dim * sizeof(float);
+        const size_t src_pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
+        const size_t dst_pitch = (size_t)new_cap * kv->hs.head_dim * sizeof(float);
+        CU(cudaMemcpy2DAsync(nk, dst_pitch, kv->k, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s));
+        CU(cudaMemcpy2DAsync(nv, dst_pitch, kv->v, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s));
+    }
+    if (kv->k) {
+        CU(cudaStreamSynchronize(s));
+        CU(cudaFree(kv->k));
+        CU(cudaFree(kv->v));
+    }
+    kv->k = nk;
+    kv->v = nv;
+    kv->cap = new_cap;
+    return SHAINET_ATTN_OK;
+}
+
+int check_status(shainet_attn_ctx* ctx) {
+    if (ctx->status_host && ctx->status_host->code != DEV_OK) {
+        const int where = ctx->status_host->where;
+        ctx->status_host->code = DEV_OK;
+        ctx->status_host->where = 0;
+        return fail(SHAINET_ATTN_E_DEVICE_WAIT, "a kernel gave up on a bounded wait (site %d)", where);
+    }
+    return SHAINET_ATTN_OK;
+}
+
+enum class Kernel { Generic, SplitK };
+
+int pick_kernel(const HeadShape& hs, int T, unsigned flags, Kernel* out) {
+    const bool sk_ok = splitk_supported(hs);
+    if (flags & SHAINET_ATTN_F_TENSOR) return fail(SHAINET_ATTN_E_UNSUPPORTED, "tensor-core prefill kernel not available for this shape");
+    if (flags & SHAINET_ATTN_F_SPLITK) {
+        if (!sk_ok) return fail(SHAINET_ATTN_E_UNSUPPORTED, "split-K decode needs head_dim 64/128 and group size 1/2/4/8/16");
+        *out = Kernel::SplitK;
+        return SHAINET_ATTN_OK;
+    }
+    if (flags & SHAINET_ATTN_F_GENERIC) {
+        *out = Kernel::Generic;
+        return SHAINET_ATTN_OK;
+    }
+    *out = (sk_ok && T <= SPLITK_MAX_T) ? Kernel::SplitK : Kernel::Generic;
+    return SHAINET_ATTN_OK;
+}
+
+// Rows of cache per split so that about one CTA lands on every SM.
+void plan_splits(int sm_count, const HeadShape& hs, int rows, long long total_visible, int max_visible,
+                 int waves, int* chunk_rows, int* max_splits) {
+    const int tw = splitk_tile_rows(hs);
+    const long long ctas = std::max<long long>(1, (long long)sm_count * waves);
+    long long chunk = (total_visible * hs.num_kv_heads + ctas - 1) / ctas;
+    const long long min_chunk = 8ll * tw;  // one tile per consumer warp
+    chunk = std::max(chunk, min_chunk);
+    chunk = (chunk + tw - 1) / tw * tw;
+    if (chunk > 0x3fffffff) chunk = 0x3fffffff / tw * tw;
+    *chunk_rows = (int)chunk;
+    *max_splits = (int)((max_visible + chunk - 1) / chunk);
+    (void)rows;
+}
+
+int run_attention_untimed(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seqs, int batch, int T,
+                          long long total_visible, int max_visible, const float* q_rot, float* out, float scale,
+                          unsigned flags, cudaStream_t s);
+
+int run_attention(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seqs, int batch, int T, long long total_visible,
+                  int max_visible, const float* q_rot, float* out, float scale, unsigned flags, cudaStream_t s) {
+    if (!ctx->timing)
+        return run_attention_untimed(ctx, hs, seqs, batch, T, total_visible, max_visible, q_rot, out, scale, flags, s);
+    std::pair<cudaEvent_t, cudaEvent_t> ev;
+    if (!ctx->ev_pool.empty()) {
+        ev = ctx->ev_pool.back();
+        ctx->ev_pool.pop_back();
+    } else {
+        CU(cudaEventCreate(&ev.first));
+        CU(cudaEventCreate(&ev.second));
+    }
+    CU(cudaEventRecord(ev.first, s));
+    int rc = run_attention_untimed(ctx, hs, seqs, batch, T, total_visible, max_visible, q_rot, out, scale, flags, s);
+    CU(cudaEventRecord(ev.second, s));
+    ctx->timed.push_back(ev);
+    return rc;
+}
+
+int run_attention_untimed(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seqs, int batch, int T,
+                          long long total_visible, int max_visible, const float* q_rot, float* out, float scale,
+                          unsigned flags, cudaStream_t s) {
+    Kernel kern;
+    int rc = pick_kernel(hs, T, flags, &kern);
+    if (rc) return rc;
+    AttnArgs a{};
+    a.q_rot = q_rot;
+    a.out = out;
+    a.seqs = seqs;
+    a.batch = batch;
+    a.T = T;
+    a.hs = hs;
+    a.scale = scale;
+    a.status = ctx->status_dev;
+    if (kern == Kernel::Generic) {
+        if (hs.head_dim > 256) return fail(SHAINET_ATTN_E_UNSUPPORTED, "head_dim %d > 256", hs.head_dim);
+        CU(launch_attn_generic(a, s));
+        return SHAINET_ATTN_OK;
+    }
+    const int rows = batch * T;
+    plan_splits(ctx->sm_count, hs, rows, total_visible, max_visible, batch > 1 ? 8 : 1, &a.chunk_rows, &a.max_splits);
+    if (a.max_splits > 1) {
+        const size_t need = splitk_scratch_floats(hs, rows, a.max_splits);
+        rc = grow(ctx->part, need, s);
+        if (rc) return rc;
+        a.part_o = ctx->part.p;
+        a.part_ml = ctx->part.p + (size_t)rows * hs.num_heads * a.max_splits * hs.head_dim;
+    }
+    CU(launch_attn_splitk(a, s));
+    return SHAINET_ATTN_OK;
+}
+
+int validate_forward(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const void* q, const void* k, const void* v,
+                     const void* out, int new_tokens) {
+    if (!ctx || !kv) return fail(SHAINET_ATTN_E_INVALID, "null context or cache");
+    if (kv->ctx != ctx) return fail(SHAINET_ATTN_E_INVALID, "cache belongs to another context");
+    if (new_tokens < 0) return fail(SHAINET_ATTN_E_INVALID, "new_tokens %d < 0", new_tokens);
+    if (new_tokens > 0 && (!q || !k || !v || !out)) return fail(SHAINET_ATTN_E_INVALID, "null tensor pointer");
+    if ((long long)kv->len + new_tokens > 0x7fffffffll) return fail(SHAINET_ATTN_E_INVALID, "cache length overflow");
+    return SHAINET_ATTN_OK;
+}
+
+int forward_device(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new, const float* v_new,
+                   float* out, int T, float scale, unsigned flags, cudaStream_t s) {
+    const HeadShape hs = kv->hs;
+    int rc = kv_ensure(kv, kv->len + T, s);
+    if (rc) return rc;
+    rc = grow(ctx->q_rot, (size_t)T * hs.num_heads * hs.head_dim, s);
+    if (rc) return rc;
+    SeqRef seqs{};
+    seqs.one = SeqDesc{kv->k, kv->v, kv->len, kv->cap};
+    seqs.many = nullptr;
+    PrepArgs p{};
+    p.q = q;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.b_q = kv->b_q;
+    p.b_k = kv->b_k;
+    p.b_v = kv->b_v;
+    p.q_norm = kv->q_norm;
+    p.k_norm = kv->k_norm;
+    p.inv_freq = kv->inv_freq;
+    p.eps = kv->eps;
+    p.q_rot = ctx->q_rot.p;
+    p.seqs = seqs;
+    p.batch = 1;
+    p.T = T;
+    p.hs = hs;
+    CU(launch_prep_append(p, s));
+    const long long total_visible = (long long)T * kv->len + (long long)T * (T + 1) / 2;
+    rc = run_attention(ctx, hs, seqs, 1, T, total_visible, kv->len + T, ctx->q_rot.p, out, scale, flags, s);
+    if (rc) return rc;
+    kv->len += T;
+    return SHAINET_ATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int shainet_attn_version(void) { return SHAINET_ATTN_VERSION; }
+
+int shainet_attn_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+const char* shainet_attn_last_error(void) { return g_last_error.c_str(); }
+
+int shainet_attn_ctx_create(shainet_attn_ctx** out, int device) {
+    if (!out) return fail(SHAINET_ATTN_E_INVALID, "null out pointer");
+    *out = nullptr;
+    int n = shainet_attn_device_count();
+    if (n <= 0) return fail(SHAINET_ATTN_E_CUDA, "no CUDA device (this library has no CPU path)");
+    if (device < 0 || device >= n) return fail(SHAINET_ATTN_E_INVALID, "device %d out of range [0,%d)", device, n);
+    DeviceGuard g(device);
+    if (!g.ok) return fail(SHAINET_ATTN_E_CUDA, "cudaSetDevice(%d) failed", device);
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(SHAINET_ATTN_E_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    shainet_attn_ctx* c = new (std::nothrow) shainet_attn_ctx();
+    if (!c) return fail(SHAINET_ATTN_E_NOMEM, "out of host memory");
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaHostAlloc(&c->status_host, sizeof(AttnStatus), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        c->status_host->code = DEV_OK;
+        c->status_host->where = 0;
+        e = cudaHostGetDevicePointer(&c->status_dev, c->status_host, 0);
+    }
+    for (int i = 0; i < SEQ_RING && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&c->seq_ev[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        shainet_attn_ctx_destroy(c);
+        return fail_cuda(e, "context setup");
+    }
+    *out = c;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
+    if (!c) return SHAINET_ATTN_OK;
+    if (c->live_caches != 0) return fail(SHAINET_ATTN_E_STATE, "%d caches still alive", c->live_caches);
+    DeviceGuard g(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    for (DevBuf* b : {&c->q_rot, &c->part, &c->dev_in, &c->dev_out})
+        if (b->p) cudaFree(b->p);
+    if (c->pin_in) cudaFreeHost(c->pin_in);
+    if (c->pin_out) cudaFreeHost(c->pin_out);
+    if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->seq_host) cudaFreeHost(c->seq_host);
+    if (c->seq_dev) cudaFree(c->seq_dev);
+    for (int i = 0; i < SEQ_RING; ++i)
+        if (c->seq_ev[i]) cudaEventDestroy(c->seq_ev[i]);
+    for (auto* v : {&c->timed, &c->ev_pool})
+        for (auto& ev : *v) {
+            cudaEventDestroy(ev.first);
+            cudaEventDestroy(ev.second);
+        }
+    if (c->stream) cudaStreamDestroy(c->stream);
+    cudaGetLastError();
+    delete c;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_ctx_sync(shainet_attn_ctx* c) {
+    if (!c) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    DeviceGuard g(c->device);
+    CU(cudaStreamSynchronize(c->stream));
+    return check_status(c);
+}
+
+int shainet_attn_ctx_timing_enable(shainet_attn_ctx* c, int enable) {
+    if (!c) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    c->timing = enable != 0;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_ctx_timing_read(shainet_attn_ctx* c, double* total_ms, int* launches) {
+    if (!c || !total_ms || !launches) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    DeviceGuard g(c->device);
+    double sum = 0.0;
+    for (auto& ev : c->timed) {
+        CU(cudaEventSynchronize(ev.second));
+        float ms = 0.0f;
+        CU(cudaEventElapsedTime(&ms, ev.first, ev.second));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = (int)c->timed.size();
+    c->ev_pool.insert(c->ev_pool.end(), c->timed.begin(), c->timed.end());
+    c->timed.clear();
+    return SHAINET_ATTN_OK;
+}
+
+size_t shainet_attn_ctx_scratch_bytes(shainet_attn_ctx* c) {
+    if (!c) return 0;
+    return (c->q_rot.cap + c->part.cap + c->dev_in.cap + c->dev_out.cap) * sizeof(float);
+}
+
+int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                           int head_dim, int initial_capacity) {
+    if (!ctx || !out) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    *out = nullptr;
+    // LlamaBlock.new's checks (llama_block.cr:80-89)
+    if (num_kv_heads <= 0 || num_heads <= 0 || num_heads % num_kv_heads != 0)
+        return fail(SHAINET_ATTN_E_INVALID, "num_heads must be divisible by num_kv_heads");
+    if (head_dim <= 0) return fail(SHAINET_ATTN_E_INVALID, "head_dim must be positive");
+    if (head_dim % 2 != 0) return fail(SHAINET_ATTN_E_UNSUPPORTED, "odd head_dim %d", head_dim);
+    if (head_dim > 256) return fail(SHAINET_ATTN_E_UNSUPPORTED, "head_dim %d > 256", head_dim);
+    if (initial_capacity < 0) return fail(SHAINET_ATTN_E_INVALID, "negative capacity");
+    DeviceGuard g(ctx->device);
+    shainet_attn_kv* kv = new (std::nothrow) shainet_attn_kv();
+    if (!kv) return fail(SHAINET_ATTN_E_NOMEM, "out of host memory");
+    kv->ctx = ctx;
+    kv->hs = HeadShape{num_heads, num_kv_heads, head_dim};
+    ctx->live_caches++;
+    int rc = shainet_attn_kv_set_rope_theta(kv, 10000.0);
+    if (rc == SHAINET_ATTN_OK && initial_capacity > 0) rc = kv_ensure(kv, initial_capacity, ctx->stream);
+    if (rc != SHAINET_ATTN_OK) {
+        std::string keep = g_last_error;
+        shainet_attn_kv_destroy(kv);
+        g_last_error = keep;
+        return rc;
+    }
+    *out = kv;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_destroy(shainet_attn_kv* kv) {
+    if (!kv) return SHAINET_ATTN_OK;
+    DeviceGuard g(kv->ctx->device);
+    cudaStreamSynchronize(kv->ctx->stream);
+    for (float* p : {kv->k, kv->v, kv->inv_freq, kv->q_norm, kv->k_norm, kv->b_q, kv->b_k, kv->b_v})
+        if (p) cudaFree(p);
+    cudaGetLastError();
+    kv->ctx->live_caches--;
+    delete kv;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_reset(shainet_attn_kv* kv) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    kv->len = 0;  // buffers stay; stale rows are rewritten before they become visible
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_truncate(shainet_attn_kv* kv, int len) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    if (len < 0 || len > kv->len) return fail(SHAINET_ATTN_E_STATE, "truncate to %d of a cache of %d", len, kv->len);
+    kv->len = len;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_len(const shainet_attn_kv* kv) { return kv ? kv->len : fail(SHAINET_ATTN_E_INVALID, "null cache"); }
+
+int shainet_attn_kv_capacity(const shainet_attn_kv* kv) {
+    return kv ? kv->cap : fail(SHAINET_ATTN_E_INVALID, "null cache");
+}
+
+int shainet_attn_kv_reserve(shainet_attn_kv* kv, int total_len) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    if (total_len < 0) return fail(SHAINET_ATTN_E_INVALID, "negative length");
+    DeviceGuard g(kv->ctx->device);
+    return kv_ensure(kv, total_len, kv->ctx->stream);
+}
+
+int shainet_attn_kv_set_rope_theta(shainet_attn_kv* kv, double theta) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    if (!(theta > 0.0)) return fail(SHAINET_ATTN_E_INVALID, "rope theta must be positive");
+    const int half = kv->hs.head_dim / 2;
+    std::vector<float> f(half);
+    for (int i = 0; i < half; ++i) f[i] = (float)(1.0 / pow(theta, 2.0 * (double)i / (double)kv->hs.head_dim));
+    return shainet_attn_kv_set_rope(kv, f.data(), half);
+}
+
+int shainet_attn_kv_set_rope(shainet_attn_kv* kv, const float* inv_freq_host, int half) {
+    if (!kv || !inv_freq_host) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (half != kv->hs.head_dim / 2) return fail(SHAINET_ATTN_E_INVALID, "rope table has %d entries, head_dim/2 is %d", half, kv->hs.head_dim / 2);
+    DeviceGuard g(kv->ctx->device);
+    CU(cudaStreamSynchronize(kv->ctx->stream));
+    return upload_vec(kv->inv_freq, inv_freq_host, (size_t)half);
+}
+
+int shainet_attn_kv_set_qk_norm(shainet_attn_kv* kv, const float* qw, const float* kw, double eps) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    DeviceGuard g(kv->ctx->device);
+    CU(cudaStreamSynchronize(kv->ctx->stream));
+    int rc = upload_vec(kv->q_norm, qw, (size_t)kv->hs.head_dim);
+    if (rc) return rc;
+    rc = upload_vec(kv->k_norm, kw, (size_t)kv->hs.head_dim);
+    if (rc) return rc;
+    kv->eps = eps;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_set_bias(shainet_attn_kv* kv, const float* bq, const float* bk, const float* bv) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    DeviceGuard g(kv->ctx->device);
+    CU(cudaStreamSynchronize(kv->ctx->stream));
+    const size_t qd = (size_t)kv->hs.num_heads * kv->hs.head_dim, kd = (size_t)kv->hs.num_kv_heads * kv->hs.head_dim;
+    int rc = upload_vec(kv->b_q, bq, qd);
+    if (rc) return rc;
+    rc = upload_vec(kv->b_k, bk, kd);
+    if (rc) return rc;
+    return upload_vec(kv->b_v, bv, kd);
+}
+
+int shainet_attn_kv_export(shainet_attn_kv* kv, float* k_host, float* v_host, int len) {
+    if (!kv || !k_host || !v_host) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (len < 0 || len > kv->len) return fail(SHAINET_ATTN_E_STATE, "export of %d rows from a cache of %d", len, kv->len);
+    if (len == 0) return SHAINET_ATTN_OK;
+    DeviceGuard g(kv->ctx->device);
+    CU(cudaStreamSynchronize(kv->ctx->stream));
+    const size_t row_bytes = (size_t)len * kv->hs.head_dim * sizeof(float);
+    const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
+    CU(cudaMemcpy2D(k_host, row_bytes, kv->k, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
+    CU(cudaMemcpy2D(v_host, row_bytes, kv->v, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_import(shainet_attn_kv* kv, const float* k_host, const float* v_host, int len) {
+    if (!kv || (len > 0 && (!k_host || !v_host))) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (len < 0) return fail(SHAINET_ATTN_E_INVALID, "negative length");
+    DeviceGuard g(kv->ctx->device);
+    kv->len = 0;
+    int rc = kv_ensure(kv, len, kv->ctx->stream);
+    if (rc) return rc;
+    if (len > 0) {
+        CU(cudaStreamSynchronize(kv->ctx->stream));
+        const size_t row_bytes = (size_t)len * kv->hs.head_dim * sizeof(float);
+        const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
+        CU(cudaMemcpy2D(kv->k, pitch, k_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
+        CU(cudaMemcpy2D(kv->v, pitch, v_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
+    }
+    kv->len = len;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_fill_normal(shainet_attn_kv* kv, int len, uint64_t seed) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    if (len < 0) return fail(SHAINET_ATTN_E_INVALID, "negative length");
+    DeviceGuard g(kv->ctx->device);
+    kv->len = 0;
+    int rc = kv_ensure(kv, len, kv->ctx->stream);
+    if (rc) return rc;
+    CU(launch_fill_normal(kv->k, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed, kv->ctx->stream));
+    CU(launch_fill_normal(kv->v, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed + 1, kv->ctx->stream));
+    CU(cudaStreamSynchronize(kv->ctx->stream));
+    kv->len = len;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_kv_device_ptrs(shainet_attn_kv* kv, float** k_dev, float** v_dev) {
+    if (!kv || !k_dev || !v_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    *k_dev = kv->k;
+    *v_dev = kv->v;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_forward_host(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                              const float* v_new, float* out, int T, float scale, unsigned flags) {
+    int rc = validate_forward(ctx, kv, q, k_new, v_new, out, T);
+    if (rc) return rc;
+    if (T == 0) return SHAINET_ATTN_OK;
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = ctx->stream;
+    const size_t qn = (size_t)T * kv->hs.num_heads * kv->hs.head_dim;
+    const size_t kn = (size_t)T * kv->hs.num_kv_heads * kv->hs.head_dim;
+    const size_t in_n = qn + 2 * kn;
+    rc = grow(ctx->dev_in, in_n, s);
+    if (rc) return rc;
+    rc = grow(ctx->dev_out, qn, s);
+    if (rc) return rc;
+    float* dq = ctx->dev_in.p;
+    float* dk = dq + qn;
+    float* dv = dk + kn;
+    const bool small = in_n * sizeof(float) <= SMALL_COPY;
+    if (small) {
+        // One pinned blob, one H2D: q | k | v.
+        rc = grow_pinned(ctx->pin_in, ctx->pin_in_cap, in_n);
+        if (rc) return rc;
+        rc = grow_pinned(ctx->pin_out, ctx->pin_out_cap, qn);
+        if (rc) return rc;
+        memcpy(ctx->pin_in, q, qn * sizeof(float));
+        memcpy(ctx->pin_in + qn, k_new, kn * sizeof(float));
+        memcpy(ctx->pin_in + qn + kn, v_new, kn * sizeof(float));
+        CU(cudaMemcpyAsync(dq, ctx->pin_in, in_n * sizeof(float), cudaMemcpyHostToDevice, s));
+    } else {
+        CU(cudaMemcpyAsync(dq, q, qn * sizeof(float), cudaMemcpyHostToDevice, s));
+        CU(cudaMemcpyAsync(dk, k_new, kn * sizeof(float), cudaMemcpyHostToDevice, s));
+        CU(cudaMemcpyAsync(dv, v_new, kn * sizeof(float), cudaMemcpyHostToDevice, s));
+    }
+    rc = forward_device(ctx, kv, dq, dk, dv, ctx->dev_out.p, T, scale, flags, s);
+    if (rc) return rc;
+    if (small) {
+        CU(cudaMemcpyAsync(ctx->pin_out, ctx->dev_out.p, qn * sizeof(float), cudaMemcpyDeviceToHost, s));
+        CU(cudaStreamSynchronize(s));
+        memcpy(out, ctx->pin_out, qn * sizeof(float));
+    } else {
+        CU(cudaMemcpyAsync(out, ctx->dev_out.p, qn * sizeof(float), cudaMemcpyDeviceToHost, s));
+        CU(cudaStreamSynchronize(s));
+    }
+    return check_status(ctx);
+}
+
+int shainet_attn_forward_dev(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                             const float* v_new, float* out, int T, float scale, unsigned flags, void* stream) {
+    int rc = validate_forward(ctx, kv, q, k_new, v_new, out, T);
+    if (rc) return rc;
+    if (T == 0) return SHAINET_ATTN_OK;
+    if (!aligned16(q) || !aligned16(k_new) || !aligned16(v_new) || !aligned16(out))
+        return fail(SHAINET_ATTN_E_INVALID, "device pointers must be 16-byte aligned");
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    return forward_device(ctx, kv, q, k_new, v_new, out, T, scale, flags, s);
+}
+
+int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* const* kvs, int batch, const float* q,
+                                     const float* k_new, const float* v_new, float* out, float scale, unsigned flags,
+                                     void* stream) {
+    if (!ctx || !kvs) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (batch < 0) return fail(SHAINET_ATTN_E_INVALID, "negative batch");
+    if (batch == 0) return SHAINET_ATTN_OK;
+    if (!q || !k_new || !v_new || !out) return fail(SHAINET_ATTN_E_INVALID, "null tensor pointer");
+    if (!aligned16(q) || !aligned16(k_new) || !aligned16(v_new) || !aligned16(out))
+        return fail(SHAINET_ATTN_E_INVALID, "device pointers must be 16-byte aligned");
+    if (batch > 65535) return fail(SHAINET_ATTN_E_UNSUPPORTED, "batch %d > 65535", batch);
+    const shainet_attn_kv* first = kvs[0];
+    if (!first) return fail(SHAINET_ATTN_E_INVALID, "null cache in batch");
+    for (int b = 0; b < batch; ++b) {
+        const shainet_attn_kv* kv = kvs[b];
+        if (!kv || kv->ctx != ctx) return fail(SHAINET_ATTN_E_INVALID, "cache %d is null or of another context", b);
+        if (kv->hs.num_heads != first->hs.num_heads || kv->hs.num_kv_heads != first->hs.num_kv_heads ||
+            kv->hs.head_dim != first->hs.head_dim)
+            return fail(SHAINET_ATTN_E_INVALID, "cache %d has a different head shape", b);
+        for (int c = 0; c < b; ++c)
+            if (kvs[c] == kv) return fail(SHAINET_ATTN_E_INVALID, "cache %d appears twice in the batch", b);
+        if (kv->len == 0x7fffffff) return fail(SHAINET_ATTN_E_INVALID, "cache length overflow");
+    }
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    const HeadShape hs = first->hs;
+    int rc;
+    for (int b = 0; b < batch; ++b) {
+        rc = kv_ensure(kvs[b], kvs[b]->len + 1, s);
+        if (rc) return rc;
+    }
+    if (ctx->seq_cap < batch) {
+        CU(cudaStreamSynchronize(s));
+        for (int i = 0; i < SEQ_RING; ++i) CU(cudaEventSynchronize(ctx->seq_ev[i]));
+        if (ctx->seq_host) CU(cudaFreeHost(ctx->seq_host));
+        if (ctx->seq_dev) CU(cudaFree(ctx->seq_dev));
+        ctx->seq_host = nullptr;
+        ctx->seq_dev = nullptr;
+        ctx->seq_cap = 0;
+        const int cap = std::max(batch, 64);
+        CU(cudaMallocHost(&ctx->seq_host, sizeof(SeqDesc) * cap * SEQ_RING));
+        CU(cudaMalloc(&ctx->seq_dev, sizeof(SeqDesc) * cap * SEQ_RING));
+        ctx->seq_cap = cap;
+    }
+    const int slot = ctx->seq_slot;
+    ctx->seq_slot = (slot + 1) % SEQ_RING;
+    CU(cudaEventSynchronize(ctx->seq_ev[slot]));  // the upload that last used this slot has run
+    SeqDesc* hd = ctx->seq_host + (size_t)slot * ctx->seq_cap;
+    SeqDesc* dd = ctx->seq_dev + (size_t)slot * ctx->seq_cap;
+    long long total_visible = 0;
+    int max_visible = 0;
+    for (int b = 0; b < batch; ++b) {
+        hd[b] = SeqDesc{kvs[b]->k, kvs[b]->v, kvs[b]->len, kvs[b]->cap};
+        total_visible += kvs[b]->len + 1;
+        max_visible = std::max(max_visible, kvs[b]->len + 1);
+    }
+    CU(cudaMemcpyAsync(dd, hd, sizeof(SeqDesc) * batch, cudaMemcpyHostToDevice, s));
+    CU(cudaEventRecord(ctx->seq_ev[slot], s));
+    rc = grow(ctx->q_rot, (size_t)batch * hs.num_heads * hs.head_dim, s);
+    if (rc) return rc;
+    SeqRef seqs{};
+    seqs.many = dd;
+    PrepArgs p{};
+    p.q = q;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.b_q = first->b_q;
+    p.b_k = first->b_k;
+    p.b_v = first->b_v;
+    p.q_norm = first->q_norm;
+    p.k_norm = first->k_norm;
+    p.inv_freq = first->inv_freq;
+    p.eps = first->eps;
+    p.q_rot = ctx->q_rot.p;
+    p.seqs = seqs;
+    p.batch = batch;
+    p.T = 1;
+    p.hs = hs;
+    CU(launch_prep_append(p, s));
+    rc = run_attention(ctx, hs, seqs, batch, 1, total_visible, max_visible, ctx->q_rot.p, out, scale, flags, s);
+    if (rc) return rc;
+    for (int b = 0; b < batch; ++b) kvs[b]->len += 1;
+    return SHAINET_ATTN_OK;
+}
+
+// ---- reference-signature entry points (legacy default stream) ----
+
+void kv_cache_append_f32(const float* staging, float* kc, float* vc, int new_tokens, int start_pos,
+                         int num_kv_heads, int head_dim, int capacity) {
+    cudaError_t e = launch_ref_append(staging, kc, vc, new_tokens, start_pos, num_kv_heads, head_dim, capacity, 0);
+    if (e != cudaSuccess) printf("CUDA Error in kv_cache_append_f32: %s\n", cudaGetErrorString(e));
+}
+
+void attention_kv_f32(const float* q, const float* kc, const float* vc, float* out, float* ws, int new_tokens,
+                      int start_pos, int num_heads, int heads_per_kv, int head_dim, int capacity, float scale) {
+    if (new_tokens <= 0 || num_heads <= 0 || heads_per_kv <= 0 || num_heads % heads_per_kv != 0) return;
+    AttnArgs a{};
+    a.q_rot = q;
+    a.out = out;
+    a.seqs.one = SeqDesc{const_cast<float*>(kc), const_cast<float*>(vc), start_pos, capacity};
+    a.seqs.many = nullptr;
+    a.batch = 1;
+    a.T = new_tokens;
+    a.hs = HeadShape{num_heads, num_heads / heads_per_kv, head_dim};
+    a.scale = scale;
+    a.status = nullptr;
+    cudaError_t e = cudaSuccess;
+    const int total_len = start_pos + new_tokens;
+    bool done = false;
+    if (splitk_supported(a.hs) && new_tokens <= SPLITK_MAX_T && aligned16(q) && aligned16(kc) && aligned16(vc) && aligned16(out)) {
+        int sm = 148, dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+        const long long tv = (long long)new_tokens * start_pos + (long long)new_tokens * (new_tokens + 1) / 2;
+        plan_splits(sm, a.hs, new_tokens, tv, total_len, 1, &a.chunk_rows, &a.max_splits);
+        // The caller's scratch holds num_heads*new_tokens*total_len floats; use it
+        // for the split partials when they fit, otherwise take fewer splits.
+        const long long ws_floats = (long long)num_heads * new_tokens * total_len;
+        while (a.max_splits > 1 && (long long)splitk_scratch_floats(a.hs, new_tokens, a.max_splits) > ws_floats) {
+            a.chunk_rows *= 2;
+            a.max_splits = (total_len + a.chunk_rows - 1) / a.chunk_rows;
+        }
+        if (a.max_splits == 1 || (ws && aligned16(ws))) {
+            a.part_o = ws;
+            a.part_ml = ws + (size_t)new_tokens * num_heads * a.max_splits * head_dim;
+            e = launch_attn_splitk(a, 0);
+            done = true;
+        }
+    }
+    if (!done) {
+        if (head_dim > 256 || head_dim <= 0) {
+            printf("CUDA Error in attention_kv_f32: head_dim %d not supported\n", head_dim);
+            return;
+        }
+        e = launch_attn_generic(a, 0);
+    }
+    if (e != cudaSuccess) printf("CUDA Error in attention_kv_f32: %s\n", cudaGetErrorString(e));
+}
+
+}  // extern "C"

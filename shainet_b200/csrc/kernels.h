@@ -1,0 +1,85 @@
+// Internal launch interfaces of libshainet_attn's kernels (host side).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include "common.cuh"
+
+namespace shainet {
+
+// One sequence's device KV cache, [num_kv_heads, capacity, head_dim] fp32 per
+// tensor, and the number of positions held BEFORE the rows of this call.
+struct SeqDesc {
+    float* k;
+    float* v;
+    int start;
+    int capacity;
+};
+
+// A launch covers `batch` sequences of `T` new tokens each (rows = batch*T).
+// batch == 1 passes its descriptor by value in `one`; batched decode passes a
+// device array in `many` (T == 1).
+struct SeqRef {
+    SeqDesc one;
+    const SeqDesc* many;
+};
+
+struct HeadShape {
+    int num_heads;
+    int num_kv_heads;
+    int head_dim;
+};
+
+struct PrepArgs {
+    const float* q;        // [rows, num_heads*head_dim]
+    const float* k_new;    // [rows, num_kv_heads*head_dim]
+    const float* v_new;
+    const float* b_q;      // nullable biases (Qwen2)
+    const float* b_k;
+    const float* b_v;
+    const float* q_norm;   // nullable per-head RMSNorm weights (Qwen3), [head_dim]
+    const float* k_norm;
+    const float* inv_freq; // [head_dim/2]
+    double eps;
+    float* q_rot;          // [rows, num_heads*head_dim]
+    SeqRef seqs;
+    int batch, T;
+    HeadShape hs;
+};
+
+struct AttnArgs {
+    const float* q_rot;    // rotated queries [rows, num_heads*head_dim]
+    float* out;            // [rows, num_heads*head_dim]
+    SeqRef seqs;
+    int batch, T;
+    HeadShape hs;
+    float scale;
+    // split-K only
+    float* part_o;         // [rows, num_heads, max_splits, head_dim]
+    float* part_ml;        // [rows, num_heads, max_splits, 2]
+    int chunk_rows;        // cache rows per split (multiple of the warp tile)
+    int max_splits;        // grid.x
+    AttnStatus* status;
+};
+
+// Fused (bias +) per-head RMSNorm + RoPE for q and k, and the append of the
+// rotated k rows and raw v rows into the cache.
+cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s);
+
+// Any head_dim <= 256 (even), any group size, any T: one CTA per (head, row).
+cudaError_t launch_attn_generic(const AttnArgs& a, cudaStream_t s);
+
+// Split-K flash-decode for head_dim in {64,128} and group size in {1,2,4,8,16}.
+bool splitk_supported(const HeadShape& hs);
+int splitk_tile_rows(const HeadShape& hs);
+size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits);
+cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s);
+
+// Standard-normal fill of `len` positions per kv head (benchmark caches).
+cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
+                               unsigned long long seed, cudaStream_t s);
+
+// Drop-in bodies for the reference's two exported kernels.
+cudaError_t launch_ref_append(const float* staging, float* kc, float* vc, int new_tokens, int start_pos,
+                              int num_kv_heads, int head_dim, int capacity, cudaStream_t s);
+
+}  // namespace shainet

@@ -1,0 +1,203 @@
+// Fused (bias +) per-head RMSNorm + RoPE + KV-cache append.
+//
+// Replaces, in one launch, the host loops of the reference between the q/k/v
+// projections and the attention kernel:
+//   add_bias!            src/shainet/transformer/llama_block.cr:585-601
+//   apply_head_rmsnorm!  src/shainet/transformer/llama_block.cr:615-641
+//   K RoPE + append      src/shainet/transformer/llama_block.cr:266-286
+//   Q RoPE               src/shainet/transformer/llama_block.cr:440-467
+//   kv_cache_append_f32  src/shainet/native/cuda_kernels.cu:695-726
+//
+// Every arithmetic step uses the reference's order with explicitly rounded,
+// unfused fp32 operations (the Crystal build does not contract a*b+c), so the
+// cache contents differ from the host path only by the ulp-level difference
+// between the device's and libm's cosf/sinf.
+#include "kernels.h"
+
+namespace shainet {
+
+namespace {
+
+constexpr int PREP_WARPS = 4;
+
+__global__ void __launch_bounds__(PREP_WARPS * 32) prep_append_kernel(PrepArgs a) {
+    extern __shared__ float prep_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int H = a.hs.num_heads, KV = a.hs.num_kv_heads, hd = a.hs.head_dim;
+    const int per_row = H + 2 * KV;
+    const long long item = (long long)blockIdx.x * PREP_WARPS + warp;
+    const long long rows = (long long)a.batch * a.T;
+    if (item >= rows * per_row) return;  // warp-uniform
+    const int r = (int)(item / per_row);
+    const int slot = (int)(item % per_row);
+    const int b = r / a.T, t = r % a.T;
+    const SeqDesc sd = a.seqs.many ? a.seqs.many[b] : a.seqs.one;
+    const int pos = sd.start + t;
+    const int half = hd >> 1;
+    float* row = prep_smem + warp * hd;
+
+    const float* src;
+    const float* bias;
+    const float* w;
+    float* dst;
+    bool is_v = false;
+    if (slot < H) {
+        src = a.q + (size_t)r * H * hd + (size_t)slot * hd;
+        bias = a.b_q ? a.b_q + (size_t)slot * hd : nullptr;
+        w = a.q_norm;
+        dst = a.q_rot + (size_t)r * H * hd + (size_t)slot * hd;
+    } else if (slot < H + KV) {
+        const int kh = slot - H;
+        src = a.k_new + (size_t)r * KV * hd + (size_t)kh * hd;
+        bias = a.b_k ? a.b_k + (size_t)kh * hd : nullptr;
+        w = a.k_norm;
+        dst = sd.k + ((size_t)kh * sd.capacity + pos) * hd;
+    } else {
+        const int kh = slot - H - KV;
+        src = a.v_new + (size_t)r * KV * hd + (size_t)kh * hd;
+        bias = a.b_v ? a.b_v + (size_t)kh * hd : nullptr;
+        w = nullptr;
+        dst = sd.v + ((size_t)kh * sd.capacity + pos) * hd;
+        is_v = true;
+    }
+
+    for (int d = lane; d < hd; d += 32) {
+        float x = src[d];
+        if (bias) x = __fadd_rn(x, bias[d]);
+        row[d] = x;
+    }
+    __syncwarp();
+    if (is_v) {
+        for (int d = lane; d < hd; d += 32) dst[d] = row[d];
+        return;
+    }
+
+    float inv = 1.0f;
+    if (w) {
+        if (lane == 0) {
+            // Sequential fp32 sum in ascending d, as the host loop does.
+            float ss = 0.0f;
+            for (int d = 0; d < hd; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
+            const float mean = __fdiv_rn(ss, (float)hd);
+            inv = (float)(1.0 / sqrt((double)mean + a.eps));
+        }
+        inv = __shfl_sync(0xffffffffu, inv, 0);
+    }
+    const float fpos = (float)pos;
+    for (int i = lane; i < half; i += 32) {
+        float x0 = row[i], x1 = row[i + half];
+        if (w) {
+            x0 = __fmul_rn(__fmul_rn(x0, inv), w[i]);
+            x1 = __fmul_rn(__fmul_rn(x1, inv), w[i + half]);
+        }
+        const float angle = __fmul_rn(fpos, a.inv_freq[i]);
+        float s, c;
+        sincosf(angle, &s, &c);
+        dst[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        dst[i + half] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+    }
+}
+
+// Scatter of already-rotated staging rows, the reference kernel's contract:
+// staging = K chunks [kv_head][t][d] followed by V chunks in the same layout.
+__global__ void ref_append_kernel(const float4* __restrict__ staging, float* __restrict__ kc, float* __restrict__ vc,
+                                  int new_tokens, int start_pos, int num_kv_heads, int hd4, int capacity) {
+    const long long chunk = (long long)new_tokens * hd4;
+    const long long total = (long long)num_kv_heads * chunk;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < 2 * total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const bool is_v = idx >= total;
+        const long long rr = is_v ? idx - total : idx;
+        const long long kv_h = rr / chunk;
+        const long long rem = rr - kv_h * chunk;
+        float4* base = reinterpret_cast<float4*>(is_v ? vc : kc);
+        base[(kv_h * capacity + start_pos) * hd4 + rem] = staging[idx];
+    }
+}
+
+__global__ void ref_append_scalar_kernel(const float* __restrict__ staging, float* __restrict__ kc,
+                                         float* __restrict__ vc, int new_tokens, int start_pos, int num_kv_heads,
+                                         int hd, int capacity) {
+    const long long chunk = (long long)new_tokens * hd;
+    const long long total = (long long)num_kv_heads * chunk;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < 2 * total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const bool is_v = idx >= total;
+        const long long rr = is_v ? idx - total : idx;
+        const long long kv_h = rr / chunk;
+        const long long rem = rr - kv_h * chunk;
+        (is_v ? vc : kc)[(kv_h * capacity + start_pos) * hd + rem] = staging[idx];
+    }
+}
+
+// Counter-based standard normal: SplitMix64 of (seed, index) -> Box-Muller.
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+__global__ void fill_normal_kernel(float* base, int num_kv_heads, int capacity, int hd, int len,
+                                   unsigned long long seed) {
+    const long long per_head = (long long)len * hd;
+    const long long pairs = ((long long)num_kv_heads * per_head + 1) / 2;
+    for (long long pidx = (long long)blockIdx.x * blockDim.x + threadIdx.x; pidx < pairs;
+         pidx += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long bits = splitmix64(seed * 0xD1342543DE82EF95ull + (unsigned long long)pidx);
+        const float u1 = ((float)(unsigned)(bits >> 40) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
+        const float u2 = (float)(unsigned)((bits >> 8) & 0xFFFFFFu) * (1.0f / 16777216.0f);
+        const float rad = sqrtf(-2.0f * logf(u1));
+        float s, c;
+        sincospif(2.0f * u2, &s, &c);
+        const float z[2] = {rad * c, rad * s};
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long e = 2 * pidx + k;
+            if (e < (long long)num_kv_heads * per_head) {
+                const long long h = e / per_head, rem = e - h * per_head;
+                base[h * (long long)capacity * hd + rem] = z[k];
+            }
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s) {
+    const long long items = (long long)a.batch * a.T * (a.hs.num_heads + 2 * a.hs.num_kv_heads);
+    if (items == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((items + PREP_WARPS - 1) / PREP_WARPS);
+    const size_t smem = (size_t)PREP_WARPS * a.hs.head_dim * sizeof(float);
+    prep_append_kernel<<<blocks, PREP_WARPS * 32, smem, s>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ref_append(const float* staging, float* kc, float* vc, int new_tokens, int start_pos,
+                              int num_kv_heads, int head_dim, int capacity, cudaStream_t s) {
+    const long long total = 2ll * num_kv_heads * new_tokens * head_dim;
+    if (total == 0) return cudaSuccess;
+    const bool vec = (head_dim % 4 == 0) && ((((uintptr_t)staging) | ((uintptr_t)kc) | ((uintptr_t)vc)) % 16 == 0);
+    const long long work = vec ? total / 4 : total;
+    long long blocks = (work + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (vec)
+        ref_append_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(staging), kc, vc, new_tokens,
+                                                          start_pos, num_kv_heads, head_dim / 4, capacity);
+    else
+        ref_append_scalar_kernel<<<(unsigned)blocks, 256, 0, s>>>(staging, kc, vc, new_tokens, start_pos, num_kv_heads,
+                                                                 head_dim, capacity);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
+                               unsigned long long seed, cudaStream_t s) {
+    const long long pairs = ((long long)num_kv_heads * len * head_dim + 1) / 2;
+    if (pairs == 0) return cudaSuccess;
+    long long blocks = (pairs + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    fill_normal_kernel<<<(unsigned)blocks, 256, 0, s>>>(base, num_kv_heads, capacity, head_dim, len, seed);
+    return cudaGetLastError();
+}
+
+}  // namespace shainet

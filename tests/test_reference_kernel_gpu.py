@@ -1,0 +1,102 @@
+"""The reference's own CUDA kernels (compiled unmodified into oracle/_ref) run on
+the GPU: they pin the CPU oracle to the reference's executable code, and the
+library's symbol-compatible kv_cache_append_f32 / attention_kv_f32 are checked
+against both."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from helpers import DECODE_TOL, L1B, Q30, SPEC_ABS_TOL, cosine, rel_err
+
+pytestmark = pytest.mark.gpu
+
+_SIG_APPEND = [C.c_void_p] * 3 + [C.c_int] * 5
+_SIG_ATTN = [C.c_void_p] * 5 + [C.c_int] * 6 + [C.c_float]
+
+
+def _ref_lib():
+    from oracle import build_oracle
+    path = build_oracle.build_reference_kernels()
+    if path is None or not os.path.exists(path):
+        pytest.skip("reference kernels were not built (reference tree absent at build time)")
+    lib = C.CDLL(path)
+    lib.kv_cache_append_f32.argtypes = _SIG_APPEND
+    lib.kv_cache_append_f32.restype = None
+    lib.attention_kv_f32.argtypes = _SIG_ATTN
+    lib.attention_kv_f32.restype = None
+    return lib
+
+
+def _drive(lib, shape, steps, rng, cap):
+    """Replays attention_heads_gpu's call sequence (llama_block.cr:407-479) with
+    torch tensors as the device buffers; K rows and q arrive already rotated."""
+    import torch
+    from oracle import oracle as O
+    H, KV, hd = shape["H"], shape["KV"], shape["hd"]
+    o = O.OracleAttention(H, KV, hd, shape["theta"])
+    dev = torch.device("cuda:0")
+    kc = torch.zeros(KV * cap * hd, device=dev)
+    vc = torch.zeros(KV * cap * hd, device=dev)
+    outs = []
+    start = 0
+    for T in steps:
+        q = rng.uniform(-1, 1, (T, H * hd)).astype(np.float32)
+        k = rng.uniform(-1, 1, (T, KV * hd)).astype(np.float32)
+        v = rng.uniform(-1, 1, (T, KV * hd)).astype(np.float32)
+        ref = o.attend_cached(q, k, v, threads=8)
+        ko, vo = o.export_cache()
+        # staging: K chunks [kv][t][d] then V chunks; q rotated on the host
+        stag = np.concatenate([ko[:, start:start + T].ravel(), vo[:, start:start + T].ravel()])
+        half = hd // 2
+        inv = o.inv_freq()
+        qr = q.reshape(T, H, hd).copy()
+        for t in range(T):
+            ang = (np.float32(start + t) * inv).astype(np.float32)
+            c, s = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+            x0, x1 = qr[t, :, :half].copy(), qr[t, :, half:].copy()
+            qr[t, :, :half] = x0 * c - x1 * s
+            qr[t, :, half:] = x1 * c + x0 * s
+        total = start + T
+        d_st = torch.from_numpy(stag).to(dev)
+        d_q = torch.from_numpy(qr.reshape(T, H * hd)).to(dev)
+        d_out = torch.zeros(T * H * hd, device=dev)
+        d_ws = torch.zeros(H * T * total, device=dev)
+        torch.cuda.synchronize()
+        lib.kv_cache_append_f32(d_st.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, start, KV, hd, cap)
+        lib.attention_kv_f32(d_q.data_ptr(), kc.data_ptr(), vc.data_ptr(), d_out.data_ptr(), d_ws.data_ptr(), T, start,
+                             H, H // KV, hd, cap, np.float32(1.0 / np.sqrt(float(hd))))
+        torch.cuda.synchronize()
+        outs.append((ref, d_out.cpu().numpy().reshape(T, H * hd)))
+        start = total
+    kcache = kc.cpu().numpy().reshape(KV, cap, hd)[:, :start]
+    return outs, kcache, o.export_cache()[0]
+
+
+SHAPES = [(dict(H=8, KV=4, hd=8, theta=10000.0), [6, 1, 1, 1], 256),      # spec/llama_attention_gpu_spec.cr:17-66
+          (dict(H=4, KV=2, hd=8, theta=10000.0), [290] + [1] * 4, 512),   # :68-104
+          (L1B, [300, 1, 1], 512),
+          (Q30, [1500, 1, 3], 2048)]
+
+
+@pytest.mark.parametrize("shape,steps,cap", SHAPES, ids=["spec_gqa", "spec_growth", "llama1b", "qwen3_30b"])
+def test_reference_cuda_kernel_agrees_with_oracle(shape, steps, cap):
+    lib = _ref_lib()
+    outs, kc, ko = _drive(lib, shape, steps, np.random.default_rng(42), cap)
+    assert np.array_equal(kc, ko)
+    for ref, got in outs:
+        assert np.abs(ref - got).max() < SPEC_ABS_TOL        # the reference's own bound
+        assert cosine(got, ref) > 0.9999
+        assert rel_err(got, ref) <= 5e-6                     # and what is actually observed
+
+
+@pytest.mark.parametrize("shape,steps,cap", SHAPES, ids=["spec_gqa", "spec_growth", "llama1b", "qwen3_30b"])
+def test_symbol_compatible_entry_points(shape, steps, cap):
+    from shainet_b200 import _lib, build
+    build.build()
+    lib = _lib.load()
+    outs, kc, ko = _drive(lib, shape, steps, np.random.default_rng(42), cap)
+    assert np.array_equal(kc, ko)
+    for ref, got in outs:
+        assert rel_err(got, ref) <= DECODE_TOL
