@@ -44,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     obj_dir = os.path.join(PKG, "build")
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    common = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+    common = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-diag-suppress", "177", "-Xcompiler", "-fPIC",
               "-I", INCLUDE]
     if verbose:
         common += ["-Xptxas", "-v"]

@@ -32,33 +32,50 @@ namespace {
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int SK_SMEM_BUDGET = 200 * 1024;  // dynamic shared memory per CTA (one CTA per SM)
 constexpr int SK_MAX_STAGES = 32;
 
+// Tile geometry.  R*G = 16 scores per half-warp per batch, so a batch is
+// BR = 2*16/G rows; a warp tile is a whole number of batches.  The ring has a
+// multiple of NW stages so that every stage is always consumed by the same
+// warp: an mbarrier phase wait is only meaningful for a waiter that saw the
+// previous phase, which a fixed stage->warp map guarantees.
 template <int HD, int G>
+struct SKDefault {
+    static constexpr int BR = 2 * (16 / G);
+    static constexpr int TW = BR > 8 ? BR : 8;                         // rows per warp tile
+    static constexpr int NW = (2 * TW * HD * 4 > 16 * 1024) ? 4 : 8;   // consumer warps
+    static constexpr int SMEM_KB = 200;                                // one CTA per SM
+    static constexpr int CTAS_PER_SM = 1;
+};
+
+template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
+          int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = true>
 struct SK {
-    static constexpr int NW = 8;                       // consumer warps
+    static constexpr int NW = NW_;                     // consumer warps
     static constexpr int CPL = HD / 64;                // 16-byte chunks per lane per K row
     static constexpr int R = 16 / G;                   // rows per half-warp per batch
     static constexpr int BR = 2 * R;                   // rows per batch
-    static constexpr int TW = BR > 8 ? BR : 8;         // rows per warp tile
+    static constexpr int TW = TW_;                     // rows per warp tile
     static constexpr int NB = TW / BR;                 // batches per tile
     static constexpr int TILE_FLOATS = TW * HD;        // per tensor
     static constexpr int STAGE_FLOATS = 2 * TILE_FLOATS;
     static constexpr int RPI = 128 / HD;               // V rows covered by one warp-wide 128-bit load
     static constexpr int WARP_SCRATCH = 32 + 16;       // p[BR*G = 32] + alpha[G <= 16]
     static constexpr int THREADS = (NW + 1) * 32;
+    static constexpr int CTAS_PER_SM = CTAS_;
+    static constexpr bool MATH = MATH_;
+    static constexpr int FIXED_BYTES = NW * WARP_SCRATCH * 4 + 2 * SK_MAX_STAGES * 8;
+    static constexpr int NS_RAW = (SMEM_KB_ * 1024 - FIXED_BYTES) / (STAGE_FLOATS * 4);
+    static constexpr int NS_CAP = NS_RAW > SK_MAX_STAGES ? SK_MAX_STAGES : NS_RAW;
+    static constexpr int NS = NS_CAP / NW * NW;        // ring stages, a multiple of NW
+    static constexpr int MERGE_FLOATS = NW * G * (HD + 2);
+    static constexpr size_t SMEM_BYTES = (size_t)NS * STAGE_FLOATS * 4 + FIXED_BYTES;
     static_assert(HD == 64 || HD == 128, "head_dim");
     static_assert(G == 1 || G == 2 || G == 4 || G == 8 || G == 16, "group size");
+    static_assert(TW % BR == 0, "a warp tile is a whole number of batches");
+    static_assert(NS >= NW, "ring shorter than the number of consumer warps");
+    static_assert(MERGE_FLOATS <= NS * STAGE_FLOATS, "merge area must fit in the ring");
 };
-
-template <int HD, int G>
-__host__ __device__ constexpr int sk_stages() {
-    using C = SK<HD, G>;
-    int fixed = C::NW * C::WARP_SCRATCH * 4 + 2 * SK_MAX_STAGES * 8 + 128;
-    int n = (SK_SMEM_BUDGET - fixed) / (C::STAGE_FLOATS * 4);
-    return n > SK_MAX_STAGES ? SK_MAX_STAGES : n;
-}
 
 // 16-lane reduce-scatter of 16 values: on return acc[0] of lane i (i = lane & 15)
 // holds the sum over the half-warp of the callers' acc[i].
@@ -79,10 +96,9 @@ __device__ __forceinline__ void reduce_scatter16(float (&acc)[16], int lane) {
     }
 }
 
-template <int HD, int G>
-__global__ void __launch_bounds__(SK<HD, G>::THREADS, 1) attn_splitk_kernel(AttnArgs a) {
-    using C = SK<HD, G>;
-    constexpr int NS = sk_stages<HD, G>();
+template <int HD, int G, class C>
+__global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_splitk_kernel(AttnArgs a) {
+    constexpr int NS = C::NS;
     extern __shared__ __align__(1024) unsigned char sk_smem_raw[];
     float* stages = reinterpret_cast<float*>(sk_smem_raw);
     float* warp_scratch = stages + (size_t)NS * C::STAGE_FLOATS;
@@ -160,7 +176,7 @@ __global__ void __launch_bounds__(SK<HD, G>::THREADS, 1) attn_splitk_kernel(Attn
             const int nrows = min(C::TW, (row1 - row0) - i * C::TW);
 
 #pragma unroll
-            for (int bb = 0; bb < C::NB; ++bb) {
+            for (int bb = 0; bb < (C::MATH ? C::NB : 0); ++bb) {
                 const int base = bb * C::BR;
                 if (base >= nrows) break;  // warp-uniform
                 // ---- scores: acc[rr*G + g] for the R rows of this half-warp ----
@@ -314,21 +330,22 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(AttnArgs a) {
     a.out[((size_t)r * a.hs.num_heads + h) * HD + d] = acc / L;
 }
 
-template <int HD, int G>
+template <int HD, int G, class C = SK<HD, G>>
 cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
-    using C = SK<HD, G>;
-    constexpr int NS = sk_stages<HD, G>();
-    const size_t smem = (size_t)NS * C::STAGE_FLOATS * 4 + C::NW * C::WARP_SCRATCH * 4 + 2 * NS * 8;
-    static bool configured = false;  // per process; every device shares the attribute request
+    const size_t smem = C::SMEM_BYTES;
+    static unsigned long long configured = 0;  // bit per device
     cudaError_t e;
-    if (!configured) {
-        e = cudaFuncSetAttribute(attn_splitk_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int dev = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 64 || !(configured >> dev & 1ull)) {
+        e = cudaFuncSetAttribute(attn_splitk_kernel<HD, G, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = true;
+        if (dev < 64) configured |= 1ull << dev;
     }
     const int rows = a.batch * a.T;
     dim3 grid(a.max_splits, a.hs.num_kv_heads, rows);
-    attn_splitk_kernel<HD, G><<<grid, C::THREADS, smem, s>>>(a);
+    attn_splitk_kernel<HD, G, C><<<grid, C::THREADS, smem, s>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (a.max_splits > 1) {

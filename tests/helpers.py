@@ -32,11 +32,12 @@ def make_pair(ctx, shape, rng, eps=1e-6, **extra):
     from oracle import oracle as O
     import shainet_b200 as S
     kw = dict(extra)
+    cap = kw.pop("initial_capacity", 0)
     if shape.get("qk_norm"):
         kw.setdefault("q_norm", norm_weights(rng, shape["hd"]))
         kw.setdefault("k_norm", norm_weights(rng, shape["hd"]))
     o = O.OracleAttention(shape["H"], shape["KV"], shape["hd"], shape["theta"], eps, **kw)
-    g = S.LlamaAttention(ctx, shape["H"], shape["KV"], shape["hd"], shape["theta"], eps, **kw)
+    g = S.LlamaAttention(ctx, shape["H"], shape["KV"], shape["hd"], shape["theta"], eps, initial_capacity=cap, **kw)
     return o, g
 
 
