@@ -36,6 +36,7 @@ extern "C" {
 #define SHAINET_ATTN_F_GENERIC 1u  /* force the shape-agnostic kernel */
 #define SHAINET_ATTN_F_SPLITK 2u   /* force the split-K decode kernel (error if unsupported) */
 #define SHAINET_ATTN_F_TENSOR 4u   /* force the tcgen05 prefill kernel (error if unsupported) */
+#define SHAINET_ATTN_F_UNFUSED 8u  /* decode as three launches (RoPE/append, split-K, merge) instead of one */
 
 typedef struct shainet_attn_ctx shainet_attn_ctx;
 typedef struct shainet_attn_kv shainet_attn_kv;

@@ -71,6 +71,9 @@ struct shainet_attn_ctx {
     int seq_slot = 0;
     cudaEvent_t seq_ev[SEQ_RING] = {};
     int live_caches = 0;
+    unsigned* tickets = nullptr;        // split-merge tickets of the fused decode kernel, zero between launches
+    size_t tickets_cap = 0;
+    bool last_fused = false;            // the newest launch on this context was a fused decode kernel
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool;  // reusable pairs
@@ -185,12 +188,28 @@ int check_status(shainet_attn_ctx* ctx) {
         const int where = ctx->status_host->where;
         ctx->status_host->code = DEV_OK;
         ctx->status_host->where = 0;
+        if (ctx->tickets) cudaMemset(ctx->tickets, 0, ctx->tickets_cap * sizeof(unsigned));  // an unwound kernel may leave counts
         return fail(SHAINET_ATTN_E_DEVICE_WAIT, "a kernel gave up on a bounded wait (site %d)", where);
     }
     return SHAINET_ATTN_OK;
 }
 
 enum class Kernel { Generic, SplitK };
+
+int ensure_tickets(shainet_attn_ctx* ctx, size_t n, cudaStream_t s) {
+    if (ctx->tickets_cap >= n && ctx->tickets) return SHAINET_ATTN_OK;
+    if (ctx->tickets) {
+        CU(cudaStreamSynchronize(s));
+        CU(cudaFree(ctx->tickets));
+        ctx->tickets = nullptr;
+        ctx->tickets_cap = 0;
+    }
+    const size_t want = std::max<size_t>(n, 256);
+    CU(cudaMalloc(&ctx->tickets, want * sizeof(unsigned)));
+    CU(cudaMemset(ctx->tickets, 0, want * sizeof(unsigned)));
+    ctx->tickets_cap = want;
+    return SHAINET_ATTN_OK;
+}
 
 int pick_kernel(const HeadShape& hs, int T, unsigned flags, Kernel* out) {
     const bool sk_ok = splitk_supported(hs);
@@ -212,9 +231,9 @@ int pick_kernel(const HeadShape& hs, int T, unsigned flags, Kernel* out) {
 void plan_splits(int sm_count, const HeadShape& hs, int rows, long long total_visible, int max_visible,
                  int waves, int* chunk_rows, int* max_splits) {
     const int tw = splitk_tile_rows(hs);
-    const long long ctas = std::max<long long>(1, (long long)sm_count * waves);
+    const long long ctas = std::max<long long>(1, (long long)sm_count * splitk_ctas_per_sm(hs) * waves);
     long long chunk = (total_visible * hs.num_kv_heads + ctas - 1) / ctas;
-    const long long min_chunk = 8ll * tw;  // one tile per consumer warp
+    const long long min_chunk = 4ll * tw;  // one tile per consumer warp
     chunk = std::max(chunk, min_chunk);
     chunk = (chunk + tw - 1) / tw * tw;
     if (chunk > 0x3fffffff) chunk = 0x3fffffff / tw * tw;
@@ -289,35 +308,99 @@ int validate_forward(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const void* q, 
     return SHAINET_ATTN_OK;
 }
 
+// One call = `batch` sequences x T new tokens: norm/RoPE/append + attention.
+// `par` supplies the shared head shape, RoPE table, norm weights and biases.
+int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int batch, int T, long long total_visible,
+             int max_visible, const float* q, const float* k_new, const float* v_new, float* out, float scale,
+             unsigned flags, cudaStream_t s) {
+    const HeadShape hs = par->hs;
+    const bool fused = T == 1 && splitk_supported(hs) &&
+                       !(flags & (SHAINET_ATTN_F_GENERIC | SHAINET_ATTN_F_UNFUSED | SHAINET_ATTN_F_TENSOR));
+    int rc;
+    if (!fused) {
+        ctx->last_fused = false;
+        rc = grow(ctx->q_rot, (size_t)batch * T * hs.num_heads * hs.head_dim, s);
+        if (rc) return rc;
+        PrepArgs p{};
+        p.q = q;
+        p.k_new = k_new;
+        p.v_new = v_new;
+        p.b_q = par->b_q;
+        p.b_k = par->b_k;
+        p.b_v = par->b_v;
+        p.q_norm = par->q_norm;
+        p.k_norm = par->k_norm;
+        p.inv_freq = par->inv_freq;
+        p.eps = par->eps;
+        p.q_rot = ctx->q_rot.p;
+        p.seqs = seqs;
+        p.batch = batch;
+        p.T = T;
+        p.hs = hs;
+        CU(launch_prep_append(p, s));
+        return run_attention(ctx, hs, seqs, batch, T, total_visible, max_visible, ctx->q_rot.p, out, scale, flags, s);
+    }
+    FusedArgs f{};
+    f.q = q;
+    f.k_new = k_new;
+    f.v_new = v_new;
+    f.b_q = par->b_q;
+    f.b_k = par->b_k;
+    f.b_v = par->b_v;
+    f.q_norm = par->q_norm;
+    f.k_norm = par->k_norm;
+    f.inv_freq = par->inv_freq;
+    f.eps = par->eps;
+    f.out = out;
+    f.seqs = seqs;
+    f.batch = batch;
+    f.hs = hs;
+    f.scale = scale;
+    f.status = ctx->status_dev;
+    plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits);
+    if (f.max_splits > 1) {
+        rc = grow(ctx->part, splitk_scratch_floats(hs, batch, f.max_splits), s);
+        if (rc) return rc;
+        f.part_o = ctx->part.p;
+        f.part_ml = ctx->part.p + (size_t)batch * hs.num_heads * f.max_splits * hs.head_dim;
+    }
+    rc = ensure_tickets(ctx, (size_t)batch * hs.num_kv_heads, s);
+    if (rc) return rc;
+    f.tickets = ctx->tickets;
+    // A fused kernel may start while the previous fused kernel still runs; that
+    // one can be appending the newest row of this very cache.
+    f.unsafe_tail = ctx->last_fused ? 1 : 0;
+    std::pair<cudaEvent_t, cudaEvent_t> ev{};
+    if (ctx->timing) {
+        if (!ctx->ev_pool.empty()) {
+            ev = ctx->ev_pool.back();
+            ctx->ev_pool.pop_back();
+        } else {
+            CU(cudaEventCreate(&ev.first));
+            CU(cudaEventCreate(&ev.second));
+        }
+        CU(cudaEventRecord(ev.first, s));
+    }
+    CU(launch_decode_fused(f, s));
+    if (ctx->timing) {
+        CU(cudaEventRecord(ev.second, s));
+        ctx->timed.push_back(ev);
+    }
+    ctx->last_fused = true;
+    return SHAINET_ATTN_OK;
+}
+
 int forward_device(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new, const float* v_new,
                    float* out, int T, float scale, unsigned flags, cudaStream_t s) {
-    const HeadShape hs = kv->hs;
+    const int cap_before = kv->cap;
     int rc = kv_ensure(kv, kv->len + T, s);
     if (rc) return rc;
-    rc = grow(ctx->q_rot, (size_t)T * hs.num_heads * hs.head_dim, s);
-    if (rc) return rc;
+    if (kv->cap != cap_before) ctx->last_fused = false;  // growth synchronised the stream
     SeqRef seqs{};
     seqs.one = SeqDesc{kv->k, kv->v, kv->len, kv->cap};
     seqs.many = nullptr;
-    PrepArgs p{};
-    p.q = q;
-    p.k_new = k_new;
-    p.v_new = v_new;
-    p.b_q = kv->b_q;
-    p.b_k = kv->b_k;
-    p.b_v = kv->b_v;
-    p.q_norm = kv->q_norm;
-    p.k_norm = kv->k_norm;
-    p.inv_freq = kv->inv_freq;
-    p.eps = kv->eps;
-    p.q_rot = ctx->q_rot.p;
-    p.seqs = seqs;
-    p.batch = 1;
-    p.T = T;
-    p.hs = hs;
-    CU(launch_prep_append(p, s));
     const long long total_visible = (long long)T * kv->len + (long long)T * (T + 1) / 2;
-    rc = run_attention(ctx, hs, seqs, 1, T, total_visible, kv->len + T, ctx->q_rot.p, out, scale, flags, s);
+    rc = run_step(ctx, kv, seqs, 1, T, total_visible, kv->len + T, q, k_new, v_new, out, scale, flags, s);
     if (rc) return rc;
     kv->len += T;
     return SHAINET_ATTN_OK;
@@ -383,6 +466,7 @@ int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->seq_host) cudaFreeHost(c->seq_host);
     if (c->seq_dev) cudaFree(c->seq_dev);
+    if (c->tickets) cudaFree(c->tickets);
     for (int i = 0; i < SEQ_RING; ++i)
         if (c->seq_ev[i]) cudaEventDestroy(c->seq_ev[i]);
     for (auto* v : {&c->timed, &c->ev_pool})
@@ -673,7 +757,6 @@ int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* con
     }
     DeviceGuard g(ctx->device);
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
-    const HeadShape hs = first->hs;
     int rc;
     for (int b = 0; b < batch; ++b) {
         rc = kv_ensure(kvs[b], kvs[b]->len + 1, s);
@@ -706,28 +789,9 @@ int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* con
     }
     CU(cudaMemcpyAsync(dd, hd, sizeof(SeqDesc) * batch, cudaMemcpyHostToDevice, s));
     CU(cudaEventRecord(ctx->seq_ev[slot], s));
-    rc = grow(ctx->q_rot, (size_t)batch * hs.num_heads * hs.head_dim, s);
-    if (rc) return rc;
     SeqRef seqs{};
     seqs.many = dd;
-    PrepArgs p{};
-    p.q = q;
-    p.k_new = k_new;
-    p.v_new = v_new;
-    p.b_q = first->b_q;
-    p.b_k = first->b_k;
-    p.b_v = first->b_v;
-    p.q_norm = first->q_norm;
-    p.k_norm = first->k_norm;
-    p.inv_freq = first->inv_freq;
-    p.eps = first->eps;
-    p.q_rot = ctx->q_rot.p;
-    p.seqs = seqs;
-    p.batch = batch;
-    p.T = 1;
-    p.hs = hs;
-    CU(launch_prep_append(p, s));
-    rc = run_attention(ctx, hs, seqs, batch, 1, total_visible, max_visible, ctx->q_rot.p, out, scale, flags, s);
+    rc = run_step(ctx, first, seqs, batch, 1, total_visible, max_visible, q, k_new, v_new, out, scale, flags, s);
     if (rc) return rc;
     for (int b = 0; b < batch; ++b) kvs[b]->len += 1;
     return SHAINET_ATTN_OK;

@@ -1,29 +1,40 @@
 // Split-K flash-decode over the fp32 KV cache, CUDA cores, sm_100a.
 //
 // Replaces the reference's attention_kv_kernel
-// (src/shainet/native/cuda_kernels.cu:734-806) for decode rows.  The reference
-// launches one 128-thread CTA per (query head, token): 32 CTAs for a 32-head
-// model, every query head of a group re-reading its kv head's K and V, scores
-// round-tripping through a global scratch.  Here:
+// (src/shainet/native/cuda_kernels.cu:734-806) for decode rows, and in its fused
+// form also the host loops in front of it (bias, per-head RMSNorm, RoPE, cache
+// append: src/shainet/transformer/llama_block.cr:257-286, 440-467, 585-641).
+// The reference launches one 128-thread CTA per (query head, token): 32 CTAs
+// for a 32-head model, every query head of a group re-reading its kv head's K
+// and V, scores round-tripping through a global scratch.  Here:
 //
 //  * the visible cache rows of one kv head are cut into `chunk_rows`-sized
 //    splits; one CTA per (split, kv head, row) streams its slice ONCE for all
 //    G = heads_per_kv query heads of the group;
 //  * a producer warp moves K and V tiles global -> shared with 1-D bulk
 //    asynchronous copies (the TMA engine; no tensor map, no multicast) through
-//    a ring of mbarrier-guarded stages, so tens of KB per SM are in flight
+//    a ring of mbarrier-guarded stages, so ~100 KB per SM are in flight
 //    without holding registers;
 //  * each consumer warp owns whole tiles: q lives in registers (16 lanes per K
 //    row, 128-bit shared loads), the 16 x G partial dot products of a batch of
 //    rows are reduce-scattered across the half-warp so every lane ends with one
 //    score, the softmax is the single-pass (online) form kept per warp, and
-//    P.V runs with one lane per four output columns;
-//  * per-split (max, sum, unnormalised output) go to a small scratch and a
-//    second kernel merges the splits.
+//    P.V runs with one lane per four output columns; multiply-adds are issued
+//    as packed fp32 pairs (fma.rn.f32x2);
+//  * per-split (max, sum, unnormalised output) go to a small scratch.  The
+//    plain kernel leaves the merge to a second kernel; the fused kernel lets
+//    the last CTA of each kv head (an atomic ticket, no waiting) do it.
+//
+// The fused kernel is launched with programmatic stream serialization: it
+// prefetches cache tiles that no running kernel can still be writing, then
+// waits for the previous grid, then lets the next grid start.  Consecutive
+// layers therefore hand SMs over one CTA at a time instead of draining the GPU
+// between launches.
 //
 // All waits are bounded (see mbar_wait); a timed-out wait records a status
 // word and the kernel unwinds.
 #include <math.h>
+#include <type_traits>
 #include "kernels.h"
 
 namespace shainet {
@@ -34,6 +45,37 @@ constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int SK_MAX_STAGES = 32;
 
+// Packed fp32 pairs: sm_100 executes fma.rn.f32x2 on a 64-bit register pair,
+// two fused multiply-adds per issued instruction.
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+__device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+__device__ __forceinline__ ulonglong2 lds128x2(const void* p) { return *reinterpret_cast<const ulonglong2*>(p); }
+
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Tile geometry.  R*G = 16 scores per half-warp per batch, so a batch is
 // BR = 2*16/G rows; a warp tile is a whole number of batches.  The ring has a
 // multiple of NW stages so that every stage is always consumed by the same
@@ -43,9 +85,10 @@ template <int HD, int G>
 struct SKDefault {
     static constexpr int BR = 2 * (16 / G);
     static constexpr int TW = BR > 8 ? BR : 8;                         // rows per warp tile
-    static constexpr int NW = (2 * TW * HD * 4 > 16 * 1024) ? 4 : 8;   // consumer warps
-    static constexpr int SMEM_KB = 200;                                // one CTA per SM
-    static constexpr int CTAS_PER_SM = 1;
+    static constexpr int NW = 4;                                       // consumer warps
+    static constexpr bool BIG = 2 * TW * HD * 4 > 16 * 1024;           // ring + extras would not fit twice per SM
+    static constexpr int SMEM_KB = BIG ? 216 : 110;                    // 2 x (110 + 1 KB reserved) fits 227 KB
+    static constexpr int CTAS_PER_SM = BIG ? 1 : 2;
 };
 
 template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
@@ -60,11 +103,16 @@ struct SK {
     static constexpr int TILE_FLOATS = TW * HD;        // per tensor
     static constexpr int STAGE_FLOATS = 2 * TILE_FLOATS;
     static constexpr int RPI = 128 / HD;               // V rows covered by one warp-wide 128-bit load
-    static constexpr int WARP_SCRATCH = 32 + 16;       // p[BR*G = 32] + alpha[G <= 16]
+    static constexpr int WARP_SCRATCH = 2 * (32 + 16); // (p,p)[BR*G = 32] + (alpha,alpha)[G <= 16], as floats
     static constexpr int THREADS = (NW + 1) * 32;
     static constexpr int CTAS_PER_SM = CTAS_;
     static constexpr bool MATH = MATH_;
-    static constexpr int FIXED_BYTES = NW * WARP_SCRATCH * 4 + 2 * SK_MAX_STAGES * 8;
+    // fused kernel extras: rotated q of the group, and a one-batch tile for the new row
+    static constexpr int QS_FLOATS = G * HD;
+    static constexpr int XK_FLOATS = BR * HD;
+    static constexpr int XV_FLOATS = HD;
+    static constexpr int EXTRA_FLOATS = QS_FLOATS + XK_FLOATS + XV_FLOATS + 8;
+    static constexpr int FIXED_BYTES = (NW * WARP_SCRATCH + EXTRA_FLOATS) * 4 + 2 * SK_MAX_STAGES * 8;
     static constexpr int NS_RAW = (SMEM_KB_ * 1024 - FIXED_BYTES) / (STAGE_FLOATS * 4);
     static constexpr int NS_CAP = NS_RAW > SK_MAX_STAGES ? SK_MAX_STAGES : NS_RAW;
     static constexpr int NS = NS_CAP / NW * NW;        // ring stages, a multiple of NW
@@ -75,6 +123,29 @@ struct SK {
     static_assert(TW % BR == 0, "a warp tile is a whole number of batches");
     static_assert(NS >= NW, "ring shorter than the number of consumer warps");
     static_assert(MERGE_FLOATS <= NS * STAGE_FLOATS, "merge area must fit in the ring");
+};
+
+// Carve-up of the dynamic shared memory, common to both kernels.
+template <class C>
+struct Smem {
+    float* stages;
+    float* warp_scratch;
+    float* qs;   // [G][HD] rotated q (fused kernel)
+    float* xk;   // [BR][HD], row 0 = the new rotated k row (fused kernel, last split)
+    float* xv;   // [HD] the new v row
+    int* flag;   // ticket broadcast
+    uint64_t* full_bar;
+    uint64_t* empty_bar;
+    __device__ explicit Smem(unsigned char* raw) {
+        stages = reinterpret_cast<float*>(raw);
+        warp_scratch = stages + (size_t)C::NS * C::STAGE_FLOATS;
+        qs = warp_scratch + C::NW * C::WARP_SCRATCH;
+        xk = qs + C::QS_FLOATS;
+        xv = xk + C::XK_FLOATS;
+        flag = reinterpret_cast<int*>(xv + C::XV_FLOATS);
+        full_bar = reinterpret_cast<uint64_t*>(xv + C::XV_FLOATS + 8);
+        empty_bar = full_bar + SK_MAX_STAGES;
+    }
 };
 
 // 16-lane reduce-scatter of 16 values: on return acc[0] of lane i (i = lane & 15)
@@ -96,15 +167,221 @@ __device__ __forceinline__ void reduce_scatter16(float (&acc)[16], int lane) {
     }
 }
 
+// Running state of one consumer warp.
+template <int G>
+struct WarpState {
+    f32x2 o[G][2];  // this lane's four output columns of every head, as two packed pairs
+    float m, l;     // running max / partial sum for head (lane & 15) % G
+    __device__ void init() {
+#pragma unroll
+        for (int g = 0; g < G; ++g) o[g][0] = o[g][1] = 0ull;
+        m = -INFINITY;
+        l = 0.0f;
+    }
+};
+
+// q of the G heads, this lane's 4*CPL columns of each, as packed pairs
+// (columns 0-1 and 2-3 of every 16-byte chunk).  qrow: [G][HD], global or shared.
+template <int HD, int G, class C>
+__device__ __forceinline__ void load_q(ulonglong2 (&q)[G][C::CPL], const float* qrow, int i16) {
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int c = 0; c < C::CPL; ++c)
+            q[g][c] = *reinterpret_cast<const ulonglong2*>(qrow + (size_t)g * HD + (c * 16 + i16) * 4);
+}
+
+// One warp tile: `nrows` valid rows of K (ks) and V (vs) in shared memory.
+template <int HD, int G, class C>
+__device__ __forceinline__ void consume_tile(const float* ks, const float* vs, int nrows, const ulonglong2 (&q)[G][C::CPL],
+                                             WarpState<G>& st, f32x2* ps, f32x2* as, int lane, float scale, int nbatches) {
+    const int i16 = lane & 15, hw = lane >> 4;
+    const int my_r = hw * C::R + i16 / G;  // row in batch of this lane's score (its head is i16 % G)
+#pragma unroll
+    for (int bb = 0; bb < C::NB; ++bb) {
+        const int base = bb * C::BR;
+        if (bb >= nbatches || base >= nrows) break;  // warp-uniform
+        // ---- scores: acc[rr*G + g] for the R rows of this half-warp; even and odd
+        // columns accumulate in the two halves of a packed pair ----
+        f32x2 acc2[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
+#pragma unroll
+        for (int rr = 0; rr < C::R; ++rr) {
+            const float* krow = ks + (size_t)(base + hw * C::R + rr) * HD;
+#pragma unroll
+            for (int c = 0; c < C::CPL; ++c) {
+                const ulonglong2 kk = lds128x2(krow + (c * 16 + i16) * 4);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
+                    acc2[rr * G + g] = ffma2(q[g][c].y, kk.y, acc2[rr * G + g]);
+                }
+            }
+        }
+        float acc[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float lo, hi;
+            unpack2(acc2[k], lo, hi);
+            acc[k] = lo + hi;
+        }
+        reduce_scatter16(acc, lane);
+        float sc = acc[0] * scale;
+        if (base + my_r >= nrows) sc = -INFINITY;  // rows past the end of the slice
+        // ---- online softmax for this lane's head ----
+        float bmax = sc;
+#pragma unroll
+        for (int off = G; off < 32; off <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(FULL, bmax, off));
+        const float m_new = fmaxf(st.m, bmax);
+        const float alpha = exp2f((st.m - m_new) * LOG2E);  // 0 while the running max is -inf
+        const float p = exp2f((sc - m_new) * LOG2E);
+        st.l = fmaf(st.l, alpha, p);
+        st.m = m_new;
+        __syncwarp();  // previous batch's reads of ps/as are done
+        ps[lane] = pack2(p, p);  // index = row_in_batch * G + head
+        if (lane < G) as[lane] = pack2(alpha, alpha);
+        const bool rescale = __any_sync(FULL, alpha != 1.0f);
+        __syncwarp();
+        if (rescale) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const f32x2 al = as[g];
+                st.o[g][0] = fmul2(st.o[g][0], al);
+                st.o[g][1] = fmul2(st.o[g][1], al);
+            }
+        }
+        // ---- o += P.V ----
+#pragma unroll
+        for (int rr = 0; rr < C::BR; rr += C::RPI) {
+            const int row = base + rr + (C::RPI == 2 ? hw : 0);
+            if (base + rr >= nrows) break;  // warp-uniform
+            if (row < nrows) {
+                const int col = (C::RPI == 2 ? i16 : lane) * 4;
+                const ulonglong2 vv = lds128x2(vs + (size_t)row * HD + col);
+                const f32x2* prow = ps + (row - base) * G;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const f32x2 pg = prow[g];
+                    st.o[g][0] = ffma2(pg, vv.x, st.o[g][0]);
+                    st.o[g][1] = ffma2(pg, vv.y, st.o[g][1]);
+                }
+            }
+        }
+    }
+}
+
+// After the last tile: fold the lanes that share a head (sum) and, for
+// head_dim 64, the two half-warps that each took every other V row.
+template <int HD, int G, class C>
+__device__ __forceinline__ void finish_warp(WarpState<G>& st) {
+#pragma unroll
+    for (int off = G; off < 32; off <<= 1) st.l += __shfl_xor_sync(FULL, st.l, off);
+    if (C::RPI == 2) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                float lo, hi;
+                unpack2(st.o[g][k], lo, hi);
+                lo += __shfl_xor_sync(FULL, lo, 16);
+                hi += __shfl_xor_sync(FULL, hi, 16);
+                st.o[g][k] = pack2(lo, hi);
+            }
+    }
+}
+
+// Consumer warps park their state in the (now idle) ring.
+template <int HD, int G, class C>
+__device__ __forceinline__ void park_state(const WarpState<G>& st, float* ring, int warp, int lane) {
+    float* mo = ring;                              // [NW][G][HD]
+    float* mm = mo + (size_t)C::NW * G * HD;       // [NW][G]
+    float* ml = mm + C::NW * G;                    // [NW][G]
+    if (lane < G) {  // lane < G holds head `lane`
+        mm[warp * G + lane] = st.m;
+        ml[warp * G + lane] = st.l;
+    }
+    if (C::RPI == 1 || lane < 16) {
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            *reinterpret_cast<ulonglong2*>(mo + ((size_t)warp * G + g) * HD + lane * 4) = make_ulonglong2(st.o[g][0], st.o[g][1]);
+    }
+}
+
+// Merge of the NW warps' states for element (g, d): unnormalised o, max and sum.
+template <int HD, int G, class C>
+__device__ __forceinline__ void merge_warps(const float* ring, int g, int d, float& acc, float& M, float& L) {
+    const float* mo = ring;
+    const float* mm = mo + (size_t)C::NW * G * HD;
+    const float* ml = mm + C::NW * G;
+    M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < C::NW; ++w) M = fmaxf(M, mm[w * G + g]);
+    L = 0.0f;
+    acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < C::NW; ++w) {
+        const float mw = mm[w * G + g];
+        const float wt = (mw == -INFINITY) ? 0.0f : exp2f((mw - M) * LOG2E);
+        L = fmaf(wt, ml[w * G + g], L);
+        acc = fmaf(wt, mo[((size_t)w * G + g) * HD + d], acc);
+    }
+}
+
+template <class C>
+__device__ __forceinline__ void init_barriers(Smem<C>& sm) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::NS; ++s) {
+            mbar_init(&sm.full_bar[s], 1);
+            mbar_init(&sm.empty_bar[s], 1);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+}
+
+// Producer: tiles [first, last) of a slice starting at kbase/vbase with `rows` rows.
+template <int HD, class C>
+__device__ __forceinline__ bool produce_tiles(Smem<C>& sm, const float* kbase, const float* vbase, int rows, int first,
+                                              int last, AttnStatus* status) {
+    for (int i = first; i < last; ++i) {
+        const int s = i % C::NS;
+        if (i >= C::NS && !mbar_wait(&sm.empty_bar[s], ((i / C::NS) - 1) & 1, status, 1)) return false;
+        const int nrows = min(C::TW, rows - i * C::TW);
+        const uint32_t bytes = (uint32_t)nrows * HD * 4;
+        float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
+        float* vs = ks + C::TILE_FLOATS;
+        mbar_arrive_expect_tx(&sm.full_bar[s], 2 * bytes);
+        bulk_g2s(ks, kbase + (size_t)i * C::TILE_FLOATS, bytes, &sm.full_bar[s]);
+        bulk_g2s(vs, vbase + (size_t)i * C::TILE_FLOATS, bytes, &sm.full_bar[s]);
+    }
+    return true;
+}
+
+template <int HD, int G, class C>
+__device__ __forceinline__ void consume_slice(Smem<C>& sm, int ntiles, int rows, const ulonglong2 (&q)[G][C::CPL],
+                                              WarpState<G>& st, int warp, int lane, float scale, AttnStatus* status) {
+    f32x2* ps = reinterpret_cast<f32x2*>(sm.warp_scratch + warp * C::WARP_SCRATCH);  // (p,p) per (row, head)
+    f32x2* as = ps + 32;                                                             // (alpha,alpha) per head
+    for (int i = warp; i < ntiles; i += C::NW) {
+        const int s = i % C::NS;
+        if (!mbar_wait(&sm.full_bar[s], (i / C::NS) & 1, status, 2)) break;
+        const float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
+        const float* vs = ks + C::TILE_FLOATS;
+        const int nrows = min(C::TW, rows - i * C::TW);
+        consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::MATH ? C::NB : 0);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty_bar[s]);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Plain split-K kernel: q already rotated, cache already appended.
+// ---------------------------------------------------------------------------
 template <int HD, int G, class C>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_splitk_kernel(AttnArgs a) {
-    constexpr int NS = C::NS;
     extern __shared__ __align__(1024) unsigned char sk_smem_raw[];
-    float* stages = reinterpret_cast<float*>(sk_smem_raw);
-    float* warp_scratch = stages + (size_t)NS * C::STAGE_FLOATS;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(warp_scratch + C::NW * C::WARP_SCRATCH);
-    uint64_t* empty_bar = full_bar + NS;
-
+    Smem<C> sm(sk_smem_raw);
     const int split = blockIdx.x, kv_h = blockIdx.y, r = blockIdx.z;
     const int H = a.hs.num_heads;
     const int b = r / a.T, t = r % a.T;
@@ -113,186 +390,33 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_splitk_kernel
     const int row0 = split * a.chunk_rows;
     if (row0 >= visible) return;  // whole CTA: this sequence has fewer splits
     const int row1 = min(row0 + a.chunk_rows, visible);
-    const int ntiles = (row1 - row0 + C::TW - 1) / C::TW;
+    const int rows = row1 - row0;
+    const int ntiles = (rows + C::TW - 1) / C::TW;
     const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
     const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        fence_mbar_init();
-    }
-    __syncthreads();
+    init_barriers(sm);
 
-    // Per-warp running state (consumers only; declared here so the merge below sees it).
-    float o[G][4];
-    float m_run = -INFINITY, l_run = 0.0f;
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-        for (int k = 0; k < 4; ++k) o[g][k] = 0.0f;
-
+    WarpState<G> st;
+    st.init();
     if (warp == C::NW) {
-        // ---------------- producer ----------------
-        if (lane == 0) {
-            for (int i = 0; i < ntiles; ++i) {
-                const int s = i % NS;
-                if (i >= NS && !mbar_wait(&empty_bar[s], ((i / NS) - 1) & 1, a.status, 1)) break;
-                const int nrows = min(C::TW, (row1 - row0) - i * C::TW);
-                const uint32_t bytes = (uint32_t)nrows * HD * 4;
-                float* ks = stages + (size_t)s * C::STAGE_FLOATS;
-                float* vs = ks + C::TILE_FLOATS;
-                mbar_arrive_expect_tx(&full_bar[s], 2 * bytes);
-                bulk_g2s(ks, kbase + (size_t)i * C::TILE_FLOATS, bytes, &full_bar[s]);
-                bulk_g2s(vs, vbase + (size_t)i * C::TILE_FLOATS, bytes, &full_bar[s]);
-            }
-        }
+        if (lane == 0) produce_tiles<HD, C>(sm, kbase, vbase, rows, 0, ntiles, a.status);
     } else {
-        // ---------------- consumers ----------------
-        const int i16 = lane & 15, hw = lane >> 4;
-        const int my_r = hw * C::R + i16 / G;  // row in batch of this lane's score (its head is i16 % G)
-        float* ps = warp_scratch + warp * C::WARP_SCRATCH;
-        float* as = ps + 32;
-
-        // q for the G heads of this kv head, this lane's 4*CPL columns of each.
-        float4 q[G][C::CPL];
-        {
-            const float* qrow = a.q_rot + ((size_t)r * H + (size_t)kv_h * G) * HD;
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-#pragma unroll
-                for (int c = 0; c < C::CPL; ++c)
-                    q[g][c] = *reinterpret_cast<const float4*>(qrow + (size_t)g * HD + (c * 16 + i16) * 4);
-        }
-
-        for (int i = warp; i < ntiles; i += C::NW) {
-            const int s = i % NS;
-            if (!mbar_wait(&full_bar[s], (i / NS) & 1, a.status, 2)) break;
-            const float* ks = stages + (size_t)s * C::STAGE_FLOATS;
-            const float* vs = ks + C::TILE_FLOATS;
-            const int nrows = min(C::TW, (row1 - row0) - i * C::TW);
-
-#pragma unroll
-            for (int bb = 0; bb < (C::MATH ? C::NB : 0); ++bb) {
-                const int base = bb * C::BR;
-                if (base >= nrows) break;  // warp-uniform
-                // ---- scores: acc[rr*G + g] for the R rows of this half-warp ----
-                float acc[16];
-#pragma unroll
-                for (int k = 0; k < 16; ++k) acc[k] = 0.0f;
-#pragma unroll
-                for (int rr = 0; rr < C::R; ++rr) {
-                    const float* krow = ks + (size_t)(base + hw * C::R + rr) * HD;
-#pragma unroll
-                    for (int c = 0; c < C::CPL; ++c) {
-                        const float4 kk = lds128(krow + (c * 16 + i16) * 4);
-#pragma unroll
-                        for (int g = 0; g < G; ++g) {
-                            float v = acc[rr * G + g];
-                            v = fmaf(q[g][c].x, kk.x, v);
-                            v = fmaf(q[g][c].y, kk.y, v);
-                            v = fmaf(q[g][c].z, kk.z, v);
-                            v = fmaf(q[g][c].w, kk.w, v);
-                            acc[rr * G + g] = v;
-                        }
-                    }
-                }
-                reduce_scatter16(acc, lane);
-                float sc = acc[0] * a.scale;
-                if (base + my_r >= nrows) sc = -INFINITY;  // rows past the end of the slice
-                // ---- online softmax for head my_g ----
-                float bmax = sc;
-#pragma unroll
-                for (int off = G; off < 32; off <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(FULL, bmax, off));
-                const float m_new = fmaxf(m_run, bmax);
-                const float alpha = exp2f((m_run - m_new) * LOG2E);  // 0 while m_run is -inf
-                const float p = exp2f((sc - m_new) * LOG2E);
-                l_run = fmaf(l_run, alpha, p);
-                m_run = m_new;
-                __syncwarp();  // previous batch's reads of ps/as are done
-                ps[lane] = p;  // index = row_in_batch * G + head
-                if (lane < G) as[lane] = alpha;
-                const bool rescale = __any_sync(FULL, alpha != 1.0f);
-                __syncwarp();
-                if (rescale) {
-#pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        const float al = as[g];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) o[g][k] *= al;
-                    }
-                }
-                // ---- o += P.V ----
-#pragma unroll
-                for (int rr = 0; rr < C::BR; rr += C::RPI) {
-                    const int row = base + rr + (C::RPI == 2 ? hw : 0);
-                    if (base + rr >= nrows) break;  // warp-uniform
-                    if (row < nrows) {
-                        const int col = (C::RPI == 2 ? i16 : lane) * 4;
-                        const float4 vv = lds128(vs + (size_t)row * HD + col);
-                        const float* prow = ps + (row - base) * G;
-#pragma unroll
-                        for (int g = 0; g < G; ++g) {
-                            const float pg = prow[g];
-                            o[g][0] = fmaf(pg, vv.x, o[g][0]);
-                            o[g][1] = fmaf(pg, vv.y, o[g][1]);
-                            o[g][2] = fmaf(pg, vv.z, o[g][2]);
-                            o[g][3] = fmaf(pg, vv.w, o[g][3]);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
-        }
-
-        // Sum of p over the lanes that share a head.
-#pragma unroll
-        for (int off = G; off < 32; off <<= 1) l_run += __shfl_xor_sync(FULL, l_run, off);
-        if (C::RPI == 2) {
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-#pragma unroll
-                for (int k = 0; k < 4; ++k) o[g][k] += __shfl_xor_sync(FULL, o[g][k], 16);
-        }
+        ulonglong2 q[G][C::CPL];
+        load_q<HD, G, C>(q, a.q_rot + ((size_t)r * H + (size_t)kv_h * G) * HD, lane & 15);
+        consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
+        finish_warp<HD, G, C>(st);
     }
-
     // All tiles are consumed (or abandoned after a timeout): every bulk copy
-    // that was issued has landed, so the stage memory can be reused.
+    // that was issued has landed, so the ring can be reused.
     __syncthreads();
-    float* mo = stages;                               // [NW][G][HD]
-    float* mm = mo + (size_t)C::NW * G * HD;          // [NW][G]
-    float* ml = mm + C::NW * G;                       // [NW][G]
-    if (warp < C::NW) {
-        if (lane < G) {
-            mm[warp * G + lane] = m_run;  // lane < G holds head `lane`
-            ml[warp * G + lane] = l_run;
-        }
-        if (C::RPI == 1 || lane < 16) {
-#pragma unroll
-            for (int g = 0; g < G; ++g)
-                *reinterpret_cast<float4*>(mo + ((size_t)warp * G + g) * HD + lane * 4) =
-                    make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
-        }
-    }
+    if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
     __syncthreads();
     const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
     for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
         const int g = e / HD, d = e - g * HD;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < C::NW; ++w) M = fmaxf(M, mm[w * G + g]);
-        float L = 0.0f, acc = 0.0f;
-#pragma unroll
-        for (int w = 0; w < C::NW; ++w) {
-            const float mw = mm[w * G + g];
-            const float wt = (mw == -INFINITY) ? 0.0f : exp2f((mw - M) * LOG2E);
-            L = fmaf(wt, ml[w * G + g], L);
-            acc = fmaf(wt, mo[((size_t)w * G + g) * HD + d], acc);
-        }
+        float acc, M, L;
+        merge_warps<HD, G, C>(sm.stages, g, d, acc, M, L);
         const int h = kv_h * G + g;
         if (nsplit_here == 1) {
             a.out[((size_t)r * H + h) * HD + d] = acc / L;
@@ -330,22 +454,200 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(AttnArgs a) {
     a.out[((size_t)r * a.hs.num_heads + h) * HD + d] = acc / L;
 }
 
-template <int HD, int G, class C = SK<HD, G>>
-cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
-    const size_t smem = C::SMEM_BYTES;
-    static unsigned long long configured = 0;  // bit per device
-    cudaError_t e;
+// ---------------------------------------------------------------------------
+// Fused decode kernel: one new token per sequence.  Prologue = bias, per-head
+// RMSNorm and RoPE of the group's q heads (every CTA) and of the new k row, and
+// the append of k/v (the CTA whose slice ends at the new position); then the
+// split-K stream; then the last CTA of each (row, kv head) merges the splits.
+// ---------------------------------------------------------------------------
+
+// One head row (HD floats at `row`, shared memory, already biased): optional
+// RMSNorm with the reference's sequential fp32 sum, then the half-split
+// rotation, in place.  Same arithmetic as prep_append_kernel.
+template <int HD>
+__device__ __forceinline__ void norm_rope_row(float* row, const float* w, const float* inv_freq, double eps, float fpos,
+                                              int lane) {
+    constexpr int half = HD / 2;
+    float inv = 1.0f;
+    if (w) {
+        if (lane == 0) {
+            float ss = 0.0f;
+            for (int d = 0; d < HD; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
+            const float mean = __fdiv_rn(ss, (float)HD);
+            inv = (float)(1.0 / sqrt((double)mean + eps));
+        }
+        inv = __shfl_sync(FULL, inv, 0);
+    }
+#pragma unroll
+    for (int i = lane; i < half; i += 32) {
+        float x0 = row[i], x1 = row[i + half];
+        if (w) {
+            x0 = __fmul_rn(__fmul_rn(x0, inv), w[i]);
+            x1 = __fmul_rn(__fmul_rn(x1, inv), w[i + half]);
+        }
+        const float angle = __fmul_rn(fpos, inv_freq[i]);
+        float s, c;
+        sincosf(angle, &s, &c);
+        row[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        row[i + half] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+    }
+}
+
+template <int HD, int G, class C>
+__global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_kernel(FusedArgs a) {
+    extern __shared__ __align__(1024) unsigned char sk_smem_raw[];
+    Smem<C> sm(sk_smem_raw);
+    const int split = blockIdx.x, kv_h = blockIdx.y, r = blockIdx.z;
+    const int H = a.hs.num_heads, KV = a.hs.num_kv_heads;
+    const SeqDesc sd = a.seqs.many ? a.seqs.many[r] : a.seqs.one;
+    const int start = sd.start;     // position of the new token = rows already cached
+    const int visible = start + 1;
+    const int row0 = split * a.chunk_rows;
+    if (row0 >= visible) return;    // whole CTA: this sequence has fewer splits (an exit counts as its trigger)
+    const int row1 = min(row0 + a.chunk_rows, visible);
+    const bool owns_new = row1 == visible;              // this slice ends with the new token
+    const int rows = (owns_new ? start : row1) - row0;  // rows that come from the cache
+    const int ntiles = (rows + C::TW - 1) / C::TW;
+    // Tiles that end at or below `safe_end` cannot be under construction by the
+    // grid that may still be running; they are fetched before waiting for it.
+    const int safe_end = start - a.unsafe_tail;
+    int n_early = row0 + rows <= safe_end ? ntiles : max(0, (safe_end - row0) / C::TW);
+    n_early = min(min(n_early, ntiles), C::NS);
+    const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
+    const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    init_barriers(sm);
+
+    WarpState<G> st;
+    st.init();
+    if (warp == C::NW) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            const bool ok = produce_tiles<HD, C>(sm, kbase, vbase, rows, 0, n_early, a.status);
+            grid_dependency_wait();
+            grid_launch_dependents();
+            if (ok) produce_tiles<HD, C>(sm, kbase, vbase, rows, n_early, ntiles, a.status);
+        }
+    } else {
+        // ---------------- consumers ----------------
+        grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
+        const float fpos = (float)start;
+        const int items = G + (owns_new ? 2 : 0);
+        for (int it = warp; it < items; it += C::NW) {
+            const float* src;
+            const float* bias;
+            float* row;
+            if (it < G) {
+                const int h = kv_h * G + it;
+                src = a.q + ((size_t)r * H + h) * HD;
+                bias = a.b_q ? a.b_q + (size_t)h * HD : nullptr;
+                row = sm.qs + it * HD;
+            } else if (it == G) {
+                src = a.k_new + ((size_t)r * KV + kv_h) * HD;
+                bias = a.b_k ? a.b_k + (size_t)kv_h * HD : nullptr;
+                row = sm.xk;
+            } else {
+                src = a.v_new + ((size_t)r * KV + kv_h) * HD;
+                bias = a.b_v ? a.b_v + (size_t)kv_h * HD : nullptr;
+                row = sm.xv;
+            }
+#pragma unroll
+            for (int d = lane; d < HD; d += 32) {
+                float x = src[d];
+                if (bias) x = __fadd_rn(x, bias[d]);
+                row[d] = x;
+            }
+            __syncwarp();
+            if (it <= G) norm_rope_row<HD>(row, it < G ? a.q_norm : a.k_norm, a.inv_freq, a.eps, fpos, lane);
+            __syncwarp();
+            if (it >= G) {  // append to the cache
+                float* dst = (it == G ? sd.k : sd.v) + ((size_t)kv_h * sd.capacity + start) * HD;
+#pragma unroll
+                for (int d = lane; d < HD; d += 32) dst[d] = row[d];
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");  // consumers only: qs/xk/xv complete
+        ulonglong2 q[G][C::CPL];
+        load_q<HD, G, C>(q, sm.qs, lane & 15);
+        consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
+        if (owns_new && warp == (ntiles % C::NW)) {
+            // the new token's own row, from shared memory (one valid row)
+            f32x2* ps = reinterpret_cast<f32x2*>(sm.warp_scratch + warp * C::WARP_SCRATCH);
+            consume_tile<HD, G, C>(sm.xk, sm.xv, 1, q, st, ps, ps + 32, lane, a.scale, 1);
+        }
+        finish_warp<HD, G, C>(st);
+    }
+    __syncthreads();  // every issued copy has landed; the ring is free
+    if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
+    __syncthreads();
+    const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
+    for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
+        const int g = e / HD, d = e - g * HD;
+        float acc, M, L;
+        merge_warps<HD, G, C>(sm.stages, g, d, acc, M, L);
+        const int h = kv_h * G + g;
+        if (nsplit_here == 1) {
+            a.out[((size_t)r * H + h) * HD + d] = acc / L;
+        } else {
+            const size_t pidx = ((size_t)r * H + h) * a.max_splits + split;
+            a.part_o[pidx * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[pidx * 2] = M;
+                a.part_ml[pidx * 2 + 1] = L;
+            }
+        }
+    }
+    if (nsplit_here == 1) return;
+    // ---- last CTA of this (row, kv head) merges the splits; nobody waits ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* ticket = a.tickets + (size_t)r * KV + kv_h;
+        const unsigned t = atomicAdd(ticket, 1u);
+        const int last = t == (unsigned)(nsplit_here - 1);
+        if (last) *ticket = 0u;  // ready for the next launch
+        *sm.flag = last;
+    }
+    __syncthreads();
+    if (!*sm.flag) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
+        const int g = e / HD, d = e - g * HD;
+        const int h = kv_h * G + g;
+        const size_t p0 = ((size_t)r * H + h) * a.max_splits;
+        float M = -INFINITY;
+        for (int s = 0; s < nsplit_here; ++s) M = fmaxf(M, __ldcg(a.part_ml + (p0 + s) * 2));
+        float L = 0.0f, acc = 0.0f;
+        for (int s = 0; s < nsplit_here; ++s) {
+            const float w = exp2f((__ldcg(a.part_ml + (p0 + s) * 2) - M) * LOG2E);
+            L = fmaf(w, __ldcg(a.part_ml + (p0 + s) * 2 + 1), L);
+            acc = fmaf(w, __ldcg(a.part_o + (p0 + s) * HD + d), acc);
+        }
+        a.out[((size_t)r * H + h) * HD + d] = acc / L;
+    }
+}
+
+template <class K>
+cudaError_t set_smem_once(K kernel, size_t smem, unsigned long long& configured) {
     int dev = 0;
-    e = cudaGetDevice(&dev);
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 64 || !(configured >> dev & 1ull)) {
-        e = cudaFuncSetAttribute(attn_splitk_kernel<HD, G, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         if (dev < 64) configured |= 1ull << dev;
     }
+    return cudaSuccess;
+}
+
+template <int HD, int G, class C = SK<HD, G>>
+cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
+    static unsigned long long configured = 0;  // bit per device
+    cudaError_t e = set_smem_once(attn_splitk_kernel<HD, G, C>, C::SMEM_BYTES, configured);
+    if (e != cudaSuccess) return e;
     const int rows = a.batch * a.T;
     dim3 grid(a.max_splits, a.hs.num_kv_heads, rows);
-    attn_splitk_kernel<HD, G, C><<<grid, C::THREADS, smem, s>>>(a);
+    attn_splitk_kernel<HD, G, C><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (a.max_splits > 1) {
@@ -356,14 +658,32 @@ cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
     return e;
 }
 
-template <int HD>
-cudaError_t dispatch_g(const AttnArgs& a, cudaStream_t s) {
+template <int HD, int G, class C = SK<HD, G>>
+cudaError_t launch_fused(const FusedArgs& a, cudaStream_t s) {
+    static unsigned long long configured = 0;
+    cudaError_t e = set_smem_once(attn_decode_fused_kernel<HD, G, C>, C::SMEM_BYTES, configured);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(a.max_splits, a.hs.num_kv_heads, a.batch);
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, attn_decode_fused_kernel<HD, G, C>, a);
+}
+
+template <class A, class F>
+cudaError_t dispatch_g(const A& a, F&& f) {
     switch (a.hs.num_heads / a.hs.num_kv_heads) {
-        case 1: return launch_sk<HD, 1>(a, s);
-        case 2: return launch_sk<HD, 2>(a, s);
-        case 4: return launch_sk<HD, 4>(a, s);
-        case 8: return launch_sk<HD, 8>(a, s);
-        case 16: return launch_sk<HD, 16>(a, s);
+        case 1: return f(std::integral_constant<int, 1>{});
+        case 2: return f(std::integral_constant<int, 2>{});
+        case 4: return f(std::integral_constant<int, 4>{});
+        case 8: return f(std::integral_constant<int, 8>{});
+        case 16: return f(std::integral_constant<int, 16>{});
         default: return cudaErrorInvalidValue;
     }
 }
@@ -378,7 +698,11 @@ bool splitk_supported(const HeadShape& hs) {
 int splitk_tile_rows(const HeadShape& hs) {
     const int g = hs.num_heads / hs.num_kv_heads;
     const int br = 2 * (16 / g);
-    return br > 8 ? br : 8;
+    return br > 8 ? br : 8;  // SKDefault::TW
+}
+
+int splitk_ctas_per_sm(const HeadShape& hs) {
+    return 2 * splitk_tile_rows(hs) * hs.head_dim * 4 > 16 * 1024 ? 1 : 2;  // SKDefault::CTAS_PER_SM
 }
 
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits) {
@@ -387,8 +711,15 @@ size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits) {
 
 cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s) {
     if (a.batch * a.T == 0) return cudaSuccess;
-    if (a.hs.head_dim == 64) return dispatch_g<64>(a, s);
-    if (a.hs.head_dim == 128) return dispatch_g<128>(a, s);
+    if (a.hs.head_dim == 64) return dispatch_g(a, [&](auto g) { return launch_sk<64, decltype(g)::value>(a, s); });
+    if (a.hs.head_dim == 128) return dispatch_g(a, [&](auto g) { return launch_sk<128, decltype(g)::value>(a, s); });
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s) {
+    if (a.batch == 0) return cudaSuccess;
+    if (a.hs.head_dim == 64) return dispatch_g(a, [&](auto g) { return launch_fused<64, decltype(g)::value>(a, s); });
+    if (a.hs.head_dim == 128) return dispatch_g(a, [&](auto g) { return launch_fused<128, decltype(g)::value>(a, s); });
     return cudaErrorInvalidValue;
 }
 

@@ -61,6 +61,32 @@ struct AttnArgs {
     AttnStatus* status;
 };
 
+// One decode token per sequence, everything in one launch (T == 1).
+struct FusedArgs {
+    const float* q;        // [batch, num_heads*head_dim] raw projections
+    const float* k_new;    // [batch, num_kv_heads*head_dim]
+    const float* v_new;
+    const float* b_q;
+    const float* b_k;
+    const float* b_v;
+    const float* q_norm;
+    const float* k_norm;
+    const float* inv_freq;
+    double eps;
+    float* out;            // [batch, num_heads*head_dim]
+    SeqRef seqs;
+    int batch;
+    HeadShape hs;
+    float scale;
+    float* part_o;         // [batch, num_heads, max_splits, head_dim]
+    float* part_ml;        // [batch, num_heads, max_splits, 2]
+    unsigned* tickets;     // [batch, num_kv_heads], zero between launches
+    int chunk_rows;
+    int max_splits;
+    int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
+    AttnStatus* status;
+};
+
 // Fused (bias +) per-head RMSNorm + RoPE for q and k, and the append of the
 // rotated k rows and raw v rows into the cache.
 cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s);
@@ -71,8 +97,12 @@ cudaError_t launch_attn_generic(const AttnArgs& a, cudaStream_t s);
 // Split-K flash-decode for head_dim in {64,128} and group size in {1,2,4,8,16}.
 bool splitk_supported(const HeadShape& hs);
 int splitk_tile_rows(const HeadShape& hs);
+int splitk_ctas_per_sm(const HeadShape& hs);
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits);
 cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s);
+// Fused norm/RoPE/append + split-K decode + split merge, launched with
+// programmatic stream serialization.
+cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s);
 
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,

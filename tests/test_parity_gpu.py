@@ -137,12 +137,15 @@ def test_decode_error_against_f64_truth(ctx):
     g.close()
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["fused", "three_launches"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("G", [1, 2, 4, 8, 16])
-def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G):
-    """Forced split-K kernel: every template instance, lengths around the tile
-    and split boundaries (1 row, partial tiles, exact multiples)."""
+def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G, fused):
+    """Split-K decode, one fused launch or RoPE/append + split-K + merge: every
+    template instance, lengths around the tile and split boundaries (empty cache,
+    1 row, partial tiles, exact multiples)."""
     import shainet_b200 as S
+    flags = S.F_SPLITK | (0 if fused else S.F_UNFUSED)
     rng = np.random.default_rng(hd * 100 + G)
     KV = 2
     shape = dict(H=KV * G, KV=KV, hd=hd, theta=10000.0)
@@ -157,6 +160,46 @@ def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G):
             q, k, v = qkv(rng, shape, 1)
             e = rel_err(g.forward_cached(q, k, v, S.F_SPLITK), o.attend_cached(q, k, v))
             assert e <= DECODE_TOL, (L, e)
+        g.close()
+
+
+def test_back_to_back_decode_without_sync(ctx):
+    """Asynchronous device-pointer calls queued back to back: a fused kernel may
+    start while its predecessor is still appending the previous row of the same
+    cache; two caches are also interleaved on one stream."""
+    import torch
+    rng = np.random.default_rng(808)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    pairs = [make_pair(ctx, Q30, rng), make_pair(ctx, Q30, rng)]
+    for o, g in pairs:
+        q, k, v = qkv(rng, Q30, 4500)
+        o.attend_cached(q, k, v, threads=8)
+        kc, vc = o.export_cache()
+        g.cache.import_(kc, vc)
+        g.cache.reserve(4600)
+    steps = 24
+    ins = [[qkv(rng, Q30, 1) for _ in pairs] for _ in range(steps)]
+    dins = [[tuple(torch.from_numpy(x).to(dev) for x in trip) for trip in row] for row in ins]
+    outs = [[torch.empty(1, Q30["H"] * Q30["hd"], device=dev) for _ in pairs] for _ in range(steps)]
+    torch.cuda.synchronize()
+    for t in range(steps):
+        for i, (_, g) in enumerate(pairs):
+            reps = 2 if (t % 5 == 0 and i == 0) else 1     # sometimes the same cache twice in a row
+            for _ in range(reps):
+                tq, tk, tv = dins[t][i]
+                g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), outs[t][i].data_ptr(), 1, stream)
+    torch.cuda.synchronize()
+    ctx.sync()
+    for t in range(steps):
+        for i, (o, _) in enumerate(pairs):
+            reps = 2 if (t % 5 == 0 and i == 0) else 1
+            for _ in range(reps):
+                ref = o.attend_cached(*ins[t][i])
+            assert rel_err(outs[t][i].cpu().numpy(), ref) <= DECODE_TOL, (t, i)
+    for o, g in pairs:
+        ko, vo = o.export_cache(); kg, vg = g.cache.export()
+        assert np.array_equal(vo, vg) and np.abs(ko - kg).max() <= 4e-7 * np.abs(ko).max()
         g.close()
 
 
