@@ -358,13 +358,18 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     f.scale = scale;
     f.status = ctx->status_dev;
     plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits);
+    f.max_groups = fused_merge_groups(f.max_splits);
     if (f.max_splits > 1) {
-        rc = grow(ctx->part, splitk_scratch_floats(hs, batch, f.max_splits), s);
+        const size_t n1 = (splitk_scratch_floats(hs, batch, f.max_splits) + 3) & ~(size_t)3;  // keeps the second table 16-byte aligned
+        const size_t n2 = splitk_scratch_floats(hs, batch, f.max_groups);
+        rc = grow(ctx->part, n1 + n2, s);
         if (rc) return rc;
         f.part_o = ctx->part.p;
-        f.part_ml = ctx->part.p + (size_t)batch * hs.num_heads * f.max_splits * hs.head_dim;
+        f.part_ml = f.part_o + (size_t)batch * hs.num_heads * f.max_splits * hs.head_dim;
+        f.part2_o = ctx->part.p + n1;
+        f.part2_ml = f.part2_o + (size_t)batch * hs.num_heads * f.max_groups * hs.head_dim;
     }
-    rc = ensure_tickets(ctx, (size_t)batch * hs.num_kv_heads, s);
+    rc = ensure_tickets(ctx, (size_t)batch * hs.num_kv_heads * (1 + f.max_groups), s);
     if (rc) return rc;
     f.tickets = ctx->tickets;
     // A fused kernel may start while the previous fused kernel still runs; that

@@ -454,6 +454,94 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(AttnArgs a) {
     a.out[((size_t)r * a.hs.num_heads + h) * HD + d] = acc / L;
 }
 
+// Merge of `count` partials (max, sum, unnormalised output) of the G heads of
+// (row r, kv head kv_h), entries first..first+count-1 of a [row][head][stride]
+// table, by the whole CTA.  `final` writes the normalised output row; otherwise
+// the merged partial goes to entry dst_index of a second table.  `scratch` is
+// shared memory for 2*G*count + 2*G floats.
+constexpr int MERGE_GROUP = 8;  // splits merged by the last CTA of each group
+
+template <int HD, int G, int THREADS>
+__device__ void merge_partials(const float* po, const float* pml, size_t stride, int first, int count, int r, int kv_h,
+                               int H, float* scratch, bool final, float* out, float* dst_o, float* dst_ml,
+                               size_t dst_stride, int dst_index) {
+    float* w = scratch;                 // [G][count]: max, then weight
+    float* lsum = w + G * count;        // [G][count]
+    float* Ms = lsum + G * count;       // [G]
+    float* Ls = Ms + G;                 // [G]
+    const size_t head0 = (size_t)r * H + (size_t)kv_h * G;
+    for (int idx = threadIdx.x; idx < G * count; idx += THREADS) {
+        const int g = idx / count, s = idx - g * count;
+        const size_t e = (head0 + g) * stride + first + s;
+        w[idx] = __ldcg(pml + 2 * e);
+        lsum[idx] = __ldcg(pml + 2 * e + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < G) {
+        const int g = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = 0; s < count; ++s) M = fmaxf(M, w[g * count + s]);
+        float L = 0.0f;
+        for (int s = 0; s < count; ++s) {
+            const float wt = exp2f((w[g * count + s] - M) * LOG2E);
+            w[g * count + s] = wt;
+            L = fmaf(wt, lsum[g * count + s], L);
+        }
+        Ms[g] = M;
+        Ls[g] = L;
+    }
+    __syncthreads();
+    constexpr int D4 = HD / 4;
+    for (int task = threadIdx.x; task < G * D4; task += THREADS) {
+        const int g = task / D4, d4 = task - g * D4;
+        const float4* src = reinterpret_cast<const float4*>(po + ((head0 + g) * stride + first) * HD) + d4;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < count; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                v[k] = (s0 + k < count) ? __ldcg(src + (size_t)(s0 + k) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float wt = (s0 + k < count) ? w[g * count + s0 + k] : 0.0f;
+                acc.x = fmaf(wt, v[k].x, acc.x);
+                acc.y = fmaf(wt, v[k].y, acc.y);
+                acc.z = fmaf(wt, v[k].z, acc.z);
+                acc.w = fmaf(wt, v[k].w, acc.w);
+            }
+        }
+        if (final) {
+            const float inv = 1.0f / Ls[g];
+            *(reinterpret_cast<float4*>(out + (head0 + g) * HD) + d4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        } else {
+            const size_t e = (head0 + g) * dst_stride + dst_index;
+            *(reinterpret_cast<float4*>(dst_o + e * HD) + d4) = acc;
+            if (d4 == 0) {
+                dst_ml[2 * e] = Ms[g];
+                dst_ml[2 * e + 1] = Ls[g];
+            }
+        }
+    }
+}
+
+// The calling CTA has published something and takes a ticket; true for the
+// CTA that took the last of `expected` tickets (it also resets the counter for
+// the next launch).  Nobody waits for anybody.
+__device__ __forceinline__ bool take_last_ticket(unsigned* ticket, int expected, int* flag) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(ticket, 1u);
+        const int last = t == (unsigned)(expected - 1);
+        if (last) *ticket = 0u;
+        *flag = last;
+    }
+    __syncthreads();
+    const bool last = *flag != 0;
+    if (last) __threadfence();
+    return last;
+}
+
 // ---------------------------------------------------------------------------
 // Fused decode kernel: one new token per sequence.  Prologue = bias, per-head
 // RMSNorm and RoPE of the group's q heads (every CTA) and of the new k row, and
@@ -598,33 +686,24 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
     }
     if (nsplit_here == 1) return;
-    // ---- last CTA of this (row, kv head) merges the splits; nobody waits ----
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned* ticket = a.tickets + (size_t)r * KV + kv_h;
-        const unsigned t = atomicAdd(ticket, 1u);
-        const int last = t == (unsigned)(nsplit_here - 1);
-        if (last) *ticket = 0u;  // ready for the next launch
-        *sm.flag = last;
+    // ---- two-level merge by "last finisher" tickets: the last CTA of each group
+    // of MERGE_GROUP splits folds the group, the last group folds the groups ----
+    const int ngroups = (nsplit_here + MERGE_GROUP - 1) / MERGE_GROUP;
+    const int grp = split / MERGE_GROUP;
+    const int gsize = min(MERGE_GROUP, nsplit_here - grp * MERGE_GROUP);
+    const size_t rk = (size_t)r * KV + kv_h;
+    if (!take_last_ticket(a.tickets + a.batch * KV + rk * a.max_groups + grp, gsize, sm.flag)) return;
+    float* scratch = sm.stages;  // the ring is idle from here on
+    if (ngroups == 1) {
+        merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, 0, nsplit_here, r, kv_h, H, scratch, true, a.out,
+                                          nullptr, nullptr, 0, 0);
+        return;
     }
-    __syncthreads();
-    if (!*sm.flag) return;
-    __threadfence();
-    for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
-        const int g = e / HD, d = e - g * HD;
-        const int h = kv_h * G + g;
-        const size_t p0 = ((size_t)r * H + h) * a.max_splits;
-        float M = -INFINITY;
-        for (int s = 0; s < nsplit_here; ++s) M = fmaxf(M, __ldcg(a.part_ml + (p0 + s) * 2));
-        float L = 0.0f, acc = 0.0f;
-        for (int s = 0; s < nsplit_here; ++s) {
-            const float w = exp2f((__ldcg(a.part_ml + (p0 + s) * 2) - M) * LOG2E);
-            L = fmaf(w, __ldcg(a.part_ml + (p0 + s) * 2 + 1), L);
-            acc = fmaf(w, __ldcg(a.part_o + (p0 + s) * HD + d), acc);
-        }
-        a.out[((size_t)r * H + h) * HD + d] = acc / L;
-    }
+    merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, grp * MERGE_GROUP, gsize, r, kv_h, H, scratch, false,
+                                      nullptr, a.part2_o, a.part2_ml, a.max_groups, grp);
+    if (!take_last_ticket(a.tickets + rk, ngroups, sm.flag)) return;
+    merge_partials<HD, G, C::THREADS>(a.part2_o, a.part2_ml, a.max_groups, 0, ngroups, r, kv_h, H, scratch, true, a.out,
+                                      nullptr, nullptr, 0, 0);
 }
 
 template <class K>
@@ -708,6 +787,8 @@ int splitk_ctas_per_sm(const HeadShape& hs) {
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits) {
     return (size_t)rows * hs.num_heads * max_splits * (hs.head_dim + 2);
 }
+
+int fused_merge_groups(int max_splits) { return (max_splits + MERGE_GROUP - 1) / MERGE_GROUP; }
 
 cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s) {
     if (a.batch * a.T == 0) return cudaSuccess;

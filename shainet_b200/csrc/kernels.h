@@ -80,9 +80,12 @@ struct FusedArgs {
     float scale;
     float* part_o;         // [batch, num_heads, max_splits, head_dim]
     float* part_ml;        // [batch, num_heads, max_splits, 2]
-    unsigned* tickets;     // [batch, num_kv_heads], zero between launches
+    float* part2_o;        // [batch, num_heads, max_groups, head_dim]: merged groups of splits
+    float* part2_ml;       // [batch, num_heads, max_groups, 2]
+    unsigned* tickets;     // [batch*num_kv_heads] group-level + [batch*num_kv_heads*max_groups] split-level, zero between launches
     int chunk_rows;
     int max_splits;
+    int max_groups;
     int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
     AttnStatus* status;
 };
@@ -99,6 +102,7 @@ bool splitk_supported(const HeadShape& hs);
 int splitk_tile_rows(const HeadShape& hs);
 int splitk_ctas_per_sm(const HeadShape& hs);
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits);
+int fused_merge_groups(int max_splits);
 cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s);
 // Fused norm/RoPE/append + split-K decode + split merge, launched with
 // programmatic stream serialization.
