@@ -1,0 +1,95 @@
+# Patch of SHAInet::LlamaBlock (src/shainet/transformer/llama_block.cr) that routes
+# the cached attention through libshainet_attn.  Public API is unchanged:
+# LlamaBlock.new(...), #forward, #forward_cached, #clear_cache!, #to_gpu!,
+# #finalize and every property keep their signatures.  Only the private
+# attention_cached_cpu / gpu_attention? / clear_cache! / finalize bodies change;
+# attention_heads_gpu, ensure_gpu_cache!, grow_dev_buf and the @@gpu_* class
+# variables (llama_block.cr:57-68, 407-479, 497-530) are no longer needed.
+#
+# Not compiled here (no Crystal compiler on the build image); it is the change a
+# maintainer would make, written against the reference's own code.
+require "./shainet_attn"
+
+module SHAInet
+  class LlamaBlock < MatrixLayer
+    @attn_kv : LibShainetAttn::Kv = Pointer(Void).null.as(LibShainetAttn::Kv)
+    @attn_params_dirty : Bool = true
+
+    # Call after changing rope_theta / rope_freqs / q_norm / k_norm / b_q / b_k / b_v
+    # (the loader sets them after construction, hf_loader.cr:321-373).
+    def attn_params_changed!
+      @attn_params_dirty = true
+    end
+
+    private def attn_kv : LibShainetAttn::Kv
+      if @attn_kv.null?
+        kv = Pointer(Void).null.as(LibShainetAttn::Kv)
+        AttnB200.check LibShainetAttn.kv_create(AttnB200.ctx, pointerof(kv), @num_heads, @num_kv_heads, @head_dim, 256)
+        @attn_kv = kv
+        @attn_params_dirty = true
+      end
+      if @attn_params_dirty
+        # inv_freq stays computed by Crystal (llama_block.cr:669-675), so rope_theta,
+        # rope_freqs and LLaMA-3 scaling keep their exact semantics.
+        half = @head_dim // 2
+        freqs = Array(Float32).new(half) { |i| inv_freq(i) }
+        AttnB200.check LibShainetAttn.kv_set_rope(@attn_kv, freqs.to_unsafe, half)
+        qn = @q_norm.try(&.to_unsafe) || Pointer(Float32).null
+        kn = @k_norm.try(&.to_unsafe) || Pointer(Float32).null
+        AttnB200.check LibShainetAttn.kv_set_qk_norm(@attn_kv, qn, kn, @qk_norm_eps)
+        bq = @b_q.try(&.to_unsafe) || Pointer(Float32).null
+        bk = @b_k.try(&.to_unsafe) || Pointer(Float32).null
+        bv = @b_v.try(&.to_unsafe) || Pointer(Float32).null
+        AttnB200.check LibShainetAttn.kv_set_bias(@attn_kv, bq, bk, bv)
+        @attn_params_dirty = false
+      end
+      @attn_kv
+    end
+
+    def clear_cache!
+      @k_cache.each(&.clear)
+      @v_cache.each(&.clear)
+      @cache_len = 0
+      LibShainetAttn.kv_reset(@attn_kv) unless @attn_kv.null?
+    end
+
+    def finalize
+      LibShainetAttn.kv_destroy(@attn_kv) unless @attn_kv.null?
+    end
+
+    private def gpu_attention? : Bool
+      return false if force_cpu_attention?
+      avail = @gpu_attn_avail
+      if avail.nil?
+        avail = !ENV["SHAINET_CPU_ATTENTION"]? && AttnB200.available?
+        @gpu_attn_avail = avail
+      end
+      avail
+    end
+
+    # Replaces llama_block.cr:246-299.  The projections stay where they are; bias,
+    # QK-norm, RoPE, the cache append and the attention all happen in one library
+    # call on the raw projection outputs.
+    private def attention_cached_cpu(x : SimpleMatrix) : SimpleMatrix
+      return attention_cached_host_reference(x) unless gpu_attention?
+      new_tokens = x.rows
+      scale = (1.0 / Math.sqrt(@head_dim.to_f64)).to_f32
+      q_full = gpu_matmul(x, @w_q)
+      k_new = gpu_matmul(x, @w_k)
+      v_new = gpu_matmul(x, @w_v)
+      output = SimpleMatrix.new(new_tokens, @q_dim)
+      AttnB200.check LibShainetAttn.forward_host(AttnB200.ctx, attn_kv, q_full.data.to_unsafe, k_new.data.to_unsafe,
+        v_new.data.to_unsafe, output.data.to_unsafe, new_tokens, scale, 0_u32)
+      @cache_len += new_tokens
+      gpu_matmul(output, @w_o)
+    end
+
+    # The reference's original host path (bias, QK-norm, K-RoPE + host append,
+    # attention_heads_cpu), kept verbatim under this name for force_cpu_attention
+    # and SHAINET_CPU_ATTENTION=1; body = llama_block.cr:246-299 with the
+    # `if gpu_attention?` branch removed.
+    private def attention_cached_host_reference(x : SimpleMatrix) : SimpleMatrix
+      previous_def_body_of_attention_cached_cpu(x)
+    end
+  end
+end

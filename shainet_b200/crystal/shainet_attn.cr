@@ -1,0 +1,71 @@
+# Crystal binding of libshainet_attn.so (C ABI: include/shainet_attn.h).
+#
+# Link-time binding (no dlopen): build with
+#   crystal build -Denable_cuda --link-flags "-L<dir of libshainet_attn.so> -lshainet_attn" ...
+# This file is what a SHAInet maintainer would add under src/shainet/; it has
+# not been compiled here (no Crystal compiler on the build image).
+module SHAInet
+  @[Link("shainet_attn")]
+  lib LibShainetAttn
+    type Ctx = Void*
+    type Kv = Void*
+
+    fun version = shainet_attn_version : Int32
+    fun device_count = shainet_attn_device_count : Int32
+    fun last_error = shainet_attn_last_error : UInt8*
+
+    fun ctx_create = shainet_attn_ctx_create(out_ctx : Ctx*, device : Int32) : Int32
+    fun ctx_destroy = shainet_attn_ctx_destroy(ctx : Ctx) : Int32
+    fun ctx_sync = shainet_attn_ctx_sync(ctx : Ctx) : Int32
+
+    fun kv_create = shainet_attn_kv_create(ctx : Ctx, out_kv : Kv*, num_heads : Int32, num_kv_heads : Int32,
+                                           head_dim : Int32, initial_capacity : Int32) : Int32
+    fun kv_destroy = shainet_attn_kv_destroy(kv : Kv) : Int32
+    fun kv_reset = shainet_attn_kv_reset(kv : Kv) : Int32
+    fun kv_truncate = shainet_attn_kv_truncate(kv : Kv, len : Int32) : Int32
+    fun kv_len = shainet_attn_kv_len(kv : Kv) : Int32
+    fun kv_capacity = shainet_attn_kv_capacity(kv : Kv) : Int32
+    fun kv_reserve = shainet_attn_kv_reserve(kv : Kv, total_len : Int32) : Int32
+    fun kv_set_rope_theta = shainet_attn_kv_set_rope_theta(kv : Kv, theta : Float64) : Int32
+    fun kv_set_rope = shainet_attn_kv_set_rope(kv : Kv, inv_freq : Float32*, half : Int32) : Int32
+    fun kv_set_qk_norm = shainet_attn_kv_set_qk_norm(kv : Kv, q_w : Float32*, k_w : Float32*, eps : Float64) : Int32
+    fun kv_set_bias = shainet_attn_kv_set_bias(kv : Kv, b_q : Float32*, b_k : Float32*, b_v : Float32*) : Int32
+    fun kv_export = shainet_attn_kv_export(kv : Kv, k : Float32*, v : Float32*, len : Int32) : Int32
+    fun kv_import = shainet_attn_kv_import(kv : Kv, k : Float32*, v : Float32*, len : Int32) : Int32
+
+    fun forward_host = shainet_attn_forward_host(ctx : Ctx, kv : Kv, q : Float32*, k_new : Float32*, v_new : Float32*,
+                                                 out_ptr : Float32*, new_tokens : Int32, scale : Float32,
+                                                 flags : UInt32) : Int32
+    fun forward_dev = shainet_attn_forward_dev(ctx : Ctx, kv : Kv, q : Float32*, k_new : Float32*, v_new : Float32*,
+                                               out_ptr : Float32*, new_tokens : Int32, scale : Float32, flags : UInt32,
+                                               stream : Void*) : Int32
+  end
+
+  # Thin, exception-raising wrapper in the style of SHAInet::CUDA (src/shainet/cuda.cr).
+  module AttnB200
+    extend self
+
+    @@ctx : LibShainetAttn::Ctx = Pointer(Void).null.as(LibShainetAttn::Ctx)
+
+    # Replaces CUDA.fully_available? for the attention path (cuda.cr:778-780).
+    def available? : Bool
+      LibShainetAttn.device_count > 0
+    end
+
+    def check(rc : Int32)
+      raise "libshainet_attn: #{String.new(LibShainetAttn.last_error)}" if rc < 0
+      rc
+    end
+
+    # One context per process, created on first use: it stands for the class-level
+    # @@gpu_staging / @@gpu_attn_out / @@gpu_attn_ws scratch (llama_block.cr:57-68).
+    def ctx : LibShainetAttn::Ctx
+      if @@ctx.null?
+        c = Pointer(Void).null.as(LibShainetAttn::Ctx)
+        check LibShainetAttn.ctx_create(pointerof(c), 0)
+        @@ctx = c
+      end
+      @@ctx
+    end
+  end
+end
