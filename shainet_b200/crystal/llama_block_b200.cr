@@ -71,7 +71,10 @@ module SHAInet
     # QK-norm, RoPE, the cache append and the attention all happen in one library
     # call on the raw projection outputs.
     private def attention_cached_cpu(x : SimpleMatrix) : SimpleMatrix
-      return attention_cached_host_reference(x) unless gpu_attention?
+      # Without a device (or with force_cpu_attention / SHAINET_CPU_ATTENTION=1) the
+      # reference's own definition runs: bias, QK-norm, host K-RoPE + append,
+      # attention_heads_cpu.
+      return previous_def unless gpu_attention?
       new_tokens = x.rows
       scale = (1.0 / Math.sqrt(@head_dim.to_f64)).to_f32
       q_full = gpu_matmul(x, @w_q)
@@ -82,14 +85,6 @@ module SHAInet
         v_new.data.to_unsafe, output.data.to_unsafe, new_tokens, scale, 0_u32)
       @cache_len += new_tokens
       gpu_matmul(output, @w_o)
-    end
-
-    # The reference's original host path (bias, QK-norm, K-RoPE + host append,
-    # attention_heads_cpu), kept verbatim under this name for force_cpu_attention
-    # and SHAINET_CPU_ATTENTION=1; body = llama_block.cr:246-299 with the
-    # `if gpu_attention?` branch removed.
-    private def attention_cached_host_reference(x : SimpleMatrix) : SimpleMatrix
-      previous_def_body_of_attention_cached_cpu(x)
     end
   end
 end
