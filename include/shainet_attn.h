@@ -147,6 +147,29 @@ void kv_cache_append_f32(const float* staging, float* kc, float* vc, int new_tok
 void attention_kv_f32(const float* q, const float* kc, const float* vc, float* out, float* ws, int new_tokens,
                       int start_pos, int num_heads, int heads_per_kv, int head_dim, int capacity, float scale);
 
+/* ---- decode without allocating.  This entry has no counterpart in the
+ * reference.  It is for hosts that cannot let a library allocate device memory:
+ * a server that gave the GPU's whole memory budget to its own pool at start-up
+ * (a cudaMalloc made later from inside a library may fail or upset that plan),
+ * or a latency-critical token loop where cudaMalloc/cudaFree are unwelcome
+ * because they synchronise the whole device.  It computes what
+ * attention_kv_f32 computes for new_tokens == 1 - q [num_heads*head_dim] already
+ * rotated, the new K/V row already appended at start_pos, visible rows
+ * 0..start_pos - on the caller's stream, and returns a status like the other
+ * shainet_attn_* calls.  Its split partials live in a fixed 4 MiB array inside
+ * the library image (held by every GPU that loads the library, until exit)
+ * instead of a buffer grown on demand; it calls no cudaMalloc, cudaFree or
+ * allocating library routine.  Limits: head_dim 64 or 128; 1/2/4/8/16 query
+ * heads per kv head; num_heads * splits * (head_dim + 2) <= 1,048,576 floats
+ * (splits is the planner's count, at most two CTAs per SM spread over the kv
+ * heads) - anything larger is refused with SHAINET_ATTN_E_UNSUPPORTED.  All calls
+ * share the array: calls that overlap on the GPU race and must be ordered by
+ * the caller.  The first call made with a given device current looks up the
+ * array's device address; make that call before any stream capture starts. */
+int shainet_attn_decode_noalloc(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                float* out_dev, int start_pos, int num_heads, int heads_per_kv, int head_dim,
+                                int capacity, float scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

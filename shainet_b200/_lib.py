@@ -46,6 +46,7 @@ SIGNATURES = {
     "shainet_attn_forward_dev": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, C.c_float, C.c_uint, _P]),
     "shainet_attn_forward_batched_dev": (C.c_int, [_P, C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_float,
                                                    C.c_uint, _P]),
+    "shainet_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _P]),
     "kv_cache_append_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "attention_kv_f32": (None, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                 C.c_float]),

@@ -413,6 +413,10 @@ int forward_device(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, c
 
 }  // namespace
 
+namespace shainet {
+void set_last_error_message(const char* msg) { g_last_error = msg ? msg : ""; }
+}  // namespace shainet
+
 extern "C" {
 
 int shainet_attn_version(void) { return SHAINET_ATTN_VERSION; }

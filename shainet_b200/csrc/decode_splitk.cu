@@ -34,6 +34,7 @@
 // All waits are bounded (see mbar_wait); a timed-out wait records a status
 // word and the kernel unwinds.
 #include <math.h>
+#include <stdio.h>
 #include <type_traits>
 #include "kernels.h"
 
@@ -805,3 +806,130 @@ cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s) {
 }
 
 }  // namespace shainet
+
+// ---------------------------------------------------------------------------
+// Decode without any allocation.
+//
+// Some hosts cannot let a library allocate device memory on their behalf: an
+// inference server that has handed the GPU's whole memory budget to its own
+// pool at start-up (a later cudaMalloc from inside a library can fail, or
+// fragment what the pool planned for), and a latency-critical token loop in
+// which cudaMalloc/cudaFree are unwelcome because they synchronise the whole
+// device and stall every stream.  For them this entry point runs the plain
+// split-K decode kernel and its merge kernel with the per-split partials kept
+// in a fixed array that is part of the library image instead of in a buffer the
+// context grows on demand.  It calls no cudaMalloc, no cudaFree and no library
+// routine that allocates.
+//
+// Limits and rules, all consequences of the array being one fixed global:
+//  * it is NOALLOC_SCRATCH_FLOATS floats (4 MiB) and every GPU whose context
+//    loads this library holds it until the process exits;
+//  * a call needs num_heads * splits * (head_dim + 2) floats of it, where
+//    splits is the planner's count (at most two CTAs per SM spread over the kv
+//    heads); a shape that needs more is refused with SHAINET_ATTN_E_UNSUPPORTED;
+//  * all calls share the array and it keeps whatever the last call left there.
+//    Nothing in it has to start at zero: every entry the merge kernel reads was
+//    written by the split kernel of the same call.  For the same reason two
+//    calls that overlap on the GPU (different streams, no ordering between
+//    them) race on it and give wrong results; order them;
+//  * the address of the array is looked up once per device, by the first call
+//    made with that device current (cudaGetSymbolAddress; the symbol's name is
+//    only a host-side handle, never a device address).  Make that first call
+//    before any stream capture begins.
+// ---------------------------------------------------------------------------
+namespace shainet {
+namespace {
+
+constexpr size_t NOALLOC_SCRATCH_FLOATS = size_t(1) << 20;
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+
+struct NoAllocDevice {
+    float* scratch = nullptr;  // device address of g_noalloc_scratch on this device
+    int sm_count = 0;
+};
+NoAllocDevice g_noalloc_dev[64];
+
+}  // namespace
+}  // namespace shainet
+
+extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
+                                            float* out_dev, int start_pos, int num_heads, int heads_per_kv, int head_dim,
+                                            int capacity, float scale, void* stream) {
+    using namespace shainet;
+    char msg[256];
+    if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) {
+        set_last_error_message("shainet_attn_decode_noalloc: null pointer");
+        return -1;  // SHAINET_ATTN_E_INVALID
+    }
+    if (num_heads <= 0 || heads_per_kv <= 0 || num_heads % heads_per_kv != 0 || start_pos < 0 || capacity <= start_pos) {
+        set_last_error_message("shainet_attn_decode_noalloc: bad head counts, or start_pos outside the cache capacity");
+        return -1;
+    }
+    if (((reinterpret_cast<uintptr_t>(q_dev) | reinterpret_cast<uintptr_t>(k_cache_dev) | reinterpret_cast<uintptr_t>(v_cache_dev) |
+          reinterpret_cast<uintptr_t>(out_dev)) & 15u) != 0) {
+        set_last_error_message("shainet_attn_decode_noalloc: device pointers must be 16-byte aligned");
+        return -1;
+    }
+    const HeadShape hs{num_heads, num_heads / heads_per_kv, head_dim};
+    if (!splitk_supported(hs)) {
+        set_last_error_message("shainet_attn_decode_noalloc: needs head_dim 64 or 128 and 1, 2, 4, 8 or 16 query heads per kv head");
+        return -4;  // SHAINET_ATTN_E_UNSUPPORTED
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_last_error_message("shainet_attn_decode_noalloc: no usable current device");
+        return -2;  // SHAINET_ATTN_E_CUDA
+    }
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    if (!nd.scratch) {
+        // One-time set-up for this device: resolve the array's device address.
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            snprintf(msg, sizeof msg, "shainet_attn_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
+            set_last_error_message(msg);
+            return -2;
+        }
+        nd.scratch = ptr;
+    }
+    AttnArgs a{};
+    a.q_rot = q_dev;
+    a.out = out_dev;
+    a.seqs.one = SeqDesc{const_cast<float*>(k_cache_dev), const_cast<float*>(v_cache_dev), start_pos, capacity};
+    a.seqs.many = nullptr;
+    a.batch = 1;
+    a.T = 1;
+    a.hs = hs;
+    a.scale = scale;
+    a.status = nullptr;
+    const int visible = start_pos + 1;
+    const int tw = splitk_tile_rows(hs);
+    const long long ctas = (long long)nd.sm_count * splitk_ctas_per_sm(hs);
+    long long chunk = ((long long)visible * hs.num_kv_heads + ctas - 1) / ctas;
+    if (chunk < 4ll * tw) chunk = 4ll * tw;
+    chunk = (chunk + tw - 1) / tw * tw;
+    a.chunk_rows = (int)chunk;
+    a.max_splits = (int)((visible + chunk - 1) / chunk);
+    const size_t need = splitk_scratch_floats(hs, 1, a.max_splits);
+    if (need > NOALLOC_SCRATCH_FLOATS) {
+        snprintf(msg, sizeof msg,
+                 "shainet_attn_decode_noalloc: %d heads x %d splits x (head_dim + 2) = %zu floats exceeds the fixed scratch of %zu floats",
+                 num_heads, a.max_splits, need, NOALLOC_SCRATCH_FLOATS);
+        set_last_error_message(msg);
+        return -4;
+    }
+    a.part_o = nd.scratch;
+    a.part_ml = nd.scratch + (size_t)num_heads * a.max_splits * head_dim;
+    e = launch_attn_splitk(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        snprintf(msg, sizeof msg, "shainet_attn_decode_noalloc: launch failed: %s", cudaGetErrorString(e));
+        set_last_error_message(msg);
+        return -2;
+    }
+    return 0;
+}
+

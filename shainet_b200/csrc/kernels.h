@@ -112,6 +112,9 @@ cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s);
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
                                unsigned long long seed, cudaStream_t s);
 
+// Sets the calling thread's message for shainet_attn_last_error().
+void set_last_error_message(const char* msg);
+
 // Drop-in bodies for the reference's two exported kernels.
 cudaError_t launch_ref_append(const float* staging, float* kc, float* vc, int new_tokens, int start_pos,
                               int num_kv_heads, int head_dim, int capacity, cudaStream_t s);
