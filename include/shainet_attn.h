@@ -122,7 +122,8 @@ int shainet_attn_forward_host(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const 
                               const float* v_new, float* out, int new_tokens, float scale, unsigned flags);
 
 /* Same with device pointers (16-byte aligned) on a caller stream (a
- * cudaStream_t passed as void*; NULL = the context's stream).  Asynchronous. */
+ * cudaStream_t passed as void*; NULL = the context's own stream, so the legacy
+ * default stream has to be named as cudaStreamLegacy).  Asynchronous. */
 int shainet_attn_forward_dev(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q_dev, const float* k_new_dev,
                              const float* v_new_dev, float* out_dev, int new_tokens, float scale, unsigned flags,
                              void* stream);

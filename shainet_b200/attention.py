@@ -30,6 +30,18 @@ def _opt(a):
     return (None, None) if a is None else (lambda x: (x, _fp(x)))(_f32(a))
 
 
+CUDA_STREAM_LEGACY = 1  # cudaStreamLegacy: the handle that names the legacy default stream explicitly
+
+
+def _stream_arg(stream):
+    """None -> NULL (the context's own stream); 0 -> the legacy default stream,
+    which has to be named by its explicit handle because NULL is taken; any
+    other integer is a cudaStream_t."""
+    if stream is None:
+        return None
+    return C.c_void_p(CUDA_STREAM_LEGACY if stream == 0 else stream)
+
+
 def device_count() -> int:
     return _lib.load().shainet_attn_device_count()
 
@@ -179,19 +191,19 @@ class LlamaAttention:
                                                    T, self.scale, flags))
         return out
 
-    def forward_cached_dev(self, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, new_tokens: int, stream: int = 0,
+    def forward_cached_dev(self, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, new_tokens: int, stream=None,
                            flags: int = 0):
-        """Device pointers (ints) on a caller stream; asynchronous."""
+        """Device pointers (ints) on a caller stream (see _stream_arg); asynchronous."""
         check(self.ctx.L.shainet_attn_forward_dev(self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, new_tokens,
-                                                  self.scale, flags, stream or None))
+                                                  self.scale, flags, _stream_arg(stream)))
 
     def close(self):
         self.cache.close()
 
 
 def forward_batched_dev(ctx: AttnContext, caches, q_ptr: int, k_ptr: int, v_ptr: int, out_ptr: int, scale: float,
-                        stream: int = 0, flags: int = 0):
+                        stream=None, flags: int = 0):
     """One decode token for every cache in ``caches`` (lock step), one launch set."""
     arr = (C.c_void_p * len(caches))(*[c.h for c in caches])
     check(ctx.L.shainet_attn_forward_batched_dev(ctx.h, arr, len(caches), q_ptr, k_ptr, v_ptr, out_ptr, scale, flags,
-                                                 stream or None))
+                                                 _stream_arg(stream)))
