@@ -37,6 +37,13 @@ extern "C" {
 #define SHAINET_ATTN_F_SPLITK 2u   /* force the split-K decode kernel (error if unsupported) */
 #define SHAINET_ATTN_F_TENSOR 4u   /* force the tcgen05 prefill kernel (error if unsupported) */
 #define SHAINET_ATTN_F_UNFUSED 8u  /* decode as three launches (RoPE/append, split-K, merge) instead of one */
+/* The caller vouches that q/k_new/v_new (device-pointer entries only) were
+ * complete before the kernel launched immediately before this call on the same
+ * stream began, i.e. they are not that kernel's output.  The fused decode
+ * kernel then starts its RoPE/norm prologue and its streaming while that
+ * kernel is still draining, and only waits for it before touching the scratch
+ * the two share.  Without the flag nothing is assumed. */
+#define SHAINET_ATTN_F_INPUTS_READY 16u
 
 typedef struct shainet_attn_ctx shainet_attn_ctx;
 typedef struct shainet_attn_kv shainet_attn_kv;

@@ -5,4 +5,4 @@ this package is its host-side mirror of the reference's ``LlamaBlock`` attention
 interface.  Importing does not load the library; the first use does, and fails
 loudly if it has not been built."""
 from .attention import (AttnContext, KVCache, LlamaAttention, ShainetAttnError, default_scale, device_count,  # noqa: F401
-                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED)
+                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY)

@@ -375,6 +375,7 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     // A fused kernel may start while the previous fused kernel still runs; that
     // one can be appending the newest row of this very cache.
     f.unsafe_tail = ctx->last_fused ? 1 : 0;
+    f.inputs_ready = (flags & SHAINET_ATTN_F_INPUTS_READY) ? 1 : 0;
     std::pair<cudaEvent_t, cudaEvent_t> ev{};
     if (ctx->timing) {
         if (!ctx->ev_pool.empty()) {

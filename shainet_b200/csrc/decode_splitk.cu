@@ -108,11 +108,14 @@ struct SK {
     static constexpr int THREADS = (NW + 1) * 32;
     static constexpr int CTAS_PER_SM = CTAS_;
     static constexpr bool MATH = MATH_;
-    // fused kernel extras: rotated q of the group, and a one-batch tile for the new row
-    static constexpr int QS_FLOATS = G * HD;
+    // fused kernel extras: rotated q of the group (rows padded by 4 floats so that
+    // lanes walking different rows hit different banks), a one-batch tile for the
+    // new k row, the new v row, per-row inverse RMS values
+    static constexpr int QS_STRIDE = HD + 4;
+    static constexpr int QS_FLOATS = G * QS_STRIDE;
     static constexpr int XK_FLOATS = BR * HD;
     static constexpr int XV_FLOATS = HD;
-    static constexpr int EXTRA_FLOATS = QS_FLOATS + XK_FLOATS + XV_FLOATS + 8;
+    static constexpr int EXTRA_FLOATS = QS_FLOATS + XK_FLOATS + XV_FLOATS + 8 + 24;
     static constexpr int FIXED_BYTES = (NW * WARP_SCRATCH + EXTRA_FLOATS) * 4 + 2 * SK_MAX_STAGES * 8;
     static constexpr int NS_RAW = (SMEM_KB_ * 1024 - FIXED_BYTES) / (STAGE_FLOATS * 4);
     static constexpr int NS_CAP = NS_RAW > SK_MAX_STAGES ? SK_MAX_STAGES : NS_RAW;
@@ -135,6 +138,7 @@ struct Smem {
     float* xk;   // [BR][HD], row 0 = the new rotated k row (fused kernel, last split)
     float* xv;   // [HD] the new v row
     int* flag;   // ticket broadcast
+    float* inv;  // [G + 1] inverse RMS of the q rows and of the new k row
     uint64_t* full_bar;
     uint64_t* empty_bar;
     __device__ explicit Smem(unsigned char* raw) {
@@ -144,7 +148,8 @@ struct Smem {
         xk = qs + C::QS_FLOATS;
         xv = xk + C::XK_FLOATS;
         flag = reinterpret_cast<int*>(xv + C::XV_FLOATS);
-        full_bar = reinterpret_cast<uint64_t*>(xv + C::XV_FLOATS + 8);
+        inv = xv + C::XV_FLOATS + 8;
+        full_bar = reinterpret_cast<uint64_t*>(xv + C::XV_FLOATS + 8 + 24);
         empty_bar = full_bar + SK_MAX_STAGES;
     }
 };
@@ -184,12 +189,12 @@ struct WarpState {
 // q of the G heads, this lane's 4*CPL columns of each, as packed pairs
 // (columns 0-1 and 2-3 of every 16-byte chunk).  qrow: [G][HD], global or shared.
 template <int HD, int G, class C>
-__device__ __forceinline__ void load_q(ulonglong2 (&q)[G][C::CPL], const float* qrow, int i16) {
+__device__ __forceinline__ void load_q(ulonglong2 (&q)[G][C::CPL], const float* qrow, int row_stride, int i16) {
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int c = 0; c < C::CPL; ++c)
-            q[g][c] = *reinterpret_cast<const ulonglong2*>(qrow + (size_t)g * HD + (c * 16 + i16) * 4);
+            q[g][c] = *reinterpret_cast<const ulonglong2*>(qrow + (size_t)g * row_stride + (c * 16 + i16) * 4);
 }
 
 // One warp tile: `nrows` valid rows of K (ks) and V (vs) in shared memory.
@@ -404,7 +409,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_splitk_kernel
         if (lane == 0) produce_tiles<HD, C>(sm, kbase, vbase, rows, 0, ntiles, a.status);
     } else {
         ulonglong2 q[G][C::CPL];
-        load_q<HD, G, C>(q, a.q_rot + ((size_t)r * H + (size_t)kv_h * G) * HD, lane & 15);
+        load_q<HD, G, C>(q, a.q_rot + ((size_t)r * H + (size_t)kv_h * G) * HD, HD, lane & 15);
         consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
         finish_warp<HD, G, C>(st);
     }
@@ -458,69 +463,85 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(AttnArgs a) {
 // Merge of `count` partials (max, sum, unnormalised output) of the G heads of
 // (row r, kv head kv_h), entries first..first+count-1 of a [row][head][stride]
 // table, by the whole CTA.  `final` writes the normalised output row; otherwise
-// the merged partial goes to entry dst_index of a second table.  `scratch` is
-// shared memory for 2*G*count + 2*G floats.
-constexpr int MERGE_GROUP = 8;  // splits merged by the last CTA of each group
+// the merged partial goes to entry dst_index of a second table.
+#ifndef SK_MERGE_GROUP
+#define SK_MERGE_GROUP 8
+#endif
+constexpr int MERGE_GROUP = SK_MERGE_GROUP;  // splits merged by the last CTA of each group
 
 template <int HD, int G, int THREADS>
 __device__ void merge_partials(const float* po, const float* pml, size_t stride, int first, int count, int r, int kv_h,
-                               int H, float* scratch, bool final, float* out, float* dst_o, float* dst_ml,
-                               size_t dst_stride, int dst_index) {
-    float* w = scratch;                 // [G][count]: max, then weight
-    float* lsum = w + G * count;        // [G][count]
-    float* Ms = lsum + G * count;       // [G]
-    float* Ls = Ms + G;                 // [G]
-    const size_t head0 = (size_t)r * H + (size_t)kv_h * G;
-    for (int idx = threadIdx.x; idx < G * count; idx += THREADS) {
-        const int g = idx / count, s = idx - g * count;
-        const size_t e = (head0 + g) * stride + first + s;
-        w[idx] = __ldcg(pml + 2 * e);
-        lsum[idx] = __ldcg(pml + 2 * e + 1);
-    }
-    __syncthreads();
-    if (threadIdx.x < G) {
-        const int g = threadIdx.x;
-        float M = -INFINITY;
-        for (int s = 0; s < count; ++s) M = fmaxf(M, w[g * count + s]);
-        float L = 0.0f;
-        for (int s = 0; s < count; ++s) {
-            const float wt = exp2f((w[g * count + s] - M) * LOG2E);
-            w[g * count + s] = wt;
-            L = fmaf(wt, lsum[g * count + s], L);
-        }
-        Ms[g] = M;
-        Ls[g] = L;
-    }
-    __syncthreads();
+                               int H, bool final, float* out, float* dst_o, float* dst_ml, size_t dst_stride,
+                               int dst_index) {
+    // Every thread owns up to NT (head, four columns) tasks and walks the partials
+    // in rounds of 8: the (max, sum) pairs and the output quads of a round are
+    // all requested, for all of the thread's tasks, before any is used, so a
+    // round costs one L2 latency.  Weights are recomputed per thread instead of
+    // being staged through shared memory.
     constexpr int D4 = HD / 4;
-    for (int task = threadIdx.x; task < G * D4; task += THREADS) {
-        const int g = task / D4, d4 = task - g * D4;
-        const float4* src = reinterpret_cast<const float4*>(po + ((head0 + g) * stride + first) * HD) + d4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < count; s0 += 8) {
-            float4 v[8];
+    constexpr int NT = (G * D4 + THREADS - 1) / THREADS;
+    const size_t head0 = (size_t)r * H + (size_t)kv_h * G;
+    float M[NT], L[NT];
+    float4 acc[NT];
+    const float2* ml[NT];
+    const float4* src[NT];
+    bool on[NT];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                v[k] = (s0 + k < count) ? __ldcg(src + (size_t)(s0 + k) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < NT; ++t) {
+        const int task = threadIdx.x + t * THREADS;
+        on[t] = task < G * D4;
+        const int g = on[t] ? task / D4 : 0, d4 = on[t] ? task - g * D4 : 0;
+        const size_t e0 = (head0 + g) * stride + first;
+        ml[t] = reinterpret_cast<const float2*>(pml) + e0;
+        src[t] = reinterpret_cast<const float4*>(po + e0 * HD) + d4;
+        M[t] = -INFINITY;
+        L[t] = 0.0f;
+        acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s0 = 0; s0 < count; s0 += 8) {
+        float2 mv[NT][8];
+        float4 v[NT][8];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                const float wt = (s0 + k < count) ? w[g * count + s0 + k] : 0.0f;
-                acc.x = fmaf(wt, v[k].x, acc.x);
-                acc.y = fmaf(wt, v[k].y, acc.y);
-                acc.z = fmaf(wt, v[k].z, acc.z);
-                acc.w = fmaf(wt, v[k].w, acc.w);
+                const bool in = on[t] && s0 + k < count;
+                mv[t][k] = in ? __ldcg(ml[t] + s0 + k) : make_float2(-INFINITY, 0.f);
+                v[t][k] = in ? __ldcg(src[t] + (size_t)(s0 + k) * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float Mc = M[t];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) Mc = fmaxf(Mc, mv[t][k].x);
+            const float resc = (M[t] == -INFINITY) ? 0.0f : exp2f((M[t] - Mc) * LOG2E);
+            L[t] *= resc;
+            acc[t].x *= resc; acc[t].y *= resc; acc[t].z *= resc; acc[t].w *= resc;
+            M[t] = Mc;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float wt = (mv[t][k].x == -INFINITY) ? 0.0f : exp2f((mv[t][k].x - Mc) * LOG2E);
+                L[t] = fmaf(wt, mv[t][k].y, L[t]);
+                acc[t].x = fmaf(wt, v[t][k].x, acc[t].x);
+                acc[t].y = fmaf(wt, v[t][k].y, acc[t].y);
+                acc[t].z = fmaf(wt, v[t][k].z, acc[t].z);
+                acc[t].w = fmaf(wt, v[t][k].w, acc[t].w);
             }
         }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        if (!on[t]) continue;
+        const int task = threadIdx.x + t * THREADS;
+        const int g = task / D4, d4 = task - g * D4;
         if (final) {
-            const float inv = 1.0f / Ls[g];
-            *(reinterpret_cast<float4*>(out + (head0 + g) * HD) + d4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            const float inv = 1.0f / L[t];
+            *(reinterpret_cast<float4*>(out + (head0 + g) * HD) + d4) =
+                make_float4(acc[t].x * inv, acc[t].y * inv, acc[t].z * inv, acc[t].w * inv);
         } else {
             const size_t e = (head0 + g) * dst_stride + dst_index;
-            *(reinterpret_cast<float4*>(dst_o + e * HD) + d4) = acc;
-            if (d4 == 0) {
-                dst_ml[2 * e] = Ms[g];
-                dst_ml[2 * e + 1] = Ls[g];
-            }
+            *(reinterpret_cast<float4*>(dst_o + e * HD) + d4) = acc[t];
+            if (d4 == 0) *(reinterpret_cast<float2*>(dst_ml) + e) = make_float2(M[t], L[t]);
         }
     }
 }
@@ -550,23 +571,25 @@ __device__ __forceinline__ bool take_last_ticket(unsigned* ticket, int expected,
 // split-K stream; then the last CTA of each (row, kv head) merges the splits.
 // ---------------------------------------------------------------------------
 
-// One head row (HD floats at `row`, shared memory, already biased): optional
-// RMSNorm with the reference's sequential fp32 sum, then the half-split
-// rotation, in place.  Same arithmetic as prep_append_kernel.
+// Sum of squares of one row in the reference's order: sequential fp32, ascending
+// column, multiply and add each rounded (one lane per row; several rows run in
+// neighbouring lanes), then f32(1 / sqrt(f64(ss / hd) + eps)).
 template <int HD>
-__device__ __forceinline__ void norm_rope_row(float* row, const float* w, const float* inv_freq, double eps, float fpos,
-                                              int lane) {
+__device__ __forceinline__ float inv_rms_sequential(const float* row, double eps) {
+    float ss = 0.0f;
+#pragma unroll 16
+    for (int d = 0; d < HD; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
+    const float mean = __fdiv_rn(ss, (float)HD);
+    return (float)(1.0 / sqrt((double)mean + eps));
+}
+
+// Half-split rotation of one row in place (optionally after scaling by the
+// row's inverse RMS and the norm weight), by one warp.  Same arithmetic as
+// prep_append_kernel.
+template <int HD>
+__device__ __forceinline__ void scale_rope_row(float* row, const float* w, float inv, const float* inv_freq, float fpos,
+                                               int lane) {
     constexpr int half = HD / 2;
-    float inv = 1.0f;
-    if (w) {
-        if (lane == 0) {
-            float ss = 0.0f;
-            for (int d = 0; d < HD; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
-            const float mean = __fdiv_rn(ss, (float)HD);
-            inv = (float)(1.0 / sqrt((double)mean + eps));
-        }
-        inv = __shfl_sync(FULL, inv, 0);
-    }
 #pragma unroll
     for (int i = lane; i < half; i += 32) {
         float x0 = row[i], x1 = row[i + half];
@@ -599,9 +622,11 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const int ntiles = (rows + C::TW - 1) / C::TW;
     // Tiles that end at or below `safe_end` cannot be under construction by the
     // grid that may still be running; they are fetched before waiting for it.
+    // When the caller vouches for the inputs (inputs_ready) the consumers do not
+    // wait either, so every such tile may go out early, not just a ring's worth.
     const int safe_end = start - a.unsafe_tail;
-    int n_early = row0 + rows <= safe_end ? ntiles : max(0, (safe_end - row0) / C::TW);
-    n_early = min(min(n_early, ntiles), C::NS);
+    const int n_safe = min(ntiles, row0 + rows <= safe_end ? ntiles : max(0, (safe_end - row0) / C::TW));
+    const int n_early = a.inputs_ready ? n_safe : min(n_safe, C::NS);
     const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
     const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -619,37 +644,49 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
     } else {
         // ---------------- consumers ----------------
-        grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
+        if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
         const float fpos = (float)start;
-        const int items = G + (owns_new ? 2 : 0);
+        const int items = G + (owns_new ? 2 : 0);   // q rows of the group, then the new k row, then the new v row
+        auto item_row = [&](int it) { return it < G ? sm.qs + it * C::QS_STRIDE : (it == G ? sm.xk : sm.xv); };
+        // (1) raw rows (+ bias) into shared memory
         for (int it = warp; it < items; it += C::NW) {
             const float* src;
             const float* bias;
-            float* row;
             if (it < G) {
                 const int h = kv_h * G + it;
                 src = a.q + ((size_t)r * H + h) * HD;
                 bias = a.b_q ? a.b_q + (size_t)h * HD : nullptr;
-                row = sm.qs + it * HD;
             } else if (it == G) {
                 src = a.k_new + ((size_t)r * KV + kv_h) * HD;
                 bias = a.b_k ? a.b_k + (size_t)kv_h * HD : nullptr;
-                row = sm.xk;
             } else {
                 src = a.v_new + ((size_t)r * KV + kv_h) * HD;
                 bias = a.b_v ? a.b_v + (size_t)kv_h * HD : nullptr;
-                row = sm.xv;
             }
+            float* row = item_row(it);
 #pragma unroll
             for (int d = lane; d < HD; d += 32) {
                 float x = src[d];
                 if (bias) x = __fadd_rn(x, bias[d]);
                 row[d] = x;
             }
-            __syncwarp();
-            if (it <= G) norm_rope_row<HD>(row, it < G ? a.q_norm : a.k_norm, a.inv_freq, a.eps, fpos, lane);
-            __syncwarp();
-            if (it >= G) {  // append to the cache
+        }
+        // (2) per-row inverse RMS, one lane per row (only when a norm weight is set)
+        if (a.q_norm || a.k_norm) {
+            asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");
+            if (warp == 0 && lane <= G && lane < items && (lane < G ? a.q_norm : a.k_norm) != nullptr)
+                sm.inv[lane] = inv_rms_sequential<HD>(item_row(lane), a.eps);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");
+        // (3) scale + rotate q and k rows in place; append k and v to the cache
+        for (int it = warp; it < items; it += C::NW) {
+            float* row = item_row(it);
+            if (it <= G) {
+                const float* w = it < G ? a.q_norm : a.k_norm;
+                scale_rope_row<HD>(row, w, w ? sm.inv[it] : 1.0f, a.inv_freq, fpos, lane);
+                __syncwarp();
+            }
+            if (it >= G) {
                 float* dst = (it == G ? sd.k : sd.v) + ((size_t)kv_h * sd.capacity + start) * HD;
 #pragma unroll
                 for (int d = lane; d < HD; d += 32) dst[d] = row[d];
@@ -657,7 +694,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
         asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");  // consumers only: qs/xk/xv complete
         ulonglong2 q[G][C::CPL];
-        load_q<HD, G, C>(q, sm.qs, lane & 15);
+        load_q<HD, G, C>(q, sm.qs, C::QS_STRIDE, lane & 15);
         consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
         if (owns_new && warp == (ntiles % C::NW)) {
             // the new token's own row, from shared memory (one valid row)
@@ -667,6 +704,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         finish_warp<HD, G, C>(st);
     }
     __syncthreads();  // every issued copy has landed; the ring is free
+    if (a.inputs_ready) grid_dependency_wait();  // the shared scratch below may still be in use by the previous grid
     if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
     __syncthreads();
     const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
@@ -694,17 +732,16 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const int gsize = min(MERGE_GROUP, nsplit_here - grp * MERGE_GROUP);
     const size_t rk = (size_t)r * KV + kv_h;
     if (!take_last_ticket(a.tickets + a.batch * KV + rk * a.max_groups + grp, gsize, sm.flag)) return;
-    float* scratch = sm.stages;  // the ring is idle from here on
     if (ngroups == 1) {
-        merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, 0, nsplit_here, r, kv_h, H, scratch, true, a.out,
-                                          nullptr, nullptr, 0, 0);
+        merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, 0, nsplit_here, r, kv_h, H, true, a.out, nullptr,
+                                          nullptr, 0, 0);
         return;
     }
-    merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, grp * MERGE_GROUP, gsize, r, kv_h, H, scratch, false,
-                                      nullptr, a.part2_o, a.part2_ml, a.max_groups, grp);
+    merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, grp * MERGE_GROUP, gsize, r, kv_h, H, false, nullptr,
+                                      a.part2_o, a.part2_ml, a.max_groups, grp);
     if (!take_last_ticket(a.tickets + rk, ngroups, sm.flag)) return;
-    merge_partials<HD, G, C::THREADS>(a.part2_o, a.part2_ml, a.max_groups, 0, ngroups, r, kv_h, H, scratch, true, a.out,
-                                      nullptr, nullptr, 0, 0);
+    merge_partials<HD, G, C::THREADS>(a.part2_o, a.part2_ml, a.max_groups, 0, ngroups, r, kv_h, H, true, a.out, nullptr,
+                                      nullptr, 0, 0);
 }
 
 template <class K>

@@ -87,6 +87,7 @@ struct FusedArgs {
     int max_splits;
     int max_groups;
     int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
+    int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
     AttnStatus* status;
 };
 

@@ -163,11 +163,16 @@ def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G, fused):
         g.close()
 
 
-def test_back_to_back_decode_without_sync(ctx):
+@pytest.mark.parametrize("inputs_ready", [False, True], ids=["dependent", "inputs_ready"])
+def test_back_to_back_decode_without_sync(ctx, inputs_ready):
     """Asynchronous device-pointer calls queued back to back: a fused kernel may
     start while its predecessor is still appending the previous row of the same
-    cache; two caches are also interleaved on one stream."""
+    cache; two caches are also interleaved on one stream.  With F_INPUTS_READY
+    (the inputs here were uploaded long before) it also computes while the
+    predecessor drains."""
     import torch
+    import shainet_b200 as S
+    flags = S.F_INPUTS_READY if inputs_ready else 0
     rng = np.random.default_rng(808)
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream().cuda_stream
@@ -188,7 +193,7 @@ def test_back_to_back_decode_without_sync(ctx):
             reps = 2 if (t % 5 == 0 and i == 0) else 1     # sometimes the same cache twice in a row
             for _ in range(reps):
                 tq, tk, tv = dins[t][i]
-                g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), outs[t][i].data_ptr(), 1, stream)
+                g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), outs[t][i].data_ptr(), 1, stream, flags)
     torch.cuda.synchronize()
     ctx.sync()
     for t in range(steps):
