@@ -46,6 +46,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 constexpr int SEQ_RING = 8;           // in-flight descriptor uploads of batched decode
 constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
 constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
+constexpr int TENSOR_MIN_T = 64;      // rows per call from which the tensor-core prefill kernel takes over
 
 struct DevBuf {
     float* p = nullptr;
@@ -165,6 +166,10 @@ int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
         cudaFree(nk);
         return fail_cuda(e, "cudaMalloc(v cache)");
     }
+    // Rows past the appended length are read (and masked) by the tensor-core
+    // prefill kernel; they must be finite, so fresh buffers start at zero.
+    CU(cudaMemsetAsync(nk, 0, bytes, s));
+    CU(cudaMemsetAsync(nv, 0, bytes, s));
     if (kv->k && kv->len > 0) {
         const size_t row_bytes = (size_t)kv->len * kv->hs.head_dim * sizeof(float);
         const size_t src_pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
@@ -194,7 +199,7 @@ int check_status(shainet_attn_ctx* ctx) {
     return SHAINET_ATTN_OK;
 }
 
-enum class Kernel { Generic, SplitK };
+enum class Kernel { Generic, SplitK, Tensor };
 
 int ensure_tickets(shainet_attn_ctx* ctx, size_t n, cudaStream_t s) {
     if (ctx->tickets_cap >= n && ctx->tickets) return SHAINET_ATTN_OK;
@@ -211,9 +216,14 @@ int ensure_tickets(shainet_attn_ctx* ctx, size_t n, cudaStream_t s) {
     return SHAINET_ATTN_OK;
 }
 
-int pick_kernel(const HeadShape& hs, int T, unsigned flags, Kernel* out) {
+int pick_kernel(const HeadShape& hs, int batch, int T, unsigned flags, Kernel* out) {
     const bool sk_ok = splitk_supported(hs);
-    if (flags & SHAINET_ATTN_F_TENSOR) return fail(SHAINET_ATTN_E_UNSUPPORTED, "tensor-core prefill kernel not available for this shape");
+    const bool tc_ok = prefill_tc_supported(hs) && batch == 1;
+    if (flags & SHAINET_ATTN_F_TENSOR) {
+        if (!tc_ok) return fail(SHAINET_ATTN_E_UNSUPPORTED, "tensor-core prefill needs head_dim 64 or 128 and a single sequence");
+        *out = Kernel::Tensor;
+        return SHAINET_ATTN_OK;
+    }
     if (flags & SHAINET_ATTN_F_SPLITK) {
         if (!sk_ok) return fail(SHAINET_ATTN_E_UNSUPPORTED, "split-K decode needs head_dim 64/128 and group size 1/2/4/8/16");
         *out = Kernel::SplitK;
@@ -223,7 +233,7 @@ int pick_kernel(const HeadShape& hs, int T, unsigned flags, Kernel* out) {
         *out = Kernel::Generic;
         return SHAINET_ATTN_OK;
     }
-    *out = (sk_ok && T <= SPLITK_MAX_T) ? Kernel::SplitK : Kernel::Generic;
+    *out = (sk_ok && T <= SPLITK_MAX_T) ? Kernel::SplitK : (tc_ok && T >= TENSOR_MIN_T) ? Kernel::Tensor : Kernel::Generic;
     return SHAINET_ATTN_OK;
 }
 
@@ -269,7 +279,7 @@ int run_attention_untimed(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seq
                           long long total_visible, int max_visible, const float* q_rot, float* out, float scale,
                           unsigned flags, cudaStream_t s) {
     Kernel kern;
-    int rc = pick_kernel(hs, T, flags, &kern);
+    int rc = pick_kernel(hs, batch, T, flags, &kern);
     if (rc) return rc;
     AttnArgs a{};
     a.q_rot = q_rot;
@@ -283,6 +293,10 @@ int run_attention_untimed(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seq
     if (kern == Kernel::Generic) {
         if (hs.head_dim > 256) return fail(SHAINET_ATTN_E_UNSUPPORTED, "head_dim %d > 256", hs.head_dim);
         CU(launch_attn_generic(a, s));
+        return SHAINET_ATTN_OK;
+    }
+    if (kern == Kernel::Tensor) {
+        CU(launch_attn_prefill_tc(a, s));
         return SHAINET_ATTN_OK;
     }
     const int rows = batch * T;

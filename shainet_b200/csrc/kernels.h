@@ -109,6 +109,13 @@ cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s);
 // programmatic stream serialization.
 cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s);
 
+// Causal prefill on the tcgen05 tensor cores (TF32): head_dim 64 or 128, one
+// sequence, q already rotated, cache already appended.  Rows of the cache
+// beyond the appended length must hold finite values (the caches are zeroed
+// when allocated).
+bool prefill_tc_supported(const HeadShape& hs);
+cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s);
+
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
                                unsigned long long seed, cudaStream_t s);

@@ -1,0 +1,433 @@
+// Causal prefill attention over the KV cache on the 5th-generation tensor
+// cores (tcgen05, TF32 inputs, fp32 accumulation in tensor memory), sm_100a.
+//
+// Replaces the reference's attention_kv_kernel
+// (src/shainet/native/cuda_kernels.cu:734-806) when many new tokens arrive at
+// once: that kernel runs one 128-thread CTA per (head, token), forms scores
+// with scalar FMAs through a global scratch of heads x T x L floats (which
+// overflows Int32 at 32 x 8192 x 8192, src/shainet/transformer/llama_block.cr:418)
+// and never touches a tensor core.  Here one CTA owns a tile of 128 query rows
+// of one head and walks the visible cache positions in tiles of 64:
+//
+//   S  = Q K^T      tcgen05.mma kind::tf32, A and B from shared memory (K-major),
+//                   accumulator in tensor memory
+//   P  = exp2(S*c - max) rounded to TF32, written back over S in tensor memory
+//   OT = P V        tcgen05.mma with A from tensor memory, B = the V tile from
+//                   shared memory (MN-major), fresh accumulator per tile
+//   O  = O*alpha + OT   in registers of the thread that owns the row
+//
+// Q, K and V tiles arrive by TMA (2-D tiled, 128-byte swizzle, no multicast)
+// into an mbarrier-guarded ring.  Warp 0 is the TMA producer, warp 1 allocates
+// tensor memory and issues the MMAs, warps 4-7 each own 32 TMEM lanes (one
+// query row per thread), so row maxima and sums need no shuffles.  Score and
+// output accumulators are double-buffered in tensor memory so that the MMAs of
+// one tile overlap the softmax of its neighbours.  Every wait is bounded.
+//
+// The softmax is the same max-subtracted form as the reference's
+// (llama_block.cr:346-373); TF32 rounds the inputs of both contractions to 10
+// mantissa bits, which is the 2e-3 tolerance class of this path.
+#include <cuda.h>
+#include <math.h>
+#include "kernels.h"
+
+namespace shainet {
+
+namespace {
+
+constexpr float PF_LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version field.
+// K-major operand: rows of 128 bytes, 8-row groups every 1024 bytes (SBO), the
+// leading offset is not used.  MN-major operand: 8-row (K) groups every 1024
+// bytes (SBO), 32-element (128-byte) column blocks every `lbo_bytes`.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: fp32 accumulate, TF32 A and B, dense.
+__host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+template <int HD>
+struct PF {
+    static constexpr int BM = 128;              // query rows per CTA
+    static constexpr int BN = 64;               // cache positions per tile
+    static constexpr int NSTG = 2;              // K/V ring depth
+    static constexpr int NBOX = HD / 32;        // 128-byte column blocks per row
+    static constexpr int Q_BYTES = BM * HD * 4;
+    static constexpr int KV_BYTES = BN * HD * 4;  // one of K, V
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + NSTG * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TMEM_S = 0;            // two score/probability buffers of BN columns
+    static constexpr int TMEM_OT = 2 * BN;      // two output-tile buffers of HD columns
+    static constexpr int TMEM_COLS = (2 * BN + 2 * HD) <= 256 ? 256 : 512;
+    static constexpr int THREADS = 256;
+};
+
+struct PrefillArgs {
+    float* out;    // [T, num_heads*head_dim]
+    int T;         // new tokens (query rows)
+    int start;     // cache positions before them
+    int num_heads;
+    int num_kv_heads;
+    int capacity;
+    float scale;
+    AttnStatus* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PF<HD>::THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, PrefillArgs a) {
+    using C = PF<HD>;
+    extern __shared__ unsigned char pf_smem_raw[];
+    // 128-byte swizzle atoms want 1024-byte aligned tiles
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;
+    unsigned char* kv_s = base + C::Q_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + C::NSTG * C::STAGE_BYTES);
+    uint64_t* q_full = bars;              // 1
+    uint64_t* kv_full = bars + 1;         // NSTG
+    uint64_t* kv_empty = kv_full + C::NSTG;
+    uint64_t* s_full = kv_empty + C::NSTG;  // 2
+    uint64_t* p_full = s_full + 2;          // 2
+    uint64_t* ot_full = p_full + 2;         // 2
+    uint64_t* ot_empty = ot_full + 2;       // 2
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ot_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heaviest tiles (latest rows) first
+    const int qt = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y;
+    const int kv_h = h / (a.num_heads / a.num_kv_heads);
+    const int i0 = qt * C::BM;
+    const int rows_here = min(C::BM, a.T - i0);
+    const int kv_end = a.start + i0 + rows_here;            // positions visible to the last row of the tile
+    const int ntiles = (kv_end + C::BN - 1) / C::BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < C::NSTG; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&s_full[b], 1);
+            mbar_init(&p_full[b], 128);
+            mbar_init(&ot_full[b], 1);
+            mbar_init(&ot_empty[b], 128);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, C::Q_BYTES);
+            for (int c = 0; c < C::NBOX; ++c) tma_load_2d(q_s + c * (C::BM * 128), &tm_q, h * HD + 32 * c, i0, q_full);
+            for (int j = 0; j < ntiles; ++j) {
+                const int st = j % C::NSTG;
+                if (j >= C::NSTG && !mbar_wait(&kv_empty[st], ((j / C::NSTG) - 1) & 1, a.status, 11)) break;
+                unsigned char* k_s = kv_s + st * C::STAGE_BYTES;
+                unsigned char* v_s = k_s + C::KV_BYTES;
+                mbar_arrive_expect_tx(&kv_full[st], C::STAGE_BYTES);
+                const int y = kv_h * a.capacity + j * C::BN;
+                for (int c = 0; c < C::NBOX; ++c) {
+                    tma_load_2d(k_s + c * (C::BN * 128), &tm_k, 32 * c, y, &kv_full[st]);
+                    tma_load_2d(v_s + c * (C::BN * 128), &tm_v, 32 * c, y, &kv_full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_tf32(C::BM, C::BN, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_tf32(C::BM, HD, 0, 1);
+            const uint32_t q_addr = smem_u32(q_s);
+            bool ok = mbar_wait(q_full, 0, a.status, 12);
+            for (int j = 0; ok && j <= ntiles; ++j) {
+                if (j < ntiles) {
+                    const int st = j % C::NSTG;
+                    if (!(ok = mbar_wait(&kv_full[st], (j / C::NSTG) & 1, a.status, 13))) break;
+                    tc_fence_after();
+                    const uint32_t k_addr = smem_u32(kv_s + st * C::STAGE_BYTES);
+                    const uint32_t d = tmem + C::TMEM_S + (j & 1) * C::BN;
+#pragma unroll
+                    for (int kk = 0; kk < HD / 8; ++kk) {
+                        // k-step kk: column block kk/4, 32-byte slice kk%4 inside its 128-byte rows
+                        const uint64_t ad = smem_desc_sw128(q_addr + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
+                        const uint64_t bd = smem_desc_sw128(k_addr + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
+                        mma_ss_tf32(d, ad, bd, idesc_qk, kk > 0);
+                    }
+                    tc_commit(&s_full[j & 1]);
+                }
+                if (j >= 1) {
+                    const int t = j - 1, b = t & 1, st = t % C::NSTG;
+                    if (!(ok = mbar_wait(&p_full[b], (t >> 1) & 1, a.status, 14))) break;
+                    if (t >= 2 && !(ok = mbar_wait(&ot_empty[b], ((t >> 1) - 1) & 1, a.status, 15))) break;
+                    tc_fence_after();
+                    const uint32_t v_addr = smem_u32(kv_s + st * C::STAGE_BYTES + C::KV_BYTES);
+                    const uint32_t d = tmem + C::TMEM_OT + b * HD;
+                    const uint32_t p = tmem + C::TMEM_S + b * C::BN;
+#pragma unroll
+                    for (int kk = 0; kk < C::BN / 8; ++kk) {
+                        // k-step kk: cache rows 8kk..8kk+7 (one 1024-byte group); column blocks every BN*128 bytes
+                        const uint64_t bd = smem_desc_sw128(v_addr + kk * 1024, C::BN * 128, 1024);
+                        mma_ts_tf32(d, p + kk * 8, bd, idesc_pv, kk > 0);
+                    }
+                    tc_commit(&ot_full[b]);
+                    tc_commit(&kv_empty[st]);
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- softmax + output accumulation: one query row per thread ----------------
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const int row_pos = a.start + i0 + r;           // last visible cache position of this row
+        const float sl2 = a.scale * PF_LOG2E;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
+        bool ok = true;
+        for (int j = 0; ok && j <= ntiles; ++j) {
+            float alpha = 1.0f;
+            if (j < ntiles) {
+                const int b = j & 1;
+                if (!(ok = mbar_wait(&s_full[b], (j >> 1) & 1, a.status, 16))) break;
+                tc_fence_after();
+                uint32_t s0[32], s1[32];
+                const uint32_t sa = tmem + lane_addr + C::TMEM_S + b * C::BN;
+                tmem_ld32(sa, s0);
+                tmem_ld32(sa + 32, s1);
+                tmem_wait_ld();
+                const int c0 = j * C::BN;
+                const bool diag = c0 + C::BN - 1 > row_pos;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float x0 = __uint_as_float(s0[c]) * sl2, x1 = __uint_as_float(s1[c]) * sl2;
+                    if (diag) {
+                        if (c0 + c > row_pos) x0 = -INFINITY;
+                        if (c0 + 32 + c > row_pos) x1 = -INFINITY;
+                    }
+                    s0[c] = __float_as_uint(x0);
+                    s1[c] = __float_as_uint(x1);
+                    mx = fmaxf(mx, fmaxf(x0, x1));
+                }
+                const float m_new = fmaxf(m, mx);
+                alpha = exp2f(m - m_new);   // 0 on the first tile
+                float sum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const uint32_t p0 = round_tf32(exp2f(__uint_as_float(s0[c]) - m_new));
+                    const uint32_t p1 = round_tf32(exp2f(__uint_as_float(s1[c]) - m_new));
+                    s0[c] = p0;
+                    s1[c] = p1;
+                    sum += __uint_as_float(p0) + __uint_as_float(p1);
+                }
+                l = fmaf(l, alpha, sum);
+                m = m_new;
+                tmem_st32(sa, s0);
+                tmem_st32(sa + 32, s1);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_full[b]);
+            }
+            if (j >= 1) {
+                const int t = j - 1, b = t & 1;
+                if (!(ok = mbar_wait(&ot_full[b], (t >> 1) & 1, a.status, 17))) break;
+                tc_fence_after();
+                const uint32_t oa = tmem + lane_addr + C::TMEM_OT + b * HD;
+#pragma unroll
+                for (int ch = 0; ch < HD / 32; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(oa + ch * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[ch * 32 + c] = fmaf(o[ch * 32 + c], alpha_prev, __uint_as_float(v[c]));
+                }
+                tc_fence_before();
+                mbar_arrive(&ot_empty[b]);
+            }
+            // o is now at the scale of tile j-1's maximum; alpha brings it to tile j's
+            alpha_prev = alpha;
+        }
+        if (ok && r < rows_here) {
+            const float inv = 1.0f / l;
+            float* dst = a.out + ((size_t)(i0 + r) * a.num_heads + h) * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 4)
+                *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// fp32 matrix [rows, cols] with row pitch `pitch_floats`; box = box_rows x 32 floats (128 bytes), 128-byte swizzle.
+bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, uint64_t pitch_floats, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_floats * sizeof(float)};
+    cuuint32_t box[2] = {32, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HD>
+cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
+    using C = PF<HD>;
+    static unsigned long long configured = 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 64 || !(configured >> dev & 1ull)) {
+        e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        if (dev < 64) configured |= 1ull << dev;
+    }
+    const SeqDesc& sd = a.seqs.one;
+    const int H = a.hs.num_heads, KV = a.hs.num_kv_heads;
+    CUtensorMap tq, tk, tv;
+    if (!make_map(&tq, a.q_rot, (uint64_t)H * HD, (uint64_t)a.T, (uint64_t)H * HD, C::BM) ||
+        !make_map(&tk, sd.k, HD, (uint64_t)KV * sd.capacity, HD, C::BN) ||
+        !make_map(&tv, sd.v, HD, (uint64_t)KV * sd.capacity, HD, C::BN))
+        return cudaErrorInvalidValue;
+    PrefillArgs p{};
+    p.out = a.out;
+    p.T = a.T;
+    p.start = sd.start;
+    p.num_heads = H;
+    p.num_kv_heads = KV;
+    p.capacity = sd.capacity;
+    p.scale = a.scale;
+    p.status = a.status;
+    dim3 grid((a.T + C::BM - 1) / C::BM, H);
+    attn_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool prefill_tc_supported(const HeadShape& hs) { return hs.head_dim == 64 || hs.head_dim == 128; }
+
+cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s) {
+    if (a.batch != 1 || a.seqs.many != nullptr) return cudaErrorInvalidValue;
+    if (a.T == 0) return cudaSuccess;
+    if (a.hs.head_dim == 64) return launch_pf<64>(a, s);
+    if (a.hs.head_dim == 128) return launch_pf<128>(a, s);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace shainet

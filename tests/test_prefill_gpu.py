@@ -1,0 +1,77 @@
+"""Tensor-core (tcgen05, TF32) causal prefill against the CPU oracle.
+Tolerance: max|y-ref|/max|ref| <= 2e-3 (TF32 rounds the inputs of both
+contractions to 10 mantissa bits); decode steps that follow stay at 1e-5
+because the cache itself is fp32 and identical."""
+import numpy as np
+import pytest
+
+from helpers import DECODE_TOL, L1B, Q30, Q8B, make_pair, qkv, rel_err
+
+pytestmark = pytest.mark.gpu
+
+PREFILL_TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import shainet_b200 as S
+    from shainet_b200 import build
+    build.build()
+    c = S.AttnContext(0)
+    yield c
+    c.close()
+
+
+@pytest.mark.parametrize("shape,T", [(L1B, 512), (Q8B, 256), (Q30, 130), (Q8B, 64), (L1B, 1000)],
+                         ids=["llama1b_512", "qwen3_8b_256", "qwen3_30b_130", "qwen3_8b_64", "llama1b_1000"])
+def test_prefill_from_empty_cache(ctx, shape, T):
+    import shainet_b200 as S
+    rng = np.random.default_rng(3001)
+    o, g = make_pair(ctx, shape, rng)
+    q, k, v = qkv(rng, shape, T)
+    ref = o.attend_cached(q, k, v, threads=8)
+    got = g.forward_cached(q, k, v, S.F_TENSOR)
+    e = rel_err(got, ref)
+    assert e <= PREFILL_TOL, e
+    # every row, not only the largest: per-row error against the row's own scale
+    per_row = np.abs(got - ref).max(axis=1) / np.abs(ref).max(axis=1)
+    assert per_row.max() <= 4 * PREFILL_TOL, per_row.max()
+    # the cache is exact fp32 work, and decode after the prefill is at decode tolerance
+    ko, vo = o.export_cache(); kg, vg = g.cache.export()
+    assert np.array_equal(vo, vg) and np.abs(ko - kg).max() <= 4e-7 * np.abs(ko).max()
+    q, k, v = qkv(rng, shape, 1)
+    assert rel_err(g.forward_cached(q, k, v), o.attend_cached(q, k, v)) <= DECODE_TOL
+    g.close()
+
+
+def test_chunked_prefill_over_existing_cache(ctx):
+    """A second chunk attends to the rows of the first (start_pos > 0) and to
+    its own rows causally; chunk sizes are not multiples of the tiles."""
+    import shainet_b200 as S
+    rng = np.random.default_rng(3002)
+    o, g = make_pair(ctx, Q8B, rng)
+    for T in (300, 200, 77):
+        q, k, v = qkv(rng, Q8B, T)
+        ref = o.attend_cached(q, k, v, threads=8)
+        got = g.forward_cached(q, k, v, S.F_TENSOR)
+        assert rel_err(got, ref) <= PREFILL_TOL, (T, rel_err(got, ref))
+    assert g.cache_len == 577
+    g.close()
+
+
+def test_default_dispatch_uses_tensor_kernel_for_long_chunks(ctx):
+    """No flags: >= 64 rows go to the tensor-core kernel (TF32-level agreement
+    with the fp32 kernel, not bit equality), short chunks stay on fp32 kernels."""
+    import shainet_b200 as S
+    rng = np.random.default_rng(3003)
+    shape = Q30
+    o, g = make_pair(ctx, shape, rng)
+    _, g2 = make_pair(ctx, shape, np.random.default_rng(3003))
+    q, k, v = qkv(rng, shape, 192)
+    ref = o.attend_cached(q, k, v, threads=8)
+    a = g.forward_cached(q, k, v)                 # default: tensor cores
+    b = g2.forward_cached(q, k, v, S.F_GENERIC)   # forced fp32
+    assert rel_err(b, ref) <= DECODE_TOL
+    assert rel_err(a, ref) <= PREFILL_TOL
+    assert not np.array_equal(a, b)
+    g.close(); g2.close()
