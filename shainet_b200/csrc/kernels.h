@@ -44,6 +44,7 @@ struct PrepArgs {
     SeqRef seqs;
     int batch, T;
     HeadShape hs;
+    int round_q_tf32;      // round the rotated q to nearest TF32 (it feeds the tensor-core prefill kernel)
 };
 
 struct AttnArgs {

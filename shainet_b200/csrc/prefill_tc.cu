@@ -35,6 +35,13 @@ namespace shainet {
 namespace {
 
 constexpr float PF_LOG2E = 1.4426950408889634f;
+// The tensor core drops the 13 low mantissa bits of an fp32 operand (truncation
+// toward zero): every K and V element loses x * d with d in [0, 2^-10 / m) for a
+// mantissa m in [1, 2), i.e. 2^-11 * ln 2 on average.  The cache stays fp32, so
+// instead of rounding it the mean loss is put back as a constant factor on the
+// scores (K) and on the output (V); what remains is zero-mean, like rounding to
+// nearest.  q is rounded to nearest TF32 where it is written, P in this kernel.
+constexpr float PF_TRUNC_GAIN = 1.0f + 0.693147f / 2048.0f;
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
@@ -103,18 +110,29 @@ __device__ __forceinline__ uint32_t round_tf32(float x) {
     return r;
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, Blackwell version field.
-// K-major operand: rows of 128 bytes, 8-row groups every 1024 bytes (SBO), the
-// leading offset is not used.  MN-major operand: 8-row (K) groups every 1024
-// bytes (SBO), 32-element (128-byte) column blocks every `lbo_bytes`.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor (Blackwell version field set).
+//  * K-major operand (Q, K): rows of 128 bytes swizzled in 16-byte chunks
+//    (layout type 2 = SWIZZLE_128B), 8-row groups every 1024 bytes (SBO); the
+//    leading offset is not used.
+//  * MN-major 32-bit operand (V): the only layout the tensor core accepts is
+//    the 128-byte span swizzled in 32-byte chunks (layout type 1 =
+//    SWIZZLE_128B_BASE32B): rows (positions, the contraction index) of 128 bytes =
+//    32 head-dim columns, 4-row groups every 512 bytes (SBO), further blocks of
+//    32 columns every `lbo_bytes`.
+constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW128_BASE32B = 1;
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr >> 4) & 0x3FFF);
     d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= (uint64_t)1 << 46;  // descriptor version
-    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    d |= (uint64_t)layout << 61;
     return d;
+}
+
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return smem_desc(saddr, lbo_bytes, sbo_bytes, LAYOUT_SW128);
 }
 
 // Instruction descriptor: fp32 accumulate, TF32 A and B, dense.
@@ -149,6 +167,10 @@ struct PrefillArgs {
     int capacity;
     float scale;
     AttnStatus* status;
+#ifdef PF_DEBUG
+    float* dbg;    // [4][128][64]: raw S, P, OT(first 64 cols) of tile 0 of CTA (0,0), and scalars
+    int dbg_mode;
+#endif
 };
 
 template <int HD>
@@ -257,8 +279,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 #pragma unroll
                     for (int kk = 0; kk < C::BN / 8; ++kk) {
                         // k-step kk: cache rows 8kk..8kk+7 (one 1024-byte group); column blocks every BN*128 bytes
-                        const uint64_t bd = smem_desc_sw128(v_addr + kk * 1024, C::BN * 128, 1024);
+                        const uint64_t bd = smem_desc(v_addr + kk * 1024, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
+#ifdef PF_DBG_MMA2_SS
+                        {   // experiments on the second MMA
+                            const uint32_t k_addr2 = smem_u32(kv_s + st * C::STAGE_BYTES);
+                            const uint64_t ad = smem_desc_sw128(q_addr + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
+                            const uint64_t bk = smem_desc_sw128(k_addr2 + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
+                            const uint64_t bvk = smem_desc_sw128(v_addr + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
+                            if (a.dbg_mode == 1) mma_ss_tf32(d, ad, bk, idesc_tf32(128, 64, 0, 0), kk > 0);        // Q.K^T again at D
+                            else if (a.dbg_mode == 2) mma_ss_tf32(d, ad, bvk, idesc_tf32(128, 64, 0, 0), kk > 0);  // V read K-major
+                            else if (a.dbg_mode == 3) mma_ss_tf32(d, ad, bd, idesc_tf32(128, 64, 0, 1), kk > 0);   // MN-major, N=64
+                            else if (a.dbg_mode == 4) mma_ss_tf32(d, ad, bd, idesc_tf32(128, 128, 0, 1), kk > 0);  // MN-major, N=128
+                            else mma_ts_tf32(d, p + kk * 8, bk, idesc_tf32(128, 64, 0, 0), kk > 0);                // P from TMEM, K-major B
+                        }
+#else
                         mma_ts_tf32(d, p + kk * 8, bd, idesc_pv, kk > 0);
+#endif
                     }
                     tc_commit(&ot_full[b]);
                     tc_commit(&kv_empty[st]);
@@ -271,7 +307,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const int row_pos = a.start + i0 + r;           // last visible cache position of this row
-        const float sl2 = a.scale * PF_LOG2E;
+        const float sl2 = a.scale * PF_LOG2E * PF_TRUNC_GAIN;
         float o[HD];
 #pragma unroll
         for (int d = 0; d < HD; ++d) o[d] = 0.0f;
@@ -288,6 +324,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tmem_ld32(sa, s0);
                 tmem_ld32(sa + 32, s1);
                 tmem_wait_ld();
+#ifdef PF_DEBUG
+                if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
+                    for (int c = 0; c < 32; ++c) {
+                        a.dbg[(0 * 128 + r) * 64 + c] = __uint_as_float(s0[c]);
+                        a.dbg[(0 * 128 + r) * 64 + 32 + c] = __uint_as_float(s1[c]);
+                    }
+#endif
                 const int c0 = j * C::BN;
                 const bool diag = c0 + C::BN - 1 > row_pos;
                 float mx = -INFINITY;
@@ -313,6 +356,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     s1[c] = p1;
                     sum += __uint_as_float(p0) + __uint_as_float(p1);
                 }
+#ifdef PF_DEBUG
+                if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
+                    for (int c = 0; c < 32; ++c) {
+                        a.dbg[(1 * 128 + r) * 64 + c] = __uint_as_float(s0[c]);
+                        a.dbg[(1 * 128 + r) * 64 + 32 + c] = __uint_as_float(s1[c]);
+                    }
+#endif
                 l = fmaf(l, alpha, sum);
                 m = m_new;
                 tmem_st32(sa, s0);
@@ -326,11 +376,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (!(ok = mbar_wait(&ot_full[b], (t >> 1) & 1, a.status, 17))) break;
                 tc_fence_after();
                 const uint32_t oa = tmem + lane_addr + C::TMEM_OT + b * HD;
+#ifdef PF_DEBUG
+                if (a.dbg && t == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
+                    for (int ch = 0; ch < C::TMEM_COLS / 32; ++ch) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem + lane_addr + ch * 32, v);
+                        tmem_wait_ld();
+                        for (int c = 0; c < 32; ++c) a.dbg[4 * 128 * 64 + r * 512 + ch * 32 + c] = __uint_as_float(v[c]);
+                    }
+#endif
 #pragma unroll
                 for (int ch = 0; ch < HD / 32; ++ch) {
                     uint32_t v[32];
                     tmem_ld32(oa + ch * 32, v);
                     tmem_wait_ld();
+#ifdef PF_DEBUG
+                    if (a.dbg && t == 0 && ch < 2 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
+                        for (int c = 0; c < 32; ++c) a.dbg[(2 * 128 + r) * 64 + ch * 32 + c] = __uint_as_float(v[c]);
+#endif
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[ch * 32 + c] = fmaf(o[ch * 32 + c], alpha_prev, __uint_as_float(v[c]));
                 }
@@ -341,7 +404,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             alpha_prev = alpha;
         }
         if (ok && r < rows_here) {
-            const float inv = 1.0f / l;
+            const float inv = PF_TRUNC_GAIN / l;
             float* dst = a.out + ((size_t)(i0 + r) * a.num_heads + h) * HD;
 #pragma unroll
             for (int d = 0; d < HD; d += 4)
@@ -372,8 +435,9 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp32 matrix [rows, cols] with row pitch `pitch_floats`; box = box_rows x 32 floats (128 bytes), 128-byte swizzle.
-bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, uint64_t pitch_floats, uint32_t box_rows) {
+// fp32 matrix [rows, cols] with row pitch `pitch_floats`; box = box_rows x 32 floats (128 bytes).
+bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, uint64_t pitch_floats, uint32_t box_rows,
+              CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -381,7 +445,7 @@ bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, u
     cuuint32_t box[2] = {32, box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -400,9 +464,9 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
     const SeqDesc& sd = a.seqs.one;
     const int H = a.hs.num_heads, KV = a.hs.num_kv_heads;
     CUtensorMap tq, tk, tv;
-    if (!make_map(&tq, a.q_rot, (uint64_t)H * HD, (uint64_t)a.T, (uint64_t)H * HD, C::BM) ||
-        !make_map(&tk, sd.k, HD, (uint64_t)KV * sd.capacity, HD, C::BN) ||
-        !make_map(&tv, sd.v, HD, (uint64_t)KV * sd.capacity, HD, C::BN))
+    if (!make_map(&tq, a.q_rot, (uint64_t)H * HD, (uint64_t)a.T, (uint64_t)H * HD, C::BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tk, sd.k, HD, (uint64_t)KV * sd.capacity, HD, C::BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tv, sd.v, HD, (uint64_t)KV * sd.capacity, HD, C::BN, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
         return cudaErrorInvalidValue;
     PrefillArgs p{};
     p.out = a.out;
@@ -413,6 +477,10 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
     p.capacity = sd.capacity;
     p.scale = a.scale;
     p.status = a.status;
+#ifdef PF_DEBUG
+    p.dbg = a.part_o;  // the debug harness passes its dump buffer here
+    p.dbg_mode = a.chunk_rows;
+#endif
     dim3 grid((a.T + C::BM - 1) / C::BM, H);
     attn_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     return cudaGetLastError();

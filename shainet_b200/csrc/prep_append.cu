@@ -93,8 +93,18 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) prep_append_kernel(PrepArgs a
         const float angle = __fmul_rn(fpos, a.inv_freq[i]);
         float s, c;
         sincosf(angle, &s, &c);
-        dst[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        dst[i + half] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+        float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        float y1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+        if (a.round_q_tf32 && slot < H) {
+            // q only: the cache keeps full fp32 rows
+            unsigned u0, u1;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y0));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y1));
+            y0 = __uint_as_float(u0);
+            y1 = __uint_as_float(u1);
+        }
+        dst[i] = y0;
+        dst[i + half] = y1;
     }
 }
 
