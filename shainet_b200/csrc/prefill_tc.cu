@@ -40,7 +40,8 @@ constexpr float PF_LOG2E = 1.4426950408889634f;
 // mantissa m in [1, 2), i.e. 2^-11 * ln 2 on average.  The cache stays fp32, so
 // instead of rounding it the mean loss is put back as a constant factor on the
 // scores (K) and on the output (V); what remains is zero-mean, like rounding to
-// nearest.  q is rounded to nearest TF32 where it is written, P in this kernel.
+// nearest.  q is rounded to nearest TF32 where it is written; P is handed over
+// as fp32 bits and treated like V.
 constexpr float PF_TRUNC_GAIN = 1.0f + 0.693147f / 2048.0f;
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -104,9 +105,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__device__ __forceinline__ uint32_t round_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
 
@@ -167,10 +168,6 @@ struct PrefillArgs {
     int capacity;
     float scale;
     AttnStatus* status;
-#ifdef PF_DEBUG
-    float* dbg;    // [4][128][64]: raw S, P, OT(first 64 cols) of tile 0 of CTA (0,0), and scalars
-    int dbg_mode;
-#endif
 };
 
 template <int HD>
@@ -280,21 +277,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     for (int kk = 0; kk < C::BN / 8; ++kk) {
                         // k-step kk: cache rows 8kk..8kk+7 (one 1024-byte group); column blocks every BN*128 bytes
                         const uint64_t bd = smem_desc(v_addr + kk * 1024, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
-#ifdef PF_DBG_MMA2_SS
-                        {   // experiments on the second MMA
-                            const uint32_t k_addr2 = smem_u32(kv_s + st * C::STAGE_BYTES);
-                            const uint64_t ad = smem_desc_sw128(q_addr + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
-                            const uint64_t bk = smem_desc_sw128(k_addr2 + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
-                            const uint64_t bvk = smem_desc_sw128(v_addr + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
-                            if (a.dbg_mode == 1) mma_ss_tf32(d, ad, bk, idesc_tf32(128, 64, 0, 0), kk > 0);        // Q.K^T again at D
-                            else if (a.dbg_mode == 2) mma_ss_tf32(d, ad, bvk, idesc_tf32(128, 64, 0, 0), kk > 0);  // V read K-major
-                            else if (a.dbg_mode == 3) mma_ss_tf32(d, ad, bd, idesc_tf32(128, 64, 0, 1), kk > 0);   // MN-major, N=64
-                            else if (a.dbg_mode == 4) mma_ss_tf32(d, ad, bd, idesc_tf32(128, 128, 0, 1), kk > 0);  // MN-major, N=128
-                            else mma_ts_tf32(d, p + kk * 8, bk, idesc_tf32(128, 64, 0, 0), kk > 0);                // P from TMEM, K-major B
-                        }
-#else
                         mma_ts_tf32(d, p + kk * 8, bd, idesc_pv, kk > 0);
-#endif
                     }
                     tc_commit(&ot_full[b]);
                     tc_commit(&kv_empty[st]);
@@ -324,46 +307,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tmem_ld32(sa, s0);
                 tmem_ld32(sa + 32, s1);
                 tmem_wait_ld();
-#ifdef PF_DEBUG
-                if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
-                    for (int c = 0; c < 32; ++c) {
-                        a.dbg[(0 * 128 + r) * 64 + c] = __uint_as_float(s0[c]);
-                        a.dbg[(0 * 128 + r) * 64 + 32 + c] = __uint_as_float(s1[c]);
-                    }
-#endif
                 const int c0 = j * C::BN;
-                const bool diag = c0 + C::BN - 1 > row_pos;
+                if (c0 + C::BN - 1 > row_pos) {         // tile crosses this row's causal boundary
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        if (c0 + c > row_pos) s0[c] = 0xff800000u;        // -inf
+                        if (c0 + 32 + c > row_pos) s1[c] = 0xff800000u;
+                    }
+                }
                 float mx = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float x0 = __uint_as_float(s0[c]) * sl2, x1 = __uint_as_float(s1[c]) * sl2;
-                    if (diag) {
-                        if (c0 + c > row_pos) x0 = -INFINITY;
-                        if (c0 + 32 + c > row_pos) x1 = -INFINITY;
-                    }
-                    s0[c] = __float_as_uint(x0);
-                    s1[c] = __float_as_uint(x1);
-                    mx = fmaxf(mx, fmaxf(x0, x1));
-                }
-                const float m_new = fmaxf(m, mx);
-                alpha = exp2f(m - m_new);   // 0 on the first tile
-                float sum = 0.0f;
+                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+                // scores stay raw; the positive factor sl2 commutes with max
+                const float m_new = fmaxf(m, mx * sl2);
+                alpha = ex2_approx(m - m_new);   // 0 on the first tile
+                float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
-                    const uint32_t p0 = round_tf32(exp2f(__uint_as_float(s0[c]) - m_new));
-                    const uint32_t p1 = round_tf32(exp2f(__uint_as_float(s1[c]) - m_new));
-                    s0[c] = p0;
-                    s1[c] = p1;
-                    sum += __uint_as_float(p0) + __uint_as_float(p1);
+                    // P goes to the tensor core as fp32 bits; its truncation to TF32
+                    // there is covered by PF_TRUNC_GAIN on the output
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(s0[c]), sl2, -m_new));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(s1[c]), sl2, -m_new));
+                    s0[c] = __float_as_uint(p0);
+                    s1[c] = __float_as_uint(p1);
+                    sum0 += p0;
+                    sum1 += p1;
                 }
-#ifdef PF_DEBUG
-                if (a.dbg && j == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
-                    for (int c = 0; c < 32; ++c) {
-                        a.dbg[(1 * 128 + r) * 64 + c] = __uint_as_float(s0[c]);
-                        a.dbg[(1 * 128 + r) * 64 + 32 + c] = __uint_as_float(s1[c]);
-                    }
-#endif
-                l = fmaf(l, alpha, sum);
+                l = fmaf(l, alpha, sum0 + sum1);
                 m = m_new;
                 tmem_st32(sa, s0);
                 tmem_st32(sa + 32, s1);
@@ -376,24 +346,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (!(ok = mbar_wait(&ot_full[b], (t >> 1) & 1, a.status, 17))) break;
                 tc_fence_after();
                 const uint32_t oa = tmem + lane_addr + C::TMEM_OT + b * HD;
-#ifdef PF_DEBUG
-                if (a.dbg && t == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
-                    for (int ch = 0; ch < C::TMEM_COLS / 32; ++ch) {
-                        uint32_t v[32];
-                        tmem_ld32(tmem + lane_addr + ch * 32, v);
-                        tmem_wait_ld();
-                        for (int c = 0; c < 32; ++c) a.dbg[4 * 128 * 64 + r * 512 + ch * 32 + c] = __uint_as_float(v[c]);
-                    }
-#endif
 #pragma unroll
                 for (int ch = 0; ch < HD / 32; ++ch) {
                     uint32_t v[32];
                     tmem_ld32(oa + ch * 32, v);
                     tmem_wait_ld();
-#ifdef PF_DEBUG
-                    if (a.dbg && t == 0 && ch < 2 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0)
-                        for (int c = 0; c < 32; ++c) a.dbg[(2 * 128 + r) * 64 + ch * 32 + c] = __uint_as_float(v[c]);
-#endif
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[ch * 32 + c] = fmaf(o[ch * 32 + c], alpha_prev, __uint_as_float(v[c]));
                 }
@@ -404,7 +361,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             alpha_prev = alpha;
         }
         if (ok && r < rows_here) {
-            const float inv = PF_TRUNC_GAIN / l;
+            const float inv = PF_TRUNC_GAIN * PF_TRUNC_GAIN / l;   // V and P are both truncated by the tensor core
             float* dst = a.out + ((size_t)(i0 + r) * a.num_heads + h) * HD;
 #pragma unroll
             for (int d = 0; d < HD; d += 4)
@@ -477,10 +434,6 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
     p.capacity = sd.capacity;
     p.scale = a.scale;
     p.status = a.status;
-#ifdef PF_DEBUG
-    p.dbg = a.part_o;  // the debug harness passes its dump buffer here
-    p.dbg_mode = a.chunk_rows;
-#endif
     dim3 grid((a.T + C::BM - 1) / C::BM, H);
     attn_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
     return cudaGetLastError();
