@@ -135,6 +135,28 @@ int shainet_attn_forward_dev(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const f
                              const float* v_new_dev, float* out_dev, int new_tokens, float scale, unsigned flags,
                              void* stream);
 
+/* ---- one sequence split over several GPUs.  The reference is single-device
+ * (no cudaSetDevice, no collective anywhere in src/); these three entries serve
+ * the partition "kv-head groups over ranks, and positions round-robin over the
+ * ranks of a group when there are more ranks than kv heads".
+ *
+ * forward_dev_at: one decode token whose RoPE position is `position` (>= the
+ * rows this rank's cache holds).  append != 0: this rank stores the token's k/v
+ * row and attends over its rows including it; append == 0: it only attends over
+ * the rows it already holds (k_new/v_new may be NULL).  Fused decode kernel only.
+ * set_lse_out: while non-NULL, every fused decode call also writes max + ln(sum)
+ * of each (sequence, head) softmax to lse_dev[batch*num_heads].
+ * merge_parts: gathered_dev holds, per rank, heads_per_rank*head_dim outputs then
+ * heads_per_rank log-sum-exp values; every `seq_parts` consecutive ranks form a
+ * head group whose results are merged into out_full_dev
+ * [world/seq_parts * heads_per_rank * head_dim]. */
+int shainet_attn_forward_dev_at(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q_dev, const float* k_new_dev,
+                                const float* v_new_dev, float* out_dev, int position, int append, float scale,
+                                unsigned flags, void* stream);
+int shainet_attn_ctx_set_lse_out(shainet_attn_ctx* ctx, float* lse_dev);
+int shainet_attn_merge_parts(shainet_attn_ctx* ctx, const float* gathered_dev, int world, int seq_parts,
+                             int heads_per_rank, int head_dim, float* out_full_dev, void* stream);
+
 /* One decode token for each of `batch` sequences in lock step, one launch:
  * q [batch, q_dim], k_new/v_new [batch, kv_dim], out [batch, q_dim] on the
  * device.  All caches share one head shape, RoPE table and norm weights (those

@@ -4,5 +4,6 @@ The product is ``lib/libshainet_attn.so`` (C ABI in ``include/shainet_attn.h``);
 this package is its host-side mirror of the reference's ``LlamaBlock`` attention
 interface.  Importing does not load the library; the first use does, and fails
 loudly if it has not been built."""
+from . import sharding  # noqa: F401
 from .attention import (AttnContext, KVCache, LlamaAttention, ShainetAttnError, default_scale, device_count,  # noqa: F401
                         forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY)

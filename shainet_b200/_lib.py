@@ -44,6 +44,9 @@ SIGNATURES = {
     "shainet_attn_kv_device_ptrs": (C.c_int, [_P, C.POINTER(_P), C.POINTER(_P)]),
     "shainet_attn_forward_host": (C.c_int, [_P, _P, _F, _F, _F, _F, C.c_int, C.c_float, C.c_uint]),
     "shainet_attn_forward_dev": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, C.c_float, C.c_uint, _P]),
+    "shainet_attn_forward_dev_at": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_float, C.c_uint, _P]),
+    "shainet_attn_ctx_set_lse_out": (C.c_int, [_P, _P]),
+    "shainet_attn_merge_parts": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "shainet_attn_forward_batched_dev": (C.c_int, [_P, C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_float,
                                                    C.c_uint, _P]),
     "shainet_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _P]),

@@ -65,6 +65,16 @@ class AttnContext:
     def scratch_bytes(self) -> int:
         return self.L.shainet_attn_ctx_scratch_bytes(self.h)
 
+    def set_lse_out(self, ptr):
+        """Device pointer (int) that receives max + ln(sum) per (sequence, head) of every
+        fused decode call, or None to stop."""
+        check(self.L.shainet_attn_ctx_set_lse_out(self.h, ptr))
+
+    def merge_parts(self, gathered_ptr: int, world: int, seq_parts: int, heads_per_rank: int, head_dim: int,
+                    out_ptr: int, stream=None):
+        check(self.L.shainet_attn_merge_parts(self.h, gathered_ptr, world, seq_parts, heads_per_rank, head_dim, out_ptr,
+                                              _stream_arg(stream)))
+
     def timing_enable(self, on: bool):
         check(self.L.shainet_attn_ctx_timing_enable(self.h, int(on)))
 
@@ -196,6 +206,13 @@ class LlamaAttention:
         """Device pointers (ints) on a caller stream (see _stream_arg); asynchronous."""
         check(self.ctx.L.shainet_attn_forward_dev(self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, new_tokens,
                                                   self.scale, flags, _stream_arg(stream)))
+
+    def forward_cached_dev_at(self, q_ptr: int, k_ptr, v_ptr, out_ptr: int, position: int, append: bool, stream=None,
+                              flags: int = 0):
+        """One decode token of a sequence that is split over ranks: RoPE position
+        `position`; this rank stores and sees the token's k/v row only if `append`."""
+        check(self.ctx.L.shainet_attn_forward_dev_at(self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, position,
+                                                     int(append), self.scale, flags, _stream_arg(stream)))
 
     def close(self):
         self.cache.close()

@@ -75,6 +75,7 @@ struct shainet_attn_ctx {
     unsigned* tickets = nullptr;        // split-merge tickets of the fused decode kernel, zero between launches
     size_t tickets_cap = 0;
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
+    float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool;  // reusable pairs
@@ -326,11 +327,13 @@ int validate_forward(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const void* q, 
 // `par` supplies the shared head shape, RoPE table, norm weights and biases.
 int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int batch, int T, long long total_visible,
              int max_visible, const float* q, const float* k_new, const float* v_new, float* out, float scale,
-             unsigned flags, cudaStream_t s) {
+             unsigned flags, cudaStream_t s, int pos_delta = 0, int no_append = 0) {
     const HeadShape hs = par->hs;
     const bool fused = T == 1 && splitk_supported(hs) &&
                        !(flags & (SHAINET_ATTN_F_GENERIC | SHAINET_ATTN_F_UNFUSED | SHAINET_ATTN_F_TENSOR));
     int rc;
+    if (!fused && (pos_delta != 0 || no_append))
+        return fail(SHAINET_ATTN_E_UNSUPPORTED, "a split sequence is served by the fused decode kernel only (head_dim 64/128, group size 1/2/4/8/16)");
     if (!fused) {
         ctx->last_fused = false;
         rc = grow(ctx->q_rot, (size_t)batch * T * hs.num_heads * hs.head_dim, s);
@@ -394,6 +397,9 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     // one can be appending the newest row of this very cache.
     f.unsafe_tail = ctx->last_fused ? 1 : 0;
     f.inputs_ready = (flags & SHAINET_ATTN_F_INPUTS_READY) ? 1 : 0;
+    f.pos_delta = pos_delta;
+    f.no_append = no_append;
+    f.lse_out = ctx->lse_out;
     std::pair<cudaEvent_t, cudaEvent_t> ev{};
     if (ctx->timing) {
         if (!ctx->ev_pool.empty()) {
@@ -759,6 +765,49 @@ int shainet_attn_forward_dev(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const f
     DeviceGuard g(ctx->device);
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
     return forward_device(ctx, kv, q, k_new, v_new, out, T, scale, flags, s);
+}
+
+int shainet_attn_ctx_set_lse_out(shainet_attn_ctx* ctx, float* lse_dev) {
+    if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    ctx->lse_out = lse_dev;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_forward_dev_at(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                                const float* v_new, float* out, int position, int append, float scale, unsigned flags,
+                                void* stream) {
+    int rc = validate_forward(ctx, kv, q, append ? k_new : q, append ? v_new : q, out, 1);
+    if (rc) return rc;
+    if (!aligned16(q) || !aligned16(out) || (append && (!aligned16(k_new) || !aligned16(v_new))))
+        return fail(SHAINET_ATTN_E_INVALID, "device pointers must be 16-byte aligned");
+    if (position < kv->len) return fail(SHAINET_ATTN_E_INVALID, "position %d is before the %d rows this cache already holds", position, kv->len);
+    if (!append && kv->len == 0) return fail(SHAINET_ATTN_E_STATE, "nothing to attend to: the cache is empty and the token is not appended");
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    const int cap_before = kv->cap;
+    rc = kv_ensure(kv, kv->len + (append ? 1 : 0), s);
+    if (rc) return rc;
+    if (kv->cap != cap_before) ctx->last_fused = false;
+    SeqRef seqs{};
+    seqs.one = SeqDesc{kv->k, kv->v, kv->len, kv->cap};
+    seqs.many = nullptr;
+    const int visible = kv->len + (append ? 1 : 0);
+    rc = run_step(ctx, kv, seqs, 1, 1, visible, visible, q, k_new, v_new, out, scale, flags, s, position - kv->len, append ? 0 : 1);
+    if (rc) return rc;
+    if (append) kv->len += 1;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_merge_parts(shainet_attn_ctx* ctx, const float* gathered_dev, int world, int seq_parts, int heads_per_rank,
+                             int head_dim, float* out_full_dev, void* stream) {
+    if (!ctx || !gathered_dev || !out_full_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (world <= 0 || seq_parts <= 0 || world % seq_parts != 0 || heads_per_rank <= 0 || head_dim <= 0)
+        return fail(SHAINET_ATTN_E_INVALID, "bad partition: %d ranks in groups of %d", world, seq_parts);
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    ctx->last_fused = false;
+    CU(launch_merge_parts(gathered_dev, world, seq_parts, heads_per_rank, head_dim, out_full_dev, s));
+    return SHAINET_ATTN_OK;
 }
 
 int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* const* kvs, int batch, const float* q,

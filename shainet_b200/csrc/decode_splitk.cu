@@ -472,7 +472,7 @@ constexpr int MERGE_GROUP = SK_MERGE_GROUP;  // splits merged by the last CTA of
 template <int HD, int G, int THREADS>
 __device__ void merge_partials(const float* po, const float* pml, size_t stride, int first, int count, int r, int kv_h,
                                int H, bool final, float* out, float* dst_o, float* dst_ml, size_t dst_stride,
-                               int dst_index) {
+                               int dst_index, float* lse_out) {
     // Every thread owns up to NT (head, four columns) tasks and walks the partials
     // in rounds of 8: the (max, sum) pairs and the output quads of a round are
     // all requested, for all of the thread's tasks, before any is used, so a
@@ -538,6 +538,7 @@ __device__ void merge_partials(const float* po, const float* pml, size_t stride,
             const float inv = 1.0f / L[t];
             *(reinterpret_cast<float4*>(out + (head0 + g) * HD) + d4) =
                 make_float4(acc[t].x * inv, acc[t].y * inv, acc[t].z * inv, acc[t].w * inv);
+            if (lse_out && d4 == 0) lse_out[head0 + g] = M[t] + logf(L[t]);
         } else {
             const size_t e = (head0 + g) * dst_stride + dst_index;
             *(reinterpret_cast<float4*>(dst_o + e * HD) + d4) = acc[t];
@@ -612,12 +613,12 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const int split = blockIdx.x, kv_h = blockIdx.y, r = blockIdx.z;
     const int H = a.hs.num_heads, KV = a.hs.num_kv_heads;
     const SeqDesc sd = a.seqs.many ? a.seqs.many[r] : a.seqs.one;
-    const int start = sd.start;     // position of the new token = rows already cached
-    const int visible = start + 1;
+    const int start = sd.start;     // rows already cached; the new token's row index if it is appended
+    const int visible = start + (a.no_append ? 0 : 1);
     const int row0 = split * a.chunk_rows;
     if (row0 >= visible) return;    // whole CTA: this sequence has fewer splits (an exit counts as its trigger)
     const int row1 = min(row0 + a.chunk_rows, visible);
-    const bool owns_new = row1 == visible;              // this slice ends with the new token
+    const bool owns_new = !a.no_append && row1 == visible;   // this slice ends with the new token
     const int rows = (owns_new ? start : row1) - row0;  // rows that come from the cache
     const int ntiles = (rows + C::TW - 1) / C::TW;
     // Tiles that end at or below `safe_end` cannot be under construction by the
@@ -645,7 +646,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     } else {
         // ---------------- consumers ----------------
         if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
-        const float fpos = (float)start;
+        const float fpos = (float)(start + a.pos_delta);   // RoPE position of the new token
         const int items = G + (owns_new ? 2 : 0);   // q rows of the group, then the new k row, then the new v row
         auto item_row = [&](int it) { return it < G ? sm.qs + it * C::QS_STRIDE : (it == G ? sm.xk : sm.xv); };
         // (1) raw rows (+ bias) into shared memory
@@ -715,6 +716,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         const int h = kv_h * G + g;
         if (nsplit_here == 1) {
             a.out[((size_t)r * H + h) * HD + d] = acc / L;
+            if (a.lse_out && d == 0) a.lse_out[(size_t)r * H + h] = M + logf(L);
         } else {
             const size_t pidx = ((size_t)r * H + h) * a.max_splits + split;
             a.part_o[pidx * HD + d] = acc;
@@ -734,14 +736,14 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     if (!take_last_ticket(a.tickets + a.batch * KV + rk * a.max_groups + grp, gsize, sm.flag)) return;
     if (ngroups == 1) {
         merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, 0, nsplit_here, r, kv_h, H, true, a.out, nullptr,
-                                          nullptr, 0, 0);
+                                          nullptr, 0, 0, a.lse_out);
         return;
     }
     merge_partials<HD, G, C::THREADS>(a.part_o, a.part_ml, a.max_splits, grp * MERGE_GROUP, gsize, r, kv_h, H, false, nullptr,
-                                      a.part2_o, a.part2_ml, a.max_groups, grp);
+                                      a.part2_o, a.part2_ml, a.max_groups, grp, nullptr);
     if (!take_last_ticket(a.tickets + rk, ngroups, sm.flag)) return;
     merge_partials<HD, G, C::THREADS>(a.part2_o, a.part2_ml, a.max_groups, 0, ngroups, r, kv_h, H, true, a.out, nullptr,
-                                      nullptr, 0, 0);
+                                      nullptr, 0, 0, a.lse_out);
 }
 
 template <class K>
@@ -805,7 +807,36 @@ cudaError_t dispatch_g(const A& a, F&& f) {
     }
 }
 
+// out_full[(g*Hr + h)*hd + d] = sum_p w_p o_p / sum_p w_p with w_p = exp(lse_p - max lse)
+__global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_parts, int heads_per_rank, int head_dim,
+                                   float* __restrict__ out_full) {
+    const int g = blockIdx.y, h = blockIdx.x;
+    const size_t rank_stride = (size_t)heads_per_rank * (head_dim + 1);
+    float mx = -INFINITY;
+    for (int p = 0; p < seq_parts; ++p)
+        mx = fmaxf(mx, gathered[(size_t)(g * seq_parts + p) * rank_stride + (size_t)heads_per_rank * head_dim + h]);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.0f, wsum = 0.0f;
+        for (int p = 0; p < seq_parts; ++p) {
+            const float* base = gathered + (size_t)(g * seq_parts + p) * rank_stride;
+            const float lse = base[(size_t)heads_per_rank * head_dim + h];
+            const float w = (lse == -INFINITY) ? 0.0f : expf(lse - mx);
+            wsum += w;
+            acc = fmaf(w, base[(size_t)h * head_dim + d], acc);
+        }
+        out_full[((size_t)g * heads_per_rank + h) * head_dim + d] = acc / wsum;
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
+                               float* out_full, cudaStream_t s) {
+    if (seq_parts <= 0 || world % seq_parts != 0) return cudaErrorInvalidValue;
+    dim3 grid(heads_per_rank, world / seq_parts);
+    merge_parts_kernel<<<grid, 128, 0, s>>>(gathered, seq_parts, heads_per_rank, head_dim, out_full);
+    return cudaGetLastError();
+}
 
 bool splitk_supported(const HeadShape& hs) {
     const int g = hs.num_heads / hs.num_kv_heads;

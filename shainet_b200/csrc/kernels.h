@@ -89,6 +89,9 @@ struct FusedArgs {
     int max_groups;
     int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
     int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
+    int pos_delta;         // RoPE position of the new token minus the rows already cached (0 unless the sequence is split over ranks)
+    int no_append;         // attend over the cached rows only: k_new/v_new are not used, nothing is appended
+    float* lse_out;        // nullable [batch, num_heads]: max + ln(sum) of every row's softmax, for merging partial results
     AttnStatus* status;
 };
 
@@ -116,6 +119,13 @@ cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s);
 // when allocated).
 bool prefill_tc_supported(const HeadShape& hs);
 cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s);
+
+// Merge of attention results computed over disjoint parts of one sequence by
+// different ranks: `gathered` holds, per rank, [heads_per_rank*head_dim] outputs
+// followed by [heads_per_rank] log-sum-exp values; consecutive `seq_parts` ranks
+// form one head group.  out_full is [groups*heads_per_rank*head_dim].
+cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
+                               float* out_full, cudaStream_t s);
 
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,

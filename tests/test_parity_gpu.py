@@ -334,3 +334,49 @@ def test_error_paths(ctx):
         ctx.close()                                  # a cache is still alive
     assert e.value.code == _lib.E_STATE
     a.close()
+
+
+def test_sequence_split_over_two_parts(ctx):
+    """One sequence whose positions alternate between two caches (what two ranks
+    of one head group hold): each part attends over its own rows with the token's
+    true RoPE position, only the owner appends, and the library's merge of the
+    two (output, log-sum-exp) pairs equals the unsplit oracle."""
+    import torch
+    import shainet_b200 as S
+    from shainet_b200.sharding import plan
+    rng = np.random.default_rng(5005)
+    shape = Q30
+    H, KV, hd = shape["H"], shape["KV"], shape["hd"]
+    qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    from oracle import oracle as O
+    o = O.OracleAttention(H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn)
+    parts = [S.LlamaAttention(ctx, H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn) for _ in range(2)]
+    L0 = 3001
+    q, k, v = qkv(rng, shape, L0)
+    o.attend_cached(q, k, v, threads=8)
+    kc, vc = o.export_cache()
+    for p, part in enumerate(parts):
+        part.cache.import_(kc[:, p::2], vc[:, p::2])
+        assert len(part.cache) == plan(2 * KV, p, H, KV).local_rows(L0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    gathered = torch.zeros(2, H * hd + H, device=dev)
+    merged = torch.empty(H * hd, device=dev)
+    for step in range(5):
+        pos = L0 + step
+        q, k, v = qkv(rng, shape, 1)
+        ref = o.attend_cached(q, k, v, threads=8)[0]
+        tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (q, k, v))
+        for p, part in enumerate(parts):
+            ctx.set_lse_out(gathered[p, H * hd:].data_ptr())
+            part.forward_cached_dev_at(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), gathered[p].data_ptr(), pos,
+                                       append=(pos % 2 == p), stream=stream)
+        ctx.set_lse_out(None)
+        ctx.merge_parts(gathered.data_ptr(), 2, 2, H, hd, merged.data_ptr(), stream)
+        torch.cuda.synchronize()
+        ctx.sync()
+        assert rel_err(merged.cpu().numpy(), ref) <= DECODE_TOL, step
+    assert len(parts[0].cache) + len(parts[1].cache) == L0 + 5
+    for part in parts:
+        part.close()
