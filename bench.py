@@ -224,17 +224,19 @@ def run_ours(args, wl, rank, world, local_rank):
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=dev)
     H, KV, hd, layers, ctx_len = wl["H"], wl["KV"], wl["hd"], wl["layers"], wl["ctx"]
-    if KV % world != 0:
-        raise SystemExit(f"{world} ranks do not divide {KV} kv heads (sequence-split sharding is not built yet)")
-    KVl, Hl = KV // world, H // world      # this rank's kv-head group(s) and their query heads
+    # kv-head groups over the ranks; with more ranks than kv heads the ranks of a
+    # group also split the positions round-robin (shainet_b200/sharding.py)
+    sp = S.sharding.plan(world, rank, H, KV)
+    KVl, Hl = sp.kv_count, sp.head_count
     qd, kd = Hl * hd, KVl * hd
+    local_ctx = sp.local_rows(ctx_len)
     K, W = args.steps, args.warmup
     K_roof = min(K, 32)
     K_e2e, W_e2e = min(K, 64), 3
 
     rng = np.random.default_rng(5000 + rank)
     ctx = S.AttnContext(local_rank)
-    cap = ctx_len + max(K, W, K_roof, K_e2e + W_e2e) + 8
+    cap = local_ctx + max(K, W, K_roof, K_e2e + W_e2e) + 8
     blocks = []
     for l in range(layers):
         kw = {}
@@ -242,7 +244,7 @@ def run_ours(args, wl, rank, world, local_rank):
             kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
                       k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
         b = S.LlamaAttention(ctx, Hl, KVl, hd, wl["theta"], 1e-6, initial_capacity=cap, **kw)
-        b.cache.fill_normal(ctx_len, 5001 + 1000 * rank + l)
+        b.cache.fill_normal(local_ctx, 5001 + 1000 * rank + l)
         blocks.append(b)
 
     NV = 4  # input variants cycled over steps
@@ -251,8 +253,11 @@ def run_ours(args, wl, rank, world, local_rank):
     q_d = torch.randn(NV, layers, qd, device=dev, generator=g)
     k_d = torch.randn(NV, layers, kd, device=dev, generator=g)
     v_d = torch.randn(NV, layers, kd, device=dev, generator=g)
-    out_d = torch.empty(layers, qd, device=dev)
-    gathered = torch.empty(layers, world, qd, device=dev) if world > 1 else None
+    split = sp.seq_parts > 1
+    pay = qd + (Hl if split else 0)        # a rank's contribution per layer: outputs (+ log-sum-exp when the sequence is split)
+    out_d = torch.empty(layers, pay, device=dev)
+    gathered = torch.empty(layers, world, pay, device=dev) if world > 1 else None
+    full_d = torch.empty(layers, H * hd, device=dev) if split else None
     # Everything timed runs on one explicit (non-default) stream: the library is
     # handed its handle, and the CUDA events are recorded on it.
     tstream = torch.cuda.Stream(device=dev)
@@ -264,7 +269,7 @@ def run_ours(args, wl, rank, world, local_rank):
 
     def reset():
         for b in blocks:
-            b.cache.truncate(ctx_len)
+            b.cache.truncate(local_ctx)
 
     # Pre-built argument lists keep the host cost of a launch to one foreign call.
     fwd_dev = ctx.L.shainet_attn_forward_dev
@@ -275,14 +280,35 @@ def run_ours(args, wl, rank, world, local_rank):
                 for vi in range(NV)]
     dev_args = build_args(0)
 
+    fwd_at = ctx.L.shainet_attn_forward_dev_at
+    set_lse = ctx.L.shainet_attn_ctx_set_lse_out
+    merge = ctx.L.shainet_attn_merge_parts
+    lse_ptrs = [vp(out_d[l, qd:].data_ptr()) for l in range(layers)] if split else None
+    gath_ptrs = [vp(gathered[l].data_ptr()) for l in range(layers)] if split else None
+    full_ptrs = [vp(full_d[l].data_ptr()) for l in range(layers)] if split else None
+
     def step(i, all_args=None):
         args = (all_args or dev_args)[i % NV]
+        if not split:
+            for l in range(layers):
+                rc = fwd_dev(*args[l])
+                if rc:
+                    S.check(rc)
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])   # head outputs before o_proj
+            return
+        pos = ctx_len + i                   # the token's position; its k/v row goes to one rank of the group
+        own = 1 if sp.owns_position(pos) else 0
         for l in range(layers):
-            rc = fwd_dev(*args[l])
+            a = args[l]
+            set_lse(ctx.h, lse_ptrs[l])
+            rc = fwd_at(a[0], a[1], a[2], a[3], a[4], a[5], pos, own, a[7], a[8], a[9])
             if rc:
                 S.check(rc)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])   # head outputs before o_proj
+            dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
+            rc = merge(ctx.h, gath_ptrs[l], world, sp.seq_parts, Hl, hd, full_ptrs[l], a[9])
+            if rc:
+                S.check(rc)
 
     def barrier():
         if world > 1:
@@ -343,16 +369,25 @@ def run_ours(args, wl, rank, world, local_rank):
     fwd_host = ctx.L.shainet_attn_forward_host
     FP = C.POINTER(C.c_float)
 
+    ho_full = torch.empty(layers, (H * hd) if split else (world * qd), dtype=torch.float32).pin_memory() if world > 1 else None
+
     def host_step(i):
         vi = i % NV
-        for l, b in enumerate(blocks):
-            rc = fwd_host(ctx.h, b.cache.h, C.cast(hq[vi, l].data_ptr(), FP), C.cast(hk[vi, l].data_ptr(), FP),
-                          C.cast(hv[vi, l].data_ptr(), FP), C.cast(ho[l].data_ptr(), FP), 1, b.scale, 0)
-            if rc:
-                S.check(rc)
-            if world > 1:
-                out_d[l].copy_(ho[l], non_blocking=True)
-                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
+        if world == 1:
+            for l, b in enumerate(blocks):
+                rc = fwd_host(ctx.h, b.cache.h, C.cast(hq[vi, l].data_ptr(), FP), C.cast(hk[vi, l].data_ptr(), FP),
+                              C.cast(hv[vi, l].data_ptr(), FP), C.cast(ho[l].data_ptr(), FP), 1, b.scale, 0)
+                if rc:
+                    S.check(rc)
+            return
+        # several ranks: this step's inputs come from pinned host memory, the gathered
+        # (and merged) head outputs of every layer go back to pinned host memory
+        q_d[vi].copy_(hq[vi], non_blocking=True)
+        k_d[vi].copy_(hk[vi], non_blocking=True)
+        v_d[vi].copy_(hv[vi], non_blocking=True)
+        step(i)
+        ho_full.copy_((full_d if split else gathered.view(layers, -1)), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
     for i in range(W_e2e):
         host_step(i)
     barrier()
@@ -376,7 +411,7 @@ def run_ours(args, wl, rank, world, local_rank):
         # region is the region's device time divided by the launches in it
         # (consecutive launches overlap through programmatic stream
         # serialization, so a per-launch event bracket would serialise them).
-        bytes_per_launch = decode_bytes(wl, ctx_len + (K + 1) / 2.0, KVl)
+        bytes_per_launch = decode_bytes(wl, local_ctx + (K + 1) / (2.0 * sp.seq_parts), KVl)
         avg_kernel_s = ms / 1e3 / (K * layers)
         achieved = bytes_per_launch / avg_kernel_s / 1e9
         isolated_us = kernel_ms * 1e3 / max(launches, 1)
@@ -385,10 +420,10 @@ def run_ours(args, wl, rank, world, local_rank):
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "layers": layers, "num_heads": H, "num_kv_heads": KV, "head_dim": hd,
-                       "ctx": ctx_len, "sharding": f"kv-head groups over {world} rank(s)",
+                       "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); all-gather of head outputs per layer",
                        "l2": "working set per step (all layers' K/V) is far larger than L2; no flush needed",
                        "host_enqueue_ms_per_step": t_enq * 1e3 / K,
-                       "hbm_gbs_whole_step": decode_bytes(wl, ctx_len + (K + 1) / 2.0, KVl) * layers / (ms / K / 1e3) / 1e9},
+                       "hbm_gbs_whole_step_per_gpu": bytes_per_launch * layers / (ms / K / 1e3) / 1e9},
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
@@ -399,7 +434,8 @@ def run_ours(args, wl, rank, world, local_rank):
                                   "gbs": bytes_per_launch / (ms_ready / 1e3 / (K * layers)) / 1e9,
                                   "note": "same region with SHAINET_ATTN_F_INPUTS_READY (q/k/v not produced by the previous launch)"},
             "e2e": {"value": K_e2e / e2e_s, "unit": "tokens/s", "steps": K_e2e,
-                    "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz, "d2h_bytes_per_step": layers * qd * esz},
+                    "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz,
+                    "d2h_bytes_per_step": layers * (qd if world == 1 else H * hd) * esz},
             "gpu_launches": layers * K,
         }
         if prefill is not None:
