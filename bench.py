@@ -40,6 +40,9 @@ WORKLOADS = {
                  H=32, KV=8, hd=64, theta=5e5, qk_norm=False, layers=16, ctx=4096),
 }
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_fused_kernel launch on the cfg5 shape at L = 32770
+# (ncu capture summarised in profiles/attn_decode_fused_kernel__cfg5_ctx32k.md): 138.3 MB for 134.26 MB algorithmic.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 138.3 / 134.26
 
 
 def decode_bytes(wl, L, kv_heads=None):
@@ -427,7 +430,9 @@ def run_ours(args, wl, rank, world, local_rank):
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel", "achieved": achieved,
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "bytes_per_launch": bytes_per_launch,
+                         "traffic": bytes_per_launch * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE if args.workload == "cfg5" and world == 1 else None,
+                         "traffic_note": "ncu dram read+write bytes of one launch at L=32770, scaled by the rows of this run",
+                         "bytes_per_launch": bytes_per_launch,
                          "avg_launch_us": avg_kernel_s * 1e6, "launches_timed": K * layers,
                          "isolated_launch_us": isolated_us, "isolated_launches": launches},
             "inputs_ready_mode": {"value": K / (ms_ready / 1e3), "unit": "tokens/s", "avg_launch_us": ms_ready * 1e3 / (K * layers),

@@ -44,6 +44,9 @@ extern "C" {
  * kernel is still draining, and only waits for it before touching the scratch
  * the two share.  Without the flag nothing is assumed. */
 #define SHAINET_ATTN_F_INPUTS_READY 16u
+/* Merge the split partials of the fused decode kernel with "last finisher"
+ * tickets even where the flag-polling merge would be chosen (testing). */
+#define SHAINET_ATTN_F_TICKET_MERGE 32u
 
 typedef struct shainet_attn_ctx shainet_attn_ctx;
 typedef struct shainet_attn_kv shainet_attn_kv;

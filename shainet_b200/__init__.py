@@ -6,4 +6,4 @@ interface.  Importing does not load the library; the first use does, and fails
 loudly if it has not been built."""
 from . import sharding  # noqa: F401
 from .attention import (AttnContext, KVCache, LlamaAttention, ShainetAttnError, default_scale, device_count,  # noqa: F401
-                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY)
+                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE)

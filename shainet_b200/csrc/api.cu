@@ -74,6 +74,8 @@ struct shainet_attn_ctx {
     int live_caches = 0;
     unsigned* tickets = nullptr;        // split-merge tickets of the fused decode kernel, zero between launches
     size_t tickets_cap = 0;
+    unsigned epoch = 0;                 // flag value of the newest streaming-merge launch
+    size_t flags_offset = ~(size_t)0;   // where the flags start inside `tickets` (they move with the head shape)
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
     float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
     bool timing = false;
@@ -390,9 +392,28 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
         f.part2_o = ctx->part.p + n1;
         f.part2_ml = f.part2_o + (size_t)batch * hs.num_heads * f.max_groups * hs.head_dim;
     }
-    rc = ensure_tickets(ctx, (size_t)batch * hs.num_kv_heads * (1 + f.max_groups), s);
+    // tickets (two levels), then the streaming-merge flags
+    const size_t n_tickets = (size_t)batch * hs.num_kv_heads * (1 + f.max_groups);
+    const size_t n_flags = (size_t)batch * hs.num_kv_heads * f.max_splits;
+    const size_t cap_before = ctx->tickets_cap;
+    rc = ensure_tickets(ctx, n_tickets + n_flags, s);
     if (rc) return rc;
     f.tickets = ctx->tickets;
+    f.flags = ctx->tickets + n_tickets;
+    // Streaming merge needs every CTA of the grid resident at once and flags that
+    // cannot hold this launch's value yet: a fresh epoch per launch, and a wipe
+    // whenever the layout of the buffer changes or the counter wraps.
+    f.stream_merge = batch == 1 && f.max_splits > 1 && !(flags & SHAINET_ATTN_F_TICKET_MERGE) &&
+                     (long long)f.max_splits * hs.num_kv_heads <= (long long)ctx->sm_count * splitk_ctas_per_sm(hs);
+    if (f.stream_merge) {
+        const bool relayout = ctx->tickets_cap != cap_before || ctx->flags_offset != n_tickets;
+        if (relayout || ctx->epoch == 0xffffffffu) {
+            CU(cudaMemsetAsync(ctx->tickets, 0, ctx->tickets_cap * sizeof(unsigned), s));
+            ctx->epoch = 0;
+            ctx->flags_offset = n_tickets;
+        }
+        f.epoch = ++ctx->epoch;
+    }
     // A fused kernel may start while the previous fused kernel still runs; that
     // one can be appending the newest row of this very cache.
     f.unsafe_tail = ctx->last_fused ? 1 : 0;

@@ -547,6 +547,111 @@ __device__ void merge_partials(const float* po, const float* pml, size_t stride,
     }
 }
 
+// ---- streaming merge (single sequence, whole grid co-resident) ----
+// Every CTA publishes its partial and raises a flag (the launch's epoch value,
+// so flags never need clearing).  The first min(G, splits) CTAs of a kv head
+// each take one query head: they wait - bounded - for all flags of the kv head
+// and fold that head's partials.  Compared with the ticket scheme this removes
+// one fence + atomic + L2 round trip from the end of the kernel and spreads the
+// merge over G CTAs.  It needs all CTAs of the grid to be resident at once,
+// which the host guarantees before selecting it.
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ bool spin_until_equal(const unsigned* p, unsigned want, AttnStatus* status, int where) {
+    if (ld_acquire(p) == want) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            if (ld_acquire(p) == want) return true;
+            __nanosleep(40);
+        }
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = where;
+            return false;
+        }
+    }
+}
+
+// All partials [first .. first+count) of one query head, folded by the whole CTA.
+template <int HD, int THREADS>
+__device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int count, float* smem, float* out_row,
+                               float* lse_out) {
+    constexpr int D4 = HD / 4;
+    constexpr int NPG = THREADS / D4;   // partial groups walking the splits in parallel
+    const int pg = threadIdx.x / D4, d4 = threadIdx.x - pg * D4;
+    const float2* ml = reinterpret_cast<const float2*>(pml) + e0;
+    const float4* src = reinterpret_cast<const float4*>(po + e0 * HD) + d4;
+    float M = -INFINITY, L = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (pg < NPG) {
+        for (int s0 = pg; s0 < count; s0 += NPG * 4) {
+            float2 mv[4];
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int sidx = s0 + k * NPG;
+                const bool in = sidx < count;
+                mv[k] = in ? __ldcg(ml + sidx) : make_float2(-INFINITY, 0.f);
+                v[k] = in ? __ldcg(src + (size_t)sidx * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float Mc = M;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) Mc = fmaxf(Mc, mv[k].x);
+            const float resc = (M == -INFINITY) ? 0.0f : exp2f((M - Mc) * LOG2E);
+            L *= resc;
+            acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
+            M = Mc;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float wt = (mv[k].x == -INFINITY) ? 0.0f : exp2f((mv[k].x - Mc) * LOG2E);
+                L = fmaf(wt, mv[k].y, L);
+                acc.x = fmaf(wt, v[k].x, acc.x);
+                acc.y = fmaf(wt, v[k].y, acc.y);
+                acc.z = fmaf(wt, v[k].z, acc.z);
+                acc.w = fmaf(wt, v[k].w, acc.w);
+            }
+        }
+        float4* sa = reinterpret_cast<float4*>(smem);                 // [NPG][D4]
+        float2* sm2 = reinterpret_cast<float2*>(smem + NPG * D4 * 4);  // [NPG][D4]
+        sa[pg * D4 + d4] = acc;
+        sm2[pg * D4 + d4] = make_float2(M, L);
+    }
+    __syncthreads();
+    if (pg == 0) {
+        const float4* sa = reinterpret_cast<const float4*>(smem);
+        const float2* sm2 = reinterpret_cast<const float2*>(smem + NPG * D4 * 4);
+        float Mt = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < NPG; ++g) Mt = fmaxf(Mt, sm2[g * D4 + d4].x);
+        float Lt = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int g = 0; g < NPG; ++g) {
+            const float2 q = sm2[g * D4 + d4];
+            const float wt = (q.x == -INFINITY) ? 0.0f : exp2f((q.x - Mt) * LOG2E);
+            const float4 a4 = sa[g * D4 + d4];
+            Lt = fmaf(wt, q.y, Lt);
+            o.x = fmaf(wt, a4.x, o.x);
+            o.y = fmaf(wt, a4.y, o.y);
+            o.z = fmaf(wt, a4.z, o.z);
+            o.w = fmaf(wt, a4.w, o.w);
+        }
+        const float inv = 1.0f / Lt;
+        *(reinterpret_cast<float4*>(out_row) + d4) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        if (lse_out && d4 == 0) *lse_out = Mt + logf(Lt);
+    }
+    __syncthreads();
+}
+
 // The calling CTA has published something and takes a ticket; true for the
 // CTA that took the last of `expected` tickets (it also resets the counter for
 // the next launch).  Nobody waits for anybody.
@@ -727,6 +832,25 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
     }
     if (nsplit_here == 1) return;
+    if (a.stream_merge) {
+        unsigned* flags = a.flags + ((size_t)r * KV + kv_h) * a.max_splits;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release(flags + split, a.epoch);
+        const int nm = min(G, nsplit_here);
+        if (split >= nm) return;
+        bool seen = true;
+        for (int sidx = threadIdx.x; sidx < nsplit_here; sidx += C::THREADS)
+            seen = spin_until_equal(flags + sidx, a.epoch, a.status, 3) && seen;
+        if (!__syncthreads_and(seen)) return;
+        __threadfence();
+        for (int g = split; g < G; g += nm) {
+            const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
+            merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
+                                           a.lse_out ? a.lse_out + hrow : nullptr);
+        }
+        return;
+    }
     // ---- two-level merge by "last finisher" tickets: the last CTA of each group
     // of MERGE_GROUP splits folds the group, the last group folds the groups ----
     const int ngroups = (nsplit_here + MERGE_GROUP - 1) / MERGE_GROUP;

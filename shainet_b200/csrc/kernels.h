@@ -87,6 +87,9 @@ struct FusedArgs {
     int chunk_rows;
     int max_splits;
     int max_groups;
+    unsigned* flags;       // [batch*num_kv_heads, max_splits] streaming-merge flags (epoch values)
+    unsigned epoch;        // this launch's flag value, never 0, never reused while old flags exist
+    int stream_merge;      // merge by flag-polling CTAs (single sequence, grid fully resident) instead of tickets
     int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
     int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
     int pos_delta;         // RoPE position of the new token minus the rows already cached (0 unless the sequence is split over ranks)

@@ -137,7 +137,7 @@ def test_decode_error_against_f64_truth(ctx):
     g.close()
 
 
-@pytest.mark.parametrize("fused", [True, False], ids=["fused", "three_launches"])
+@pytest.mark.parametrize("fused", ["fused", "fused_tickets", "three_launches"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("G", [1, 2, 4, 8, 16])
 def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G, fused):
@@ -145,11 +145,11 @@ def test_splitk_every_group_size_and_ragged_lengths(ctx, hd, G, fused):
     template instance, lengths around the tile and split boundaries (empty cache,
     1 row, partial tiles, exact multiples)."""
     import shainet_b200 as S
-    flags = S.F_SPLITK | (0 if fused else S.F_UNFUSED)
+    flags = S.F_SPLITK | {"fused": 0, "fused_tickets": S.F_TICKET_MERGE, "three_launches": S.F_UNFUSED}[fused]
     rng = np.random.default_rng(hd * 100 + G)
     KV = 2
     shape = dict(H=KV * G, KV=KV, hd=hd, theta=10000.0)
-    for L in (0, 1, 7, 8, 63, 64, 65, 255, 1031):
+    for L in (0, 1, 7, 8, 63, 64, 65, 255, 1031, 9000):
         o, g = make_pair(ctx, shape, rng)
         if L:
             q, k, v = qkv(rng, shape, L)
