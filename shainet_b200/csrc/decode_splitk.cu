@@ -42,6 +42,15 @@ namespace shainet {
 
 namespace {
 
+#ifdef SK_TIMELINE
+// debug builds only: per-CTA timestamps of the fused kernel, [launch % 64][cta][8]
+__device__ unsigned long long g_timeline[64 * 320 * 8];
+__device__ unsigned g_timeline_launch;
+#define TL_MARK(k, tid) do { if (threadIdx.x == (tid)) g_timeline[((a.epoch & 63) * 320 + blockIdx.y * gridDim.x + blockIdx.x) * 8 + (k)] = globaltimer_ns(); } while (0)
+#else
+#define TL_MARK(k, tid) do { } while (0)
+#endif
+
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int SK_MAX_STAGES = 32;
@@ -587,17 +596,18 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
                                float* lse_out) {
     constexpr int D4 = HD / 4;
     constexpr int NPG = THREADS / D4;   // partial groups walking the splits in parallel
+    constexpr int MAXB = 16;            // partials a thread requests before it uses any: one L2 round trip for <= NPG*16 splits
     const int pg = threadIdx.x / D4, d4 = threadIdx.x - pg * D4;
     const float2* ml = reinterpret_cast<const float2*>(pml) + e0;
     const float4* src = reinterpret_cast<const float4*>(po + e0 * HD) + d4;
     float M = -INFINITY, L = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (pg < NPG) {
-        for (int s0 = pg; s0 < count; s0 += NPG * 4) {
-            float2 mv[4];
-            float4 v[4];
+        for (int s0 = pg; s0 < count; s0 += NPG * MAXB) {
+            float2 mv[MAXB];
+            float4 v[MAXB];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < MAXB; ++k) {
                 const int sidx = s0 + k * NPG;
                 const bool in = sidx < count;
                 mv[k] = in ? __ldcg(ml + sidx) : make_float2(-INFINITY, 0.f);
@@ -605,13 +615,13 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
             }
             float Mc = M;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) Mc = fmaxf(Mc, mv[k].x);
+            for (int k = 0; k < MAXB; ++k) Mc = fmaxf(Mc, mv[k].x);
             const float resc = (M == -INFINITY) ? 0.0f : exp2f((M - Mc) * LOG2E);
             L *= resc;
             acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
             M = Mc;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < MAXB; ++k) {
                 const float wt = (mv[k].x == -INFINITY) ? 0.0f : exp2f((mv[k].x - Mc) * LOG2E);
                 L = fmaf(wt, mv[k].y, L);
                 acc.x = fmaf(wt, v[k].x, acc.x);
@@ -656,18 +666,18 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
 // CTA that took the last of `expected` tickets (it also resets the counter for
 // the next launch).  Nobody waits for anybody.
 __device__ __forceinline__ bool take_last_ticket(unsigned* ticket, int expected, int* flag) {
-    __threadfence();
+    // barrier, then one acquire-release atomic by thread 0: the CTA's stores are
+    // released with it, the other CTAs' stores are acquired by the last taker
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned t = atomicAdd(ticket, 1u);
+        unsigned t;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(ticket) : "memory");
         const int last = t == (unsigned)(expected - 1);
         if (last) *ticket = 0u;
         *flag = last;
     }
     __syncthreads();
-    const bool last = *flag != 0;
-    if (last) __threadfence();
-    return last;
+    return *flag != 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -676,40 +686,6 @@ __device__ __forceinline__ bool take_last_ticket(unsigned* ticket, int expected,
 // the append of k/v (the CTA whose slice ends at the new position); then the
 // split-K stream; then the last CTA of each (row, kv head) merges the splits.
 // ---------------------------------------------------------------------------
-
-// Sum of squares of one row in the reference's order: sequential fp32, ascending
-// column, multiply and add each rounded (one lane per row; several rows run in
-// neighbouring lanes), then f32(1 / sqrt(f64(ss / hd) + eps)).
-template <int HD>
-__device__ __forceinline__ float inv_rms_sequential(const float* row, double eps) {
-    float ss = 0.0f;
-#pragma unroll 16
-    for (int d = 0; d < HD; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
-    const float mean = __fdiv_rn(ss, (float)HD);
-    return (float)(1.0 / sqrt((double)mean + eps));
-}
-
-// Half-split rotation of one row in place (optionally after scaling by the
-// row's inverse RMS and the norm weight), by one warp.  Same arithmetic as
-// prep_append_kernel.
-template <int HD>
-__device__ __forceinline__ void scale_rope_row(float* row, const float* w, float inv, const float* inv_freq, float fpos,
-                                               int lane) {
-    constexpr int half = HD / 2;
-#pragma unroll
-    for (int i = lane; i < half; i += 32) {
-        float x0 = row[i], x1 = row[i + half];
-        if (w) {
-            x0 = __fmul_rn(__fmul_rn(x0, inv), w[i]);
-            x1 = __fmul_rn(__fmul_rn(x1, inv), w[i + half]);
-        }
-        const float angle = __fmul_rn(fpos, inv_freq[i]);
-        float s, c;
-        sincosf(angle, &s, &c);
-        row[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        row[i + half] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
-    }
-}
 
 template <int HD, int G, class C>
 __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_kernel(FusedArgs a) {
@@ -736,6 +712,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
     const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TL_MARK(0, 0);
     init_barriers(sm);
 
     WarpState<G> st;
@@ -745,63 +722,101 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         if (lane == 0) {
             const bool ok = produce_tiles<HD, C>(sm, kbase, vbase, rows, 0, n_early, a.status);
             grid_dependency_wait();
+            TL_MARK(1, C::NW * 32);
             grid_launch_dependents();
             if (ok) produce_tiles<HD, C>(sm, kbase, vbase, rows, n_early, ntiles, a.status);
+            TL_MARK(5, C::NW * 32);
         }
     } else {
         // ---------------- consumers ----------------
-        if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
+        // Everything that does not depend on this call's inputs happens before the
+        // wait for the previous grid: norm weights, and the rotation of this
+        // position (lane owns the pairs (i, i + HD/2), i = lane + 32k).
+        constexpr int PL = HD / 64;                  // rotation pairs per lane
+        constexpr int MAXIT = (G + 2 + C::NW - 1) / C::NW;
         const float fpos = (float)(start + a.pos_delta);   // RoPE position of the new token
-        const int items = G + (owns_new ? 2 : 0);   // q rows of the group, then the new k row, then the new v row
-        auto item_row = [&](int it) { return it < G ? sm.qs + it * C::QS_STRIDE : (it == G ? sm.xk : sm.xv); };
-        // (1) raw rows (+ bias) into shared memory
-        for (int it = warp; it < items; it += C::NW) {
-            const float* src;
-            const float* bias;
-            if (it < G) {
-                const int h = kv_h * G + it;
-                src = a.q + ((size_t)r * H + h) * HD;
-                bias = a.b_q ? a.b_q + (size_t)h * HD : nullptr;
-            } else if (it == G) {
-                src = a.k_new + ((size_t)r * KV + kv_h) * HD;
-                bias = a.b_k ? a.b_k + (size_t)kv_h * HD : nullptr;
-            } else {
-                src = a.v_new + ((size_t)r * KV + kv_h) * HD;
-                bias = a.b_v ? a.b_v + (size_t)kv_h * HD : nullptr;
-            }
-            float* row = item_row(it);
+        float rc[PL], rs[PL], wq0[PL], wq1[PL], wk0[PL], wk1[PL];
 #pragma unroll
-            for (int d = lane; d < HD; d += 32) {
-                float x = src[d];
-                if (bias) x = __fadd_rn(x, bias[d]);
-                row[d] = x;
+        for (int k = 0; k < PL; ++k) {
+            const int i = lane + 32 * k;
+            sincosf(__fmul_rn(fpos, a.inv_freq[i]), &rs[k], &rc[k]);
+            wq0[k] = a.q_norm ? a.q_norm[i] : 1.0f;
+            wq1[k] = a.q_norm ? a.q_norm[i + HD / 2] : 1.0f;
+            wk0[k] = a.k_norm ? a.k_norm[i] : 1.0f;
+            wk1[k] = a.k_norm ? a.k_norm[i + HD / 2] : 1.0f;
+        }
+        if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
+        const int items = G + (owns_new ? 2 : 0);   // q rows of the group, then the new k row, then the new v row
+        // (1) all of this warp's rows in one round of loads: x[n][c] = column lane + 32c
+        float x[MAXIT][2 * PL];
+#pragma unroll
+        for (int n = 0; n < MAXIT; ++n) {
+            const int it = warp + n * C::NW;
+            if (it < items) {
+                const float* src;
+                const float* bias;
+                if (it < G) {
+                    const int h = kv_h * G + it;
+                    src = a.q + ((size_t)r * H + h) * HD;
+                    bias = a.b_q ? a.b_q + (size_t)h * HD : nullptr;
+                } else if (it == G) {
+                    src = a.k_new + ((size_t)r * KV + kv_h) * HD;
+                    bias = a.b_k ? a.b_k + (size_t)kv_h * HD : nullptr;
+                } else {
+                    src = a.v_new + ((size_t)r * KV + kv_h) * HD;
+                    bias = a.b_v ? a.b_v + (size_t)kv_h * HD : nullptr;
+                }
+#pragma unroll
+                for (int c = 0; c < 2 * PL; ++c) {
+                    x[n][c] = src[lane + 32 * c];
+                    if (bias) x[n][c] = __fadd_rn(x[n][c], bias[lane + 32 * c]);
+                }
             }
         }
-        // (2) per-row inverse RMS, one lane per row (only when a norm weight is set)
-        if (a.q_norm || a.k_norm) {
-            asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");
-            if (warp == 0 && lane <= G && lane < items && (lane < G ? a.q_norm : a.k_norm) != nullptr)
-                sm.inv[lane] = inv_rms_sequential<HD>(item_row(lane), a.eps);
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");
-        // (3) scale + rotate q and k rows in place; append k and v to the cache
-        for (int it = warp; it < items; it += C::NW) {
-            float* row = item_row(it);
+        // (2) norm (warp-tree sum of squares; the prefill kernel keeps the reference's
+        // sequential order, the two differ by the rounding of the sum), rotation with
+        // the reference's unfused arithmetic, then shared memory and, for k and v, the cache
+#pragma unroll
+        for (int n = 0; n < MAXIT; ++n) {
+            const int it = warp + n * C::NW;
+            if (it >= items) break;   // warp-uniform
+            float* row = it < G ? sm.qs + it * C::QS_STRIDE : (it == G ? sm.xk : sm.xv);
             if (it <= G) {
-                const float* w = it < G ? a.q_norm : a.k_norm;
-                scale_rope_row<HD>(row, w, w ? sm.inv[it] : 1.0f, a.inv_freq, fpos, lane);
-                __syncwarp();
+                const bool normed = (it < G ? a.q_norm : a.k_norm) != nullptr;
+                float inv = 1.0f;
+                if (normed) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 2 * PL; ++c) ss = fmaf(x[n][c], x[n][c], ss);
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(FULL, ss, off);
+                    inv = (float)(1.0 / sqrt((double)(ss / (float)HD) + a.eps));
+                }
+#pragma unroll
+                for (int k = 0; k < PL; ++k) {
+                    float x0 = x[n][k], x1 = x[n][k + PL];
+                    if (normed) {
+                        x0 = __fmul_rn(__fmul_rn(x0, inv), it < G ? wq0[k] : wk0[k]);
+                        x1 = __fmul_rn(__fmul_rn(x1, inv), it < G ? wq1[k] : wk1[k]);
+                    }
+                    x[n][k] = __fsub_rn(__fmul_rn(x0, rc[k]), __fmul_rn(x1, rs[k]));
+                    x[n][k + PL] = __fadd_rn(__fmul_rn(x1, rc[k]), __fmul_rn(x0, rs[k]));
+                }
             }
-            if (it >= G) {
+#pragma unroll
+            for (int c = 0; c < 2 * PL; ++c) row[lane + 32 * c] = x[n][c];
+            if (it >= G) {  // append to the cache
                 float* dst = (it == G ? sd.k : sd.v) + ((size_t)kv_h * sd.capacity + start) * HD;
 #pragma unroll
-                for (int d = lane; d < HD; d += 32) dst[d] = row[d];
+                for (int c = 0; c < 2 * PL; ++c) dst[lane + 32 * c] = x[n][c];
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");  // consumers only: qs/xk/xv complete
         ulonglong2 q[G][C::CPL];
         load_q<HD, G, C>(q, sm.qs, C::QS_STRIDE, lane & 15);
+        TL_MARK(2, 0);
         consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
+        TL_MARK(3, 0);
         if (owns_new && warp == (ntiles % C::NW)) {
             // the new token's own row, from shared memory (one valid row)
             f32x2* ps = reinterpret_cast<f32x2*>(sm.warp_scratch + warp * C::WARP_SCRATCH);
@@ -831,10 +846,12 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             }
         }
     }
+    TL_MARK(4, 0);
     if (nsplit_here == 1) return;
     if (a.stream_merge) {
         unsigned* flags = a.flags + ((size_t)r * KV + kv_h) * a.max_splits;
-        __threadfence();
+        // The CTA barrier orders every thread's partial stores before thread 0's
+        // releasing store (release is cumulative), so no per-thread fence is needed.
         __syncthreads();
         if (threadIdx.x == 0) st_release(flags + split, a.epoch);
         const int nm = min(G, nsplit_here);
@@ -842,13 +859,13 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         bool seen = true;
         for (int sidx = threadIdx.x; sidx < nsplit_here; sidx += C::THREADS)
             seen = spin_until_equal(flags + sidx, a.epoch, a.status, 3) && seen;
-        if (!__syncthreads_and(seen)) return;
-        __threadfence();
+        if (!__syncthreads_and(seen)) return;   // acquiring loads + barrier: the partials are visible to the CTA
         for (int g = split; g < G; g += nm) {
             const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
             merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
                                            a.lse_out ? a.lse_out + hrow : nullptr);
         }
+        TL_MARK(6, 0);
         return;
     }
     // ---- two-level merge by "last finisher" tickets: the last CTA of each group
@@ -1125,3 +1142,8 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
     return 0;
 }
 
+#ifdef SK_TIMELINE
+extern "C" int shainet_debug_timeline(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, shainet::g_timeline, sizeof(unsigned long long) * 64 * 320 * 8);
+}
+#endif
