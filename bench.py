@@ -259,7 +259,21 @@ def run_ours(args, wl, rank, world, local_rank):
     split = sp.seq_parts > 1
     pay = qd + (Hl if split else 0)        # a rank's contribution per layer: outputs (+ log-sum-exp when the sequence is split)
     out_d = torch.empty(layers, pay, device=dev)
-    gathered = torch.empty(layers, world, pay, device=dev) if world > 1 else None
+    # Several ranks: every rank's fused kernel stores its head rows straight into all
+    # ranks' exchange buffers over NVLink (layout [layer][rank][pay]) and raises a flag;
+    # a one-warp kernel per layer waits for the flags.  --nccl-gather keeps the
+    # torch.distributed all-gather instead (also used when rows are not 16-byte multiples).
+    peer = world > 1 and pay % 4 == 0 and not args.nccl_gather
+    gathered = torch.empty(layers, world, pay, device=dev) if world > 1 and not peer else None
+    comm_base = None
+    if peer:
+        mine = ctx.comm_create(layers * world * pay)
+        handles = [None] * world
+        dist.all_gather_object(handles, mine)
+        ctx.comm_open(handles, rank)
+        comm_base = ctx.comm_data_ptr()
+        dist.barrier()
+    epoch = [0]
     full_d = torch.empty(layers, H * hd, device=dev) if split else None
     # Everything timed runs on one explicit (non-default) stream: the library is
     # handed its handle, and the CUDA events are recorded on it.
@@ -287,28 +301,52 @@ def run_ours(args, wl, rank, world, local_rank):
     set_lse = ctx.L.shainet_attn_ctx_set_lse_out
     merge = ctx.L.shainet_attn_merge_parts
     lse_ptrs = [vp(out_d[l, qd:].data_ptr()) for l in range(layers)] if split else None
-    gath_ptrs = [vp(gathered[l].data_ptr()) for l in range(layers)] if split else None
+    if split:
+        gath_ptrs = [vp(comm_base + l * world * pay * 4) if peer else vp(gathered[l].data_ptr()) for l in range(layers)]
+    set_target = ctx.L.shainet_attn_comm_set_target
+    comm_wait = ctx.L.shainet_attn_comm_wait
+    out_offs = [(l * world + rank) * pay for l in range(layers)]
     full_ptrs = [vp(full_d[l].data_ptr()) for l in range(layers)] if split else None
 
     def step(i, all_args=None):
         args = (all_args or dev_args)[i % NV]
+        epoch[0] += 1
+        ep = epoch[0]
         if not split:
             for l in range(layers):
+                if peer:
+                    rc = set_target(ctx.h, out_offs[l], -1, l, ep)
+                    if rc:
+                        S.check(rc)
                 rc = fwd_dev(*args[l])
                 if rc:
                     S.check(rc)
-                if world > 1:
-                    dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])   # head outputs before o_proj
+                if peer:
+                    rc = comm_wait(ctx.h, l, ep, args[l][9])              # head outputs of all ranks, before o_proj
+                    if rc:
+                        S.check(rc)
+                elif world > 1:
+                    dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
             return
         pos = ctx_len + i                   # the token's position; its k/v row goes to one rank of the group
         own = 1 if sp.owns_position(pos) else 0
         for l in range(layers):
             a = args[l]
-            set_lse(ctx.h, lse_ptrs[l])
+            if peer:
+                rc = set_target(ctx.h, out_offs[l], out_offs[l] + qd, l, ep)
+                if rc:
+                    S.check(rc)
+            else:
+                set_lse(ctx.h, lse_ptrs[l])
             rc = fwd_at(a[0], a[1], a[2], a[3], a[4], a[5], pos, own, a[7], a[8], a[9])
             if rc:
                 S.check(rc)
-            dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
+            if peer:
+                rc = comm_wait(ctx.h, l, ep, a[9])
+                if rc:
+                    S.check(rc)
+            else:
+                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
             rc = merge(ctx.h, gath_ptrs[l], world, sp.seq_parts, Hl, hd, full_ptrs[l], a[9])
             if rc:
                 S.check(rc)
@@ -389,7 +427,12 @@ def run_ours(args, wl, rank, world, local_rank):
         k_d[vi].copy_(hk[vi], non_blocking=True)
         v_d[vi].copy_(hv[vi], non_blocking=True)
         step(i)
-        ho_full.copy_((full_d if split else gathered.view(layers, -1)), non_blocking=True)
+        if peer and not split:
+            rc = ctx.L.shainet_attn_comm_read(ctx.h, 0, C.cast(ho_full.data_ptr(), FP), ho_full.numel(), vp(stream))
+            if rc:
+                S.check(rc)
+        else:
+            ho_full.copy_((full_d if split else gathered.view(layers, -1)), non_blocking=True)
         torch.cuda.current_stream().synchronize()
     for i in range(W_e2e):
         host_step(i)
@@ -423,7 +466,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "layers": layers, "num_heads": H, "num_kv_heads": KV, "head_dim": hd,
-                       "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); all-gather of head outputs per layer",
+                       "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); " + ("no exchange" if world == 1 else ("head outputs stored into every rank's buffer by the decode kernel (peer stores over NVLink), one flag wait per layer" if peer else "torch.distributed all-gather of head outputs per layer")),
                        "l2": "working set per step (all layers' K/V) is far larger than L2; no flush needed",
                        "host_enqueue_ms_per_step": t_enq * 1e3 / K,
                        "hbm_gbs_whole_step_per_gpu": bytes_per_launch * layers / (ms / K / 1e3) / 1e9},
@@ -441,7 +484,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "e2e": {"value": K_e2e / e2e_s, "unit": "tokens/s", "steps": K_e2e,
                     "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz,
                     "d2h_bytes_per_step": layers * (qd if world == 1 else H * hd) * esz},
-            "gpu_launches": layers * K,
+            "gpu_launches": layers * K * (2 if peer else 1) + (layers * K if split else 0),
         }
         if prefill is not None:
             line["prefill"] = prefill
@@ -474,6 +517,8 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging / profiling)")
     ap.add_argument("--ctx", type=int, default=None, help="override the context length (debugging / profiling)")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="several ranks: gather head outputs with torch.distributed instead of the kernel's peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (cfg3 shape) block of the JSON line")
     args = ap.parse_args()

@@ -17,6 +17,8 @@ _F = C.POINTER(C.c_float)
 _P = C.c_void_p
 
 # name -> (restype, argtypes); every symbol include/shainet_attn.h declares
+COMM_HANDLE_BYTES = 64  # SHAINET_ATTN_COMM_HANDLE_BYTES
+
 SIGNATURES = {
     "shainet_attn_version": (C.c_int, []),
     "shainet_attn_device_count": (C.c_int, []),
@@ -47,6 +49,12 @@ SIGNATURES = {
     "shainet_attn_forward_dev_at": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_float, C.c_uint, _P]),
     "shainet_attn_ctx_set_lse_out": (C.c_int, [_P, _P]),
     "shainet_attn_merge_parts": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "shainet_attn_comm_create": (C.c_int, [_P, C.c_size_t, _P]),
+    "shainet_attn_comm_open": (C.c_int, [_P, _P, C.c_int, C.c_int]),
+    "shainet_attn_comm_set_target": (C.c_int, [_P, C.c_longlong, C.c_longlong, C.c_int, C.c_uint]),
+    "shainet_attn_comm_wait": (C.c_int, [_P, C.c_int, C.c_uint, _P]),
+    "shainet_attn_comm_read": (C.c_int, [_P, C.c_longlong, C.POINTER(C.c_float), C.c_size_t, _P]),
+    "shainet_attn_comm_data_ptr": (C.c_int, [_P, C.POINTER(_P)]),
     "shainet_attn_forward_batched_dev": (C.c_int, [_P, C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_float,
                                                    C.c_uint, _P]),
     "shainet_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _P]),

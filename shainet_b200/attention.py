@@ -75,6 +75,36 @@ class AttnContext:
         check(self.L.shainet_attn_merge_parts(self.h, gathered_ptr, world, seq_parts, heads_per_rank, head_dim, out_ptr,
                                               _stream_arg(stream)))
 
+    # ---- exchange of head outputs between the GPUs of one box ----
+    def comm_create(self, data_floats: int) -> bytes:
+        """Allocate this rank's exchange buffer; returns its inter-process handle."""
+        buf = C.create_string_buffer(_lib.COMM_HANDLE_BYTES)
+        check(self.L.shainet_attn_comm_create(self.h, data_floats, buf))
+        return buf.raw
+
+    def comm_open(self, handles, rank: int):
+        """Map the other ranks' exchange buffers; `handles` in rank order (own included)."""
+        blob = b"".join(handles)
+        assert len(blob) == _lib.COMM_HANDLE_BYTES * len(handles)
+        check(self.L.shainet_attn_comm_open(self.h, blob, len(handles), rank))
+
+    def comm_set_target(self, out_offset: int, lse_offset: int, flag_index: int, epoch: int):
+        """Arm the next fused decode call to store its head rows (and log-sum-exp values when
+        lse_offset >= 0) into every rank's buffer and then raise flag [flag_index][rank] = epoch."""
+        check(self.L.shainet_attn_comm_set_target(self.h, out_offset, lse_offset, flag_index, epoch))
+
+    def comm_wait(self, flag_index: int, epoch: int, stream=None):
+        check(self.L.shainet_attn_comm_wait(self.h, flag_index, epoch, _stream_arg(stream)))
+
+    def comm_data_ptr(self) -> int:
+        p = C.c_void_p()
+        check(self.L.shainet_attn_comm_data_ptr(self.h, C.byref(p)))
+        return p.value
+
+    def comm_read(self, offset: int, host: np.ndarray, stream=None):
+        assert host.dtype == np.float32 and host.flags.c_contiguous
+        check(self.L.shainet_attn_comm_read(self.h, offset, _fp(host), host.size, _stream_arg(stream)))
+
     def timing_enable(self, on: bool):
         check(self.L.shainet_attn_ctx_timing_enable(self.h, int(on)))
 

@@ -46,6 +46,7 @@ int fail_cuda(cudaError_t e, const char* what) {
 constexpr int SEQ_RING = 8;           // in-flight descriptor uploads of batched decode
 constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
 constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
+constexpr size_t COMM_FLAG_BYTES = 16384;  // flag words at the start of an exchange buffer
 constexpr int TENSOR_MIN_T = 64;      // rows per call from which the tensor-core prefill kernel takes over
 
 struct DevBuf {
@@ -78,6 +79,16 @@ struct shainet_attn_ctx {
     size_t flags_offset = ~(size_t)0;   // where the flags start inside `tickets` (they move with the head shape)
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
     float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
+    // exchange buffer shared with the other ranks of the box (IPC); flags first, then data
+    unsigned char* comm_base = nullptr;
+    size_t comm_data_floats = 0;
+    int comm_world = 0, comm_rank = 0;
+    unsigned char* comm_peer[MAX_PEERS] = {};
+    unsigned* comm_done_ticket = nullptr;
+    bool gather_armed = false;          // the next fused decode call delivers to the peers
+    long long gather_out_off = 0, gather_lse_off = -1;
+    int gather_flag = 0;
+    unsigned gather_epoch = 0;
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool;  // reusable pairs
@@ -197,6 +208,7 @@ int check_status(shainet_attn_ctx* ctx) {
         ctx->status_host->code = DEV_OK;
         ctx->status_host->where = 0;
         if (ctx->tickets) cudaMemset(ctx->tickets, 0, ctx->tickets_cap * sizeof(unsigned));  // an unwound kernel may leave counts
+        if (ctx->comm_done_ticket) cudaMemset(ctx->comm_done_ticket, 0, sizeof(unsigned));
         return fail(SHAINET_ATTN_E_DEVICE_WAIT, "a kernel gave up on a bounded wait (site %d)", where);
     }
     return SHAINET_ATTN_OK;
@@ -336,6 +348,10 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     int rc;
     if (!fused && (pos_delta != 0 || no_append))
         return fail(SHAINET_ATTN_E_UNSUPPORTED, "a split sequence is served by the fused decode kernel only (head_dim 64/128, group size 1/2/4/8/16)");
+    if (!fused && ctx->gather_armed) {
+        ctx->gather_armed = false;
+        return fail(SHAINET_ATTN_E_UNSUPPORTED, "peer delivery is done by the fused decode kernel only (one new token, head_dim 64/128)");
+    }
     if (!fused) {
         ctx->last_fused = false;
         rc = grow(ctx->q_rot, (size_t)batch * T * hs.num_heads * hs.head_dim, s);
@@ -421,6 +437,27 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     f.pos_delta = pos_delta;
     f.no_append = no_append;
     f.lse_out = ctx->lse_out;
+    f.gather.world = 0;
+    if (ctx->gather_armed) {
+        ctx->gather_armed = false;
+        if (!f.stream_merge)
+            return fail(SHAINET_ATTN_E_UNSUPPORTED, "peer delivery needs the flag-merged single-sequence decode kernel (context too short, batched, or tickets forced)");
+        const size_t need = (size_t)ctx->gather_out_off + (size_t)hs.num_heads * hs.head_dim;
+        if (need > ctx->comm_data_floats || (ctx->gather_lse_off >= 0 && (size_t)ctx->gather_lse_off + hs.num_heads > ctx->comm_data_floats))
+            return fail(SHAINET_ATTN_E_INVALID, "peer delivery target outside the exchange buffer");
+        GatherTarget& gt = f.gather;
+        gt.world = ctx->comm_world;
+        gt.rank = ctx->comm_rank;
+        for (int p = 0; p < ctx->comm_world; ++p) {
+            gt.peer[p] = reinterpret_cast<float*>(ctx->comm_peer[p] + COMM_FLAG_BYTES);
+            gt.peer_flags[p] = reinterpret_cast<unsigned*>(ctx->comm_peer[p]);
+        }
+        gt.out_offset = ctx->gather_out_off;
+        gt.lse_offset = ctx->gather_lse_off;
+        gt.flag_index = ctx->gather_flag;
+        gt.epoch = ctx->gather_epoch;
+        gt.done_ticket = ctx->comm_done_ticket;
+    }
     std::pair<cudaEvent_t, cudaEvent_t> ev{};
     if (ctx->timing) {
         if (!ctx->ev_pool.empty()) {
@@ -522,6 +559,10 @@ int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
     if (c->seq_host) cudaFreeHost(c->seq_host);
     if (c->seq_dev) cudaFree(c->seq_dev);
     if (c->tickets) cudaFree(c->tickets);
+    for (int p = 0; p < c->comm_world; ++p)
+        if (p != c->comm_rank && c->comm_peer[p]) cudaIpcCloseMemHandle(c->comm_peer[p]);
+    if (c->comm_base) cudaFree(c->comm_base);
+    if (c->comm_done_ticket) cudaFree(c->comm_done_ticket);
     for (int i = 0; i < SEQ_RING; ++i)
         if (c->seq_ev[i]) cudaEventDestroy(c->seq_ev[i]);
     for (auto* v : {&c->timed, &c->ev_pool})
@@ -828,6 +869,91 @@ int shainet_attn_merge_parts(shainet_attn_ctx* ctx, const float* gathered_dev, i
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
     ctx->last_fused = false;
     CU(launch_merge_parts(gathered_dev, world, seq_parts, heads_per_rank, head_dim, out_full_dev, s));
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_create(shainet_attn_ctx* ctx, size_t data_floats, void* handle_out) {
+    if (!ctx || !handle_out) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "exchange buffer already created");
+    DeviceGuard g(ctx->device);
+    const size_t bytes = COMM_FLAG_BYTES + data_floats * sizeof(float);
+    CU(cudaMalloc(&ctx->comm_base, bytes));
+    CU(cudaMemset(ctx->comm_base, 0, bytes));
+    CU(cudaMalloc(&ctx->comm_done_ticket, sizeof(unsigned)));
+    CU(cudaMemset(ctx->comm_done_ticket, 0, sizeof(unsigned)));
+    ctx->comm_data_floats = data_floats;
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, ctx->comm_base));
+    static_assert(sizeof(h) == SHAINET_ATTN_COMM_HANDLE_BYTES, "handle size");
+    memcpy(handle_out, &h, sizeof h);
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_open(shainet_attn_ctx* ctx, const void* handles, int world, int rank) {
+    if (!ctx || !handles) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (!ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "create the exchange buffer first");
+    if (world < 1 || world > MAX_PEERS || rank < 0 || rank >= world) return fail(SHAINET_ATTN_E_INVALID, "bad world/rank %d/%d", world, rank);
+    if (ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers already opened");
+    DeviceGuard g(ctx->device);
+    for (int p = 0; p < world; ++p) {
+        if (p == rank) {
+            ctx->comm_peer[p] = ctx->comm_base;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const unsigned char*>(handles) + (size_t)p * sizeof h, sizeof h);
+        void* ptr = nullptr;
+        CU(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        ctx->comm_peer[p] = static_cast<unsigned char*>(ptr);
+    }
+    ctx->comm_world = world;
+    ctx->comm_rank = rank;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_set_target(shainet_attn_ctx* ctx, long long out_offset_floats, long long lse_offset_floats,
+                                 int flag_index, unsigned epoch) {
+    if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    if (!ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers are not opened");
+    if (out_offset_floats < 0 || out_offset_floats % 4 != 0) return fail(SHAINET_ATTN_E_INVALID, "output offset must be a non-negative multiple of 4 floats");
+    if (flag_index < 0 || (size_t)(flag_index + 1) * ctx->comm_world * sizeof(unsigned) > COMM_FLAG_BYTES)
+        return fail(SHAINET_ATTN_E_INVALID, "flag index %d out of range", flag_index);
+    ctx->gather_out_off = out_offset_floats;
+    ctx->gather_lse_off = lse_offset_floats;
+    ctx->gather_flag = flag_index;
+    ctx->gather_epoch = epoch;
+    ctx->gather_armed = true;
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_wait(shainet_attn_ctx* ctx, int flag_index, unsigned epoch, void* stream) {
+    if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    if (!ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers are not opened");
+    if (flag_index < 0 || (size_t)(flag_index + 1) * ctx->comm_world * sizeof(unsigned) > COMM_FLAG_BYTES)
+        return fail(SHAINET_ATTN_E_INVALID, "flag index %d out of range", flag_index);
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    CU(launch_gather_wait(reinterpret_cast<const unsigned*>(ctx->comm_base) + (size_t)flag_index * ctx->comm_world,
+                          ctx->comm_world, epoch, ctx->status_dev, s));
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream) {
+    if (!ctx || !host_dst) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (!ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "no exchange buffer");
+    if (offset_floats < 0 || (size_t)offset_floats + floats > ctx->comm_data_floats)
+        return fail(SHAINET_ATTN_E_INVALID, "range outside the exchange buffer");
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    CU(cudaMemcpyAsync(host_dst, reinterpret_cast<const float*>(ctx->comm_base + COMM_FLAG_BYTES) + offset_floats,
+                       floats * sizeof(float), cudaMemcpyDeviceToHost, s));
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_data_ptr(shainet_attn_ctx* ctx, float** data_dev) {
+    if (!ctx || !data_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (!ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "no exchange buffer");
+    *data_dev = reinterpret_cast<float*>(ctx->comm_base + COMM_FLAG_BYTES);
     return SHAINET_ATTN_OK;
 }
 

@@ -593,7 +593,7 @@ __device__ __forceinline__ bool spin_until_equal(const unsigned* p, unsigned wan
 // All partials [first .. first+count) of one query head, folded by the whole CTA.
 template <int HD, int THREADS>
 __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int count, float* smem, float* out_row,
-                               float* lse_out) {
+                               float* lse_out, const GatherTarget& gt, size_t head_index) {
     constexpr int D4 = HD / 4;
     constexpr int NPG = THREADS / D4;   // partial groups walking the splits in parallel
     constexpr int MAXB = 16;            // partials a thread requests before it uses any: one L2 round trip for <= NPG*16 splits
@@ -656,8 +656,14 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
             o.w = fmaf(wt, a4.w, o.w);
         }
         const float inv = 1.0f / Lt;
-        *(reinterpret_cast<float4*>(out_row) + d4) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        const float4 res = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+        *(reinterpret_cast<float4*>(out_row) + d4) = res;
         if (lse_out && d4 == 0) *lse_out = Mt + logf(Lt);
+        // the same row into every rank's exchange buffer: plain stores to peer memory
+        for (int p = 0; p < gt.world; ++p) {
+            *(reinterpret_cast<float4*>(gt.peer[p] + gt.out_offset + head_index * HD) + d4) = res;
+            if (gt.lse_offset >= 0 && d4 == 0) gt.peer[p][gt.lse_offset + head_index] = Mt + logf(Lt);
+        }
     }
     __syncthreads();
 }
@@ -863,7 +869,28 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         for (int g = split; g < G; g += nm) {
             const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
             merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
-                                           a.lse_out ? a.lse_out + hrow : nullptr);
+                                           a.lse_out ? a.lse_out + hrow : nullptr, a.gather, hrow);
+        }
+        if (a.gather.world > 0) {
+            // The merging CTA that finishes last raises this rank's flag in every
+            // peer's buffer.  The CTA barrier orders all threads' peer stores before
+            // thread 0's system-scope fence (fences are cumulative); the ticket is
+            // the local rendezvous (nobody waits), and the last taker's releasing
+            // store publishes every CTA's rows to the peers.
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
+                unsigned t;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(a.gather.done_ticket) : "memory");
+                if (t == (unsigned)(nm * KV * a.batch - 1)) {
+                    *a.gather.done_ticket = 0u;
+                    asm volatile("fence.acq_rel.sys;" ::: "memory");
+                    for (int p = 0; p < a.gather.world; ++p)
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.gather.peer_flags[p] + (size_t)a.gather.flag_index * a.gather.world + a.gather.rank),
+                                     "r"(a.gather.epoch)
+                                     : "memory");
+                }
+            }
         }
         TL_MARK(6, 0);
         return;
@@ -948,6 +975,28 @@ cudaError_t dispatch_g(const A& a, F&& f) {
     }
 }
 
+// One thread per source rank polls this rank's own flag words (bounded).
+// Launched with programmatic stream serialization: the kernel behind it in the
+// stream may become resident at once and prefetch what does not depend on this
+// wait; its own grid-dependency wait then covers this kernel's completion.
+__global__ void gather_wait_kernel(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if ((int)threadIdx.x >= world) return;
+    const unsigned* p = flags_row + threadIdx.x;
+    const unsigned long long t0 = globaltimer_ns();
+    while (true) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+        if (v == epoch) return;
+        __nanosleep(100);
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 21;
+            return;
+        }
+    }
+}
+
 // out_full[(g*Hr + h)*hd + d] = sum_p w_p o_p / sum_p w_p with w_p = exp(lse_p - max lse)
 __global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_parts, int heads_per_rank, int head_dim,
                                    float* __restrict__ out_full) {
@@ -970,6 +1019,20 @@ __global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_p
 }
 
 }  // namespace
+
+cudaError_t launch_gather_wait(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status, cudaStream_t s) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_wait_kernel, flags_row, world, epoch, status);
+}
 
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
                                float* out_full, cudaStream_t s) {

@@ -62,6 +62,22 @@ struct AttnArgs {
     AttnStatus* status;
 };
 
+// Where the fused decode kernel also delivers its result when kv-head groups
+// are spread over GPUs: every rank's exchange buffer (plain peer stores over
+// NVLink, no multicast), at this rank's slot, followed by a release flag.
+constexpr int MAX_PEERS = 16;
+struct GatherTarget {
+    float* peer[MAX_PEERS];   // base of every rank's exchange buffer (this rank's own included)
+    unsigned* peer_flags[MAX_PEERS];  // flag words inside those buffers: [flag_index][source rank]
+    int world;                // 0 = no exchange
+    int rank;
+    long long out_offset;     // floats from a buffer's base to this rank's [heads*head_dim] slot
+    long long lse_offset;     // floats to this rank's [heads] log-sum-exp slot, or -1
+    int flag_index;
+    unsigned epoch;           // value stored to flags[flag_index][rank] of every peer once all heads are written
+    unsigned* done_ticket;    // local counter of merging CTAs that finished their peer stores (zero between launches)
+};
+
 // One decode token per sequence, everything in one launch (T == 1).
 struct FusedArgs {
     const float* q;        // [batch, num_heads*head_dim] raw projections
@@ -94,6 +110,7 @@ struct FusedArgs {
     int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
     int pos_delta;         // RoPE position of the new token minus the rows already cached (0 unless the sequence is split over ranks)
     int no_append;         // attend over the cached rows only: k_new/v_new are not used, nothing is appended
+    GatherTarget gather;   // peer delivery of the merged result (world == 0: none)
     float* lse_out;        // nullable [batch, num_heads]: max + ln(sum) of every row's softmax, for merging partial results
     AttnStatus* status;
 };
@@ -129,6 +146,9 @@ cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s);
 // form one head group.  out_full is [groups*heads_per_rank*head_dim].
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
                                float* out_full, cudaStream_t s);
+
+// Bounded wait until flags[flag_index][p] == epoch for every source rank p.
+cudaError_t launch_gather_wait(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status, cudaStream_t s);
 
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,

@@ -1,0 +1,173 @@
+"""Head outputs delivered into the ranks' exchange buffers by the fused decode
+kernel itself (shainet_attn_comm_*).  The one-rank case runs on any GPU box; the
+two-rank case needs two GPUs and runs as two child processes, one per GPU."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import DECODE_TOL, Q30, make_pair, qkv, rel_err
+from shainet_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    import shainet_b200 as S
+    c = S.AttnContext(0)
+    yield c
+    c.close()
+
+
+def test_self_delivery_matches_the_plain_output(ctx):
+    """world = 1: the kernel stores every head row and log-sum-exp into its own
+    exchange buffer at the armed offsets and raises its own flag; the values equal
+    what the same call leaves in `out`, and the oracle."""
+    import torch
+    import shainet_b200 as S
+    rng = np.random.default_rng(6001)
+    shape = Q30
+    H, hd = shape["H"], shape["hd"]
+    o, g = make_pair(ctx, shape, rng, initial_capacity=4096)
+    L0 = 3000
+    q, k, v = qkv(rng, shape, L0)
+    o.attend_cached(q, k, v, threads=8)
+    g.cache.import_(*o.export_cache())
+    slot = H * hd + H
+    handle = ctx.comm_create(3 * slot)
+    assert len(handle) == 64
+    ctx.comm_open([handle], 0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    out = torch.empty(H * hd, device=dev)
+    lse = torch.empty(H, device=dev)
+    for step in range(3):
+        q, k, v = qkv(rng, shape, 1)
+        ref = o.attend_cached(q, k, v, threads=8)[0]
+        tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (q, k, v))
+        off = step * slot
+        ctx.set_lse_out(lse.data_ptr())
+        ctx.comm_set_target(off, off + H * hd, flag_index=step, epoch=step + 7)
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
+        ctx.comm_wait(step, step + 7, stream)
+        got = np.empty(slot, np.float32)
+        ctx.comm_read(off, got, stream)
+        torch.cuda.synchronize()
+        ctx.sync()
+        ctx.set_lse_out(None)
+        assert np.array_equal(got[:H * hd], out.cpu().numpy())
+        assert np.array_equal(got[H * hd:], lse.cpu().numpy())
+        assert rel_err(got[:H * hd], ref) <= DECODE_TOL
+    # an armed delivery that the kernel cannot do is refused, and disarmed
+    q, k, v = qkv(rng, shape, 4)
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (q, k, v))
+    out4 = torch.empty(4 * H * hd, device=dev)
+    ctx.comm_set_target(0, -1, 0, 99)
+    with pytest.raises(S.ShainetAttnError) as ei:
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out4.data_ptr(), 4, stream=stream)
+    assert ei.value.code == _lib.E_UNSUPPORTED
+    g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out4.data_ptr(), 4, stream=stream)
+    ctx.sync()
+    ctx.comm_set_target(3 * slot, -1, 0, 1)   # one slot past the end of the buffer
+    with pytest.raises(S.ShainetAttnError) as ei:
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
+    assert ei.value.code == _lib.E_INVALID
+    g.close()
+
+
+def test_wait_for_a_flag_nobody_raises_reports_a_timeout():
+    """The flag wait is bounded: with no producer it gives up after about a second
+    and the next sync reports SHAINET_ATTN_E_DEVICE_WAIT; the context stays usable."""
+    import shainet_b200 as S
+    c = S.AttnContext(0)
+    c.comm_open([c.comm_create(64)], 0)
+    c.comm_wait(2, 12345)
+    with pytest.raises(S.ShainetAttnError) as ei:
+        c.sync()
+    assert ei.value.code == _lib.E_DEVICE_WAIT
+    c.sync()
+    c.close()
+
+
+WORKER = r"""
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.path.join(sys.argv[1], "tests")); sys.path.insert(0, sys.argv[1])
+import shainet_b200 as S
+from helpers import Q30, qkv, rel_err, DECODE_TOL
+from oracle import oracle as O
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo")
+shape = Q30
+H, KV, hd = shape["H"], shape["KV"], shape["hd"]
+sp = S.sharding.plan(world, rank, H, KV)
+Hl, KVl = sp.head_count, sp.kv_count
+rng = np.random.default_rng(6100)            # same stream on every rank: identical full inputs
+qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+o = O.OracleAttention(H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn)
+ctx = S.AttnContext(rank)
+g = S.LlamaAttention(ctx, Hl, KVl, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn, initial_capacity=4096)
+L0 = 3000
+q, k, v = qkv(rng, shape, L0)
+o.attend_cached(q, k, v, threads=8)
+kc, vc = o.export_cache()
+g.cache.import_(kc[sp.kv_begin:sp.kv_begin + KVl], vc[sp.kv_begin:sp.kv_begin + KVl])
+layers_slots = 2
+pay = Hl * hd
+mine = ctx.comm_create(layers_slots * world * pay)
+handles = [None] * world
+dist.all_gather_object(handles, mine)
+ctx.comm_open(handles, rank)
+dist.barrier()
+dev = torch.device("cuda", rank)
+stream = torch.cuda.current_stream().cuda_stream
+out = torch.empty(pay, device=dev)
+worst = 0.0
+for step in range(6):
+    q, k, v = qkv(rng, shape, 1)
+    ref = o.attend_cached(q, k, v, threads=8)[0]
+    ql = q.reshape(1, H, hd)[:, sp.head_begin:sp.head_begin + Hl].reshape(1, -1).copy()
+    kl = k.reshape(1, KV, hd)[:, sp.kv_begin:sp.kv_begin + KVl].reshape(1, -1).copy()
+    vl = v.reshape(1, KV, hd)[:, sp.kv_begin:sp.kv_begin + KVl].reshape(1, -1).copy()
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
+    slot = step % layers_slots
+    ctx.comm_set_target((slot * world + rank) * pay, -1, slot, step + 1)
+    g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
+    ctx.comm_wait(slot, step + 1, stream)
+    full = np.empty(world * pay, np.float32)
+    ctx.comm_read(slot * world * pay, full, stream)
+    torch.cuda.synchronize(); ctx.sync()
+    worst = max(worst, rel_err(full, ref))
+    dist.barrier()       # a slot is rewritten two steps later; the host barrier keeps this test's reads simple
+assert worst <= DECODE_TOL, worst
+dist.barrier()
+g.close(); ctx.close()
+print("RANK_OK", rank, worst)
+"""
+
+
+def test_two_ranks_deliver_to_each_other(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29541", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "RANK_OK" in o, f"rank {r}:\n{o[-3000:]}"
