@@ -113,7 +113,7 @@ struct SK {
     static constexpr int TILE_FLOATS = TW * HD;        // per tensor
     static constexpr int STAGE_FLOATS = 2 * TILE_FLOATS;
     static constexpr int RPI = 128 / HD;               // V rows covered by one warp-wide 128-bit load
-    static constexpr int WARP_SCRATCH = 2 * (32 + 16); // (p,p)[BR*G = 32] + (alpha,alpha)[G <= 16], as floats
+    static constexpr int WARP_SCRATCH = 2 * 2 * (32 + 16); // two buffers of (p,p)[BR*G = 32] + (alpha,alpha)[G <= 16], as floats
     static constexpr int THREADS = (NW + 1) * 32;
     static constexpr int CTAS_PER_SM = CTAS_;
     static constexpr bool MATH = MATH_;
@@ -204,6 +204,95 @@ __device__ __forceinline__ void load_q(ulonglong2 (&q)[G][C::CPL], const float* 
 #pragma unroll
         for (int c = 0; c < C::CPL; ++c)
             q[g][c] = *reinterpret_cast<const ulonglong2*>(qrow + (size_t)g * row_stride + (c * 16 + i16) * 4);
+}
+
+// Scores of one batch: acc2[rr*G + g] for the R rows of this half-warp; even and
+// odd columns accumulate in the two halves of a packed pair.
+template <int HD, int G, class C>
+__device__ __forceinline__ void score_batch(const float* ks, int base, int hw, int i16, const ulonglong2 (&q)[G][C::CPL],
+                                            f32x2 (&acc2)[16]) {
+#pragma unroll
+    for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
+#pragma unroll
+    for (int rr = 0; rr < C::R; ++rr) {
+        const float* krow = ks + (size_t)(base + hw * C::R + rr) * HD;
+#pragma unroll
+        for (int c = 0; c < C::CPL; ++c) {
+            const ulonglong2 kk = lds128x2(krow + (c * 16 + i16) * 4);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
+                acc2[rr * G + g] = ffma2(q[g][c].y, kk.y, acc2[rr * G + g]);
+            }
+        }
+    }
+}
+
+// A complete warp tile (all TW rows valid): no masks and no branches, so the
+// whole tile is one basic block; the next batch's score FMAs are issued before
+// the current batch's reduction and softmax, whose shuffle and exponent
+// latencies they hide.  p and alpha alternate between two scratch buffers, one
+// warp barrier per batch.
+template <int HD, int G, class C>
+__device__ __forceinline__ void consume_full_tile(const float* ks, const float* vs, const ulonglong2 (&q)[G][C::CPL],
+                                                  WarpState<G>& st, f32x2* scratch, int lane, float scale) {
+    const int i16 = lane & 15, hw = lane >> 4;
+    f32x2 acc2[16];
+    score_batch<HD, G, C>(ks, 0, hw, i16, q, acc2);
+#pragma unroll
+    for (int bb = 0; bb < C::NB; ++bb) {
+        const int base = bb * C::BR;
+        f32x2* ps = scratch + (bb & 1) * 48;
+        f32x2* as = ps + 32;
+        float acc[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float lo, hi;
+            unpack2(acc2[k], lo, hi);
+            acc[k] = lo + hi;
+        }
+        if (bb + 1 < C::NB) score_batch<HD, G, C>(ks, base + C::BR, hw, i16, q, acc2);
+        reduce_scatter16(acc, lane);
+        const float sc = acc[0] * scale;
+        float bmax = sc;
+#pragma unroll
+        for (int off = G; off < 32; off <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(FULL, bmax, off));
+        const float m_new = fmaxf(st.m, bmax);
+        const float alpha = exp2f((st.m - m_new) * LOG2E);  // 0 while the running max is -inf
+        const float p = exp2f((sc - m_new) * LOG2E);
+        st.l = fmaf(st.l, alpha, p);
+        st.m = m_new;
+        ps[lane] = pack2(p, p);  // index = row_in_batch * G + head
+        if (lane < G) as[lane] = pack2(alpha, alpha);
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const f32x2 al = as[g];
+            st.o[g][0] = fmul2(st.o[g][0], al);
+            st.o[g][1] = fmul2(st.o[g][1], al);
+        }
+#pragma unroll
+        for (int rr = 0; rr < C::BR; rr += C::RPI) {
+            const int rb = rr + (C::RPI == 2 ? hw : 0);
+            const int col = (C::RPI == 2 ? i16 : lane) * 4;
+            const ulonglong2 vv = lds128x2(vs + (size_t)(base + rb) * HD + col);
+            const f32x2* prow = ps + rb * G;
+            if constexpr (G >= 2) {
+#pragma unroll
+                for (int g = 0; g < G; g += 2) {
+                    const ulonglong2 pp = *reinterpret_cast<const ulonglong2*>(prow + g);
+                    st.o[g][0] = ffma2(pp.x, vv.x, st.o[g][0]);
+                    st.o[g][1] = ffma2(pp.x, vv.y, st.o[g][1]);
+                    st.o[g + 1][0] = ffma2(pp.y, vv.x, st.o[g + 1][0]);
+                    st.o[g + 1][1] = ffma2(pp.y, vv.y, st.o[g + 1][1]);
+                }
+            } else {
+                const f32x2 pg = prow[0];
+                st.o[0][0] = ffma2(pg, vv.x, st.o[0][0]);
+                st.o[0][1] = ffma2(pg, vv.y, st.o[0][1]);
+            }
+        }
+    }
 }
 
 // One warp tile: `nrows` valid rows of K (ks) and V (vs) in shared memory.
@@ -384,7 +473,15 @@ __device__ __forceinline__ void consume_slice(Smem<C>& sm, int ntiles, int rows,
         const float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
         const float* vs = ks + C::TILE_FLOATS;
         const int nrows = min(C::TW, rows - i * C::TW);
-        consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::MATH ? C::NB : 0);
+#ifndef SK_NO_FULL_TILE_PATH
+        if (C::MATH && nrows == C::TW) {
+            consume_full_tile<HD, G, C>(ks, vs, q, st, ps, lane, scale);
+        } else
+#endif
+        {
+            __syncwarp();
+            consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::MATH ? C::NB : 0);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty_bar[s]);
     }
