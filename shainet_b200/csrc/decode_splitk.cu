@@ -95,7 +95,11 @@ template <int HD, int G>
 struct SKDefault {
     static constexpr int BR = 2 * (16 / G);
     static constexpr int TW = BR > 8 ? BR : 8;                         // rows per warp tile
+#ifdef SK_NW5
+    static constexpr int NW = G >= SK_NW5 ? 5 : 4;                     // consumer warps
+#else
     static constexpr int NW = 4;                                       // consumer warps
+#endif
     static constexpr bool BIG = 2 * TW * HD * 4 > 16 * 1024;           // ring + extras would not fit twice per SM
     static constexpr int SMEM_KB = BIG ? 216 : 110;                    // 2 x (110 + 1 KB reserved) fits 227 KB
     static constexpr int CTAS_PER_SM = BIG ? 1 : 2;

@@ -28,6 +28,7 @@
 // mantissa bits, which is the 2e-3 tolerance class of this path.
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 #include "kernels.h"
 
 namespace shainet {
@@ -376,6 +377,293 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
 }
 
+// ---------------------------------------------------------------------------
+// Two query tiles per CTA.  Both tiles walk the same K/V tiles (two query heads
+// of one kv head over the same rows, or two consecutive row tiles of one head),
+// so every K/V byte fetched from L2 feeds twice the tensor work.  The output
+// accumulators stay in tensor memory: P.V accumulates straight into them, and a
+// row is rescaled there only when its running maximum has grown by more than
+// 2^8 since the scale in use was chosen (the probabilities then stay below 2^8,
+// far inside fp32 range; the final division by the row sum, kept at the same
+// scale, makes the result independent of the choice).  One warpgroup per tile
+// does the softmax, one thread issues all MMAs, one thread all TMA loads.
+// ---------------------------------------------------------------------------
+template <int HD>
+struct PF2 {
+    static constexpr int BM = 128;              // query rows per tile, two tiles per CTA
+    static constexpr int BN = 64;               // cache positions per K/V tile
+    static constexpr int NBOX = HD / 32;        // 128-byte column blocks per row
+    static constexpr int Q_BYTES = BM * HD * 4;   // one tile
+    static constexpr int KV_BYTES = BN * HD * 4;  // one of K, V
+    static constexpr int BAR_BYTES = 256;
+    static constexpr size_t SMEM_BYTES = 1024 + 2 * Q_BYTES + 3 * KV_BYTES + BAR_BYTES;  // Q x2, K x2, V x1
+    static constexpr int TMEM_S = 0;            // [tile][buffer] score/probability blocks of BN columns
+    static constexpr int TMEM_O = 4 * BN;       // [tile] output accumulators of HD columns
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int THREADS = 384;
+    static constexpr float RESCALE_STEP = 8.0f; // log2 units
+};
+
+struct Prefill2Args {
+    PrefillArgs p;
+    int pair_heads;  // 1: tiles = heads 2y, 2y+1 over the same rows; 0: tiles = row tiles 2x, 2x+1 of head y
+};
+
+template <int HD>
+__global__ void __launch_bounds__(PF2<HD>::THREADS, 1)
+attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                        const __grid_constant__ CUtensorMap tm_v, Prefill2Args pa) {
+    using C = PF2<HD>;
+    const PrefillArgs& a = pa.p;
+    extern __shared__ unsigned char pf_smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_s = base;                         // [2][Q_BYTES]
+    unsigned char* k_s = base + 2 * C::Q_BYTES;        // [2][KV_BYTES]
+    unsigned char* v_s = k_s + 2 * C::KV_BYTES;        // [KV_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + C::KV_BYTES);
+    uint64_t* q_full = bars;            // 1
+    uint64_t* k_full = bars + 1;        // 2
+    uint64_t* k_empty = k_full + 2;     // 2
+    uint64_t* v_full = k_empty + 2;     // 1
+    uint64_t* v_empty = v_full + 1;     // 1
+    uint64_t* s_full = v_empty + 1;     // [tile][buffer] = 4
+    uint64_t* p_full = s_full + 4;      // 4
+    uint64_t* o_done = p_full + 4;      // [tile] = 2
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the two tiles of this CTA; heaviest (latest rows) first
+    const int x = gridDim.x - 1 - blockIdx.x;
+    int th[2], ti0[2], trows[2], tn[2];
+    if (pa.pair_heads) {
+        th[0] = 2 * blockIdx.y;
+        th[1] = th[0] + 1;
+        ti0[0] = ti0[1] = x * C::BM;
+    } else {
+        th[0] = th[1] = blockIdx.y;
+        ti0[0] = 2 * x * C::BM;
+        ti0[1] = ti0[0] + C::BM;
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        trows[t] = max(0, min(C::BM, a.T - ti0[t]));
+        tn[t] = trows[t] > 0 ? (a.start + ti0[t] + trows[t] + C::BN - 1) / C::BN : 0;
+    }
+    const int n = max(tn[0], tn[1]);
+    const int kv_h = th[0] / (a.num_heads / a.num_kv_heads);
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&o_done[i], 1);
+        }
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+        }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const int active = (tn[0] > 0) + (tn[1] > 0);
+            mbar_arrive_expect_tx(q_full, active * C::Q_BYTES);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+                if (tn[t] > 0)
+                    for (int c = 0; c < C::NBOX; ++c)
+                        tma_load_2d(q_s + t * C::Q_BYTES + c * (C::BM * 128), &tm_q, th[t] * HD + 32 * c, ti0[t], q_full);
+            const int y0 = kv_h * a.capacity;
+            auto load_k = [&](int j) {
+                const int st = j & 1;
+                mbar_arrive_expect_tx(&k_full[st], C::KV_BYTES);
+                for (int c = 0; c < C::NBOX; ++c)
+                    tma_load_2d(k_s + st * C::KV_BYTES + c * (C::BN * 128), &tm_k, 32 * c, y0 + j * C::BN, &k_full[st]);
+            };
+            if (n > 0) load_k(0);
+            for (int j = 0; j < n; ++j) {
+                // K one tile ahead of V: the scores of tile j+1 are issued before P.V of tile j
+                if (j + 1 < n) {
+                    if (j + 1 >= 2 && !mbar_wait(&k_empty[(j + 1) & 1], (((j + 1) >> 1) - 1) & 1, a.status, 31)) break;
+                    load_k(j + 1);
+                }
+                if (j >= 1 && !mbar_wait(v_empty, (j - 1) & 1, a.status, 32)) break;
+                mbar_arrive_expect_tx(v_full, C::KV_BYTES);
+                for (int c = 0; c < C::NBOX; ++c)
+                    tma_load_2d(v_s + c * (C::BN * 128), &tm_v, 32 * c, y0 + j * C::BN, v_full);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_tf32(C::BM, C::BN, 0, 0);
+            constexpr uint32_t idesc_pv = idesc_tf32(C::BM, HD, 0, 1);
+            const uint32_t q_addr = smem_u32(q_s), k_addr0 = smem_u32(k_s), v_addr = smem_u32(v_s);
+            auto scores = [&](int j) {   // S[t][j & 1] = Q_t K(j)^T for the tiles that still see tile j
+                const uint32_t k_addr = k_addr0 + (j & 1) * C::KV_BYTES;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= tn[t]) continue;
+                    const uint32_t d = tmem + C::TMEM_S + (t * 2 + (j & 1)) * C::BN;
+#pragma unroll
+                    for (int kk = 0; kk < HD / 8; ++kk) {
+                        const uint64_t ad = smem_desc_sw128(q_addr + t * C::Q_BYTES + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
+                        const uint64_t bd = smem_desc_sw128(k_addr + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
+                        mma_ss_tf32(d, ad, bd, idesc_qk, kk > 0);
+                    }
+                    tc_commit(&s_full[t * 2 + (j & 1)]);
+                }
+                tc_commit(&k_empty[j & 1]);
+            };
+            bool ok = n > 0 && mbar_wait(q_full, 0, a.status, 33);
+            if (ok && (ok = mbar_wait(&k_full[0], 0, a.status, 34))) {
+                tc_fence_after();
+                scores(0);
+            }
+            for (int j = 0; ok && j < n; ++j) {
+                if (j + 1 < n) {
+                    if (!(ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, a.status, 35))) break;
+                    tc_fence_after();
+                    scores(j + 1);
+                }
+                if (!(ok = mbar_wait(v_full, j & 1, a.status, 36))) break;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= tn[t]) continue;
+                    const int b = j & 1;
+                    if (!(ok = mbar_wait(&p_full[t * 2 + b], (j >> 1) & 1, a.status, 37))) break;
+                    tc_fence_after();
+                    const uint32_t d = tmem + C::TMEM_O + t * HD;
+                    const uint32_t p = tmem + C::TMEM_S + (t * 2 + b) * C::BN;
+#pragma unroll
+                    for (int kk = 0; kk < C::BN / 8; ++kk) {
+                        const uint64_t bd = smem_desc(v_addr + kk * 1024, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
+                        mma_ts_tf32(d, p + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tc_commit(&o_done[t]);
+                }
+                if (!ok) break;
+                tc_commit(v_empty);
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- softmax: one warpgroup per tile, one query row per thread ----------------
+        const int t = (warp - 4) >> 2;
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const int row_pos = a.start + ti0[t] + r;       // last visible cache position of this row
+        const float sl2 = a.scale * PF_LOG2E * PF_TRUNC_GAIN;
+        const uint32_t oa = tmem + lane_addr + C::TMEM_O + t * HD;
+        const int nt = tn[t];
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < nt; ++j) {
+            const int b = j & 1;
+            if (!(ok = mbar_wait(&s_full[t * 2 + b], (j >> 1) & 1, a.status, 38))) break;
+            tc_fence_after();
+            uint32_t s0[32], s1[32];
+            const uint32_t sa = tmem + lane_addr + C::TMEM_S + (t * 2 + b) * C::BN;
+            tmem_ld32(sa, s0);
+            tmem_ld32(sa + 32, s1);
+            tmem_wait_ld();
+            const int c0 = j * C::BN;
+            if (c0 + C::BN - 1 > row_pos) {             // tile crosses this row's causal boundary
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    if (c0 + c > row_pos) s0[c] = 0xff800000u;        // -inf
+                    if (c0 + 32 + c > row_pos) s1[c] = 0xff800000u;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+            const float m_cand = fmaxf(m, mx * sl2);    // the positive factor commutes with max
+            // P.V of tile j-1 is awaited once per tile, so this barrier never runs more
+            // than one phase ahead of its waiters (a parity wait cannot tell two apart):
+            // here if the accumulator must be rescaled, otherwise after the exponentials,
+            // by which time it has long completed.
+            bool o_seen = j == 0;
+            if (__any_sync(0xffffffffu, m_cand - m > C::RESCALE_STEP)) {   // always on the first tile (m = -inf)
+                const float alpha = ex2_approx(m - m_cand);
+                m = m_cand;
+                l *= alpha;
+                if (j > 0) {
+                    // O_t is stable once P.V of tile j-1 has completed, and P.V of tile j
+                    // cannot start before this warpgroup hands over P
+                    if (!(ok = mbar_wait(&o_done[t], (j - 1) & 1, a.status, 39))) break;
+                    o_seen = true;
+                    tc_fence_after();
+#pragma unroll
+                    for (int ch = 0; ch < HD / 32; ++ch) {
+                        uint32_t v[32];
+                        tmem_ld32(oa + ch * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                        tmem_st32(oa + ch * 32, v);
+                    }
+                }
+            }
+            float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float p0 = ex2_approx(fmaf(__uint_as_float(s0[c]), sl2, -m));
+                const float p1 = ex2_approx(fmaf(__uint_as_float(s1[c]), sl2, -m));
+                s0[c] = __float_as_uint(p0);
+                s1[c] = __float_as_uint(p1);
+                sum0 += p0;
+                sum1 += p1;
+            }
+            l += sum0 + sum1;
+            tmem_st32(sa, s0);
+            tmem_st32(sa + 32, s1);
+            tmem_wait_st();
+            if (!o_seen && !(ok = mbar_wait(&o_done[t], (j - 1) & 1, a.status, 41))) break;
+            tc_fence_before();
+            mbar_arrive(&p_full[t * 2 + b]);
+        }
+        if (ok && nt > 0 && (ok = mbar_wait(&o_done[t], (nt - 1) & 1, a.status, 40))) {
+            tc_fence_after();
+            const float inv = PF_TRUNC_GAIN * PF_TRUNC_GAIN / l;   // V and P are both truncated by the tensor core
+            float* dst = a.out + ((size_t)(ti0[t] + r) * a.num_heads + th[t]) * HD;
+#pragma unroll
+            for (int ch = 0; ch < HD / 32; ++ch) {
+                uint32_t v[32];
+                tmem_ld32(oa + ch * 32, v);
+                tmem_wait_ld();
+                if (r < trows[t]) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 4)
+                        *reinterpret_cast<float4*>(dst + ch * 32 + d) =
+                            make_float4(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv,
+                                        __uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -408,13 +696,16 @@ bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, u
 
 template <int HD>
 cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
-    using C = PF<HD>;
+    using C1 = PF<HD>;
+    using C = PF2<HD>;
     static unsigned long long configured = 0;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 64 || !(configured >> dev & 1ull)) {
-        e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+        e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C1::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(attn_prefill_tc2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         if (dev < 64) configured |= 1ull << dev;
     }
@@ -425,7 +716,8 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
         !make_map(&tk, sd.k, HD, (uint64_t)KV * sd.capacity, HD, C::BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !make_map(&tv, sd.v, HD, (uint64_t)KV * sd.capacity, HD, C::BN, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
         return cudaErrorInvalidValue;
-    PrefillArgs p{};
+    Prefill2Args pa{};
+    PrefillArgs& p = pa.p;
     p.out = a.out;
     p.T = a.T;
     p.start = sd.start;
@@ -434,8 +726,18 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
     p.capacity = sd.capacity;
     p.scale = a.scale;
     p.status = a.status;
-    dim3 grid((a.T + C::BM - 1) / C::BM, H);
-    attn_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, p);
+    const int row_tiles = (a.T + C::BM - 1) / C::BM;
+    static const bool one_tile = getenv("SHAINET_PF_ONE_TILE") != nullptr;  // development switch
+    if (one_tile) {
+        dim3 grid(row_tiles, H);
+        attn_prefill_tc_kernel<HD><<<grid, C1::THREADS, C1::SMEM_BYTES, s>>>(tq, tk, tv, p);
+        return cudaGetLastError();
+    }
+    // two query heads of one kv head share a CTA when the group size is even,
+    // otherwise two consecutive row tiles of one head
+    pa.pair_heads = (H / KV) % 2 == 0 ? 1 : 0;
+    dim3 grid = pa.pair_heads ? dim3(row_tiles, H / 2) : dim3((row_tiles + 1) / 2, H);
+    attn_prefill_tc2_kernel<HD><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(tq, tk, tv, pa);
     return cudaGetLastError();
 }
 
