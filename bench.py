@@ -196,11 +196,22 @@ def prefill_block(S, ctx, dev, stream_obj):
         ms = e0.elapsed_time(e1) / len(blocks)
         if rep > 0:
             best = ms if best is None else min(best, ms)
+    # the tensor-core kernel alone: the library brackets its attention launch with events
+    ctx.timing_enable(True)
+    for b in blocks:
+        b.clear_cache()
+    for b in blocks:
+        b.forward_cached_dev(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), T, stream_obj.cuda_stream)
+    torch.cuda.synchronize()
+    kern_ms, kern_n = ctx.timing_read()
+    ctx.timing_enable(False)
+    kern_ms /= max(kern_n, 1)
     ctx.sync()
     for b in blocks:
         b.close()
     flops = 2.0 * hd * H * T * (T + 1)
     tfl = flops / (best / 1e3) / 1e12
+    kern_tfl = flops / (kern_ms / 1e3) / 1e12
     try:
         bf16 = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
         peak, kind = bf16 / 2.0, "measured bf16 burst / 2 (TF32 issues at half the bf16 rate)"
@@ -208,8 +219,11 @@ def prefill_block(S, ctx, dev, stream_obj):
         peak, kind = 1590.0 / 2.0, "fallback bf16 / 2"
     return {"workload": w["name"], "ms_per_layer": best, "tflops": tfl, "layers_timed": len(blocks),
             "est_ms_all_layers": best * w["layers_total"],
-            "roofline": {"bound": "tensor", "kernel": "attn_prefill_tc_kernel", "achieved": tfl, "peak": peak,
-                         "peak_kind": kind, "unit": "TFLOP/s", "frac": tfl / peak}}
+            "note": "ms_per_layer and tflops cover both launches of a layer (norm/RoPE/append, then attention); "
+                    "the roofline block is the attention kernel alone",
+            "roofline": {"bound": "tensor", "kernel": "attn_prefill_tc2_kernel", "achieved": kern_tfl, "peak": peak,
+                         "peak_kind": kind, "unit": "TFLOP/s", "frac": kern_tfl / peak, "kernel_ms": kern_ms,
+                         "flops_per_launch": flops}}
 
 
 def run_ours(args, wl, rank, world, local_rank):

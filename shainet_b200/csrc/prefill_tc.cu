@@ -6,29 +6,27 @@
 // once: that kernel runs one 128-thread CTA per (head, token), forms scores
 // with scalar FMAs through a global scratch of heads x T x L floats (which
 // overflows Int32 at 32 x 8192 x 8192, src/shainet/transformer/llama_block.cr:418)
-// and never touches a tensor core.  Here one CTA owns a tile of 128 query rows
-// of one head and walks the visible cache positions in tiles of 64:
+// and never touches a tensor core.  Here one CTA owns two tiles of 128 query
+// rows that see the same K/V tiles and walks the visible cache positions in
+// tiles of 64:
 //
 //   S  = Q K^T      tcgen05.mma kind::tf32, A and B from shared memory (K-major),
-//                   accumulator in tensor memory
-//   P  = exp2(S*c - max) rounded to TF32, written back over S in tensor memory
-//   OT = P V        tcgen05.mma with A from tensor memory, B = the V tile from
-//                   shared memory (MN-major), fresh accumulator per tile
-//   O  = O*alpha + OT   in registers of the thread that owns the row
+//                   accumulator in tensor memory (two score buffers per query tile)
+//   P  = exp2(S*c - max), written back over S in tensor memory
+//   O += P V        tcgen05.mma with A from tensor memory, B = the V tile from
+//                   shared memory (MN-major), accumulating in tensor memory
 //
 // Q, K and V tiles arrive by TMA (2-D tiled, 128-byte swizzle, no multicast)
-// into an mbarrier-guarded ring.  Warp 0 is the TMA producer, warp 1 allocates
-// tensor memory and issues the MMAs, warps 4-7 each own 32 TMEM lanes (one
-// query row per thread), so row maxima and sums need no shuffles.  Score and
-// output accumulators are double-buffered in tensor memory so that the MMAs of
-// one tile overlap the softmax of its neighbours.  Every wait is bounded.
+// into mbarrier-guarded buffers.  Warp 0 is the TMA producer, warp 1 allocates
+// tensor memory and issues the MMAs, warps 4-7 and 8-11 are the softmax
+// warpgroups of the two query tiles: each thread owns one query row (= one TMEM
+// lane), so row maxima and sums need no shuffles.  Every wait is bounded.
 //
 // The softmax is the same max-subtracted form as the reference's
 // (llama_block.cr:346-373); TF32 rounds the inputs of both contractions to 10
 // mantissa bits, which is the 2e-3 tolerance class of this path.
 #include <cuda.h>
 #include <math.h>
-#include <stdlib.h>
 #include "kernels.h"
 
 namespace shainet {
@@ -143,23 +141,6 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int M, int N, int a_mn_major, 
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-template <int HD>
-struct PF {
-    static constexpr int BM = 128;              // query rows per CTA
-    static constexpr int BN = 64;               // cache positions per tile
-    static constexpr int NSTG = 2;              // K/V ring depth
-    static constexpr int NBOX = HD / 32;        // 128-byte column blocks per row
-    static constexpr int Q_BYTES = BM * HD * 4;
-    static constexpr int KV_BYTES = BN * HD * 4;  // one of K, V
-    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int BAR_BYTES = 256;
-    static constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + NSTG * STAGE_BYTES + BAR_BYTES;
-    static constexpr int TMEM_S = 0;            // two score/probability buffers of BN columns
-    static constexpr int TMEM_OT = 2 * BN;      // two output-tile buffers of HD columns
-    static constexpr int TMEM_COLS = (2 * BN + 2 * HD) <= 256 ? 256 : 512;
-    static constexpr int THREADS = 256;
-};
-
 struct PrefillArgs {
     float* out;    // [T, num_heads*head_dim]
     int T;         // new tokens (query rows)
@@ -170,212 +151,6 @@ struct PrefillArgs {
     float scale;
     AttnStatus* status;
 };
-
-template <int HD>
-__global__ void __launch_bounds__(PF<HD>::THREADS, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, PrefillArgs a) {
-    using C = PF<HD>;
-    extern __shared__ unsigned char pf_smem_raw[];
-    // 128-byte swizzle atoms want 1024-byte aligned tiles
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(pf_smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_s = base;
-    unsigned char* kv_s = base + C::Q_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + C::NSTG * C::STAGE_BYTES);
-    uint64_t* q_full = bars;              // 1
-    uint64_t* kv_full = bars + 1;         // NSTG
-    uint64_t* kv_empty = kv_full + C::NSTG;
-    uint64_t* s_full = kv_empty + C::NSTG;  // 2
-    uint64_t* p_full = s_full + 2;          // 2
-    uint64_t* ot_full = p_full + 2;         // 2
-    uint64_t* ot_empty = ot_full + 2;       // 2
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ot_empty + 2);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heaviest tiles (latest rows) first
-    const int qt = gridDim.x - 1 - blockIdx.x;
-    const int h = blockIdx.y;
-    const int kv_h = h / (a.num_heads / a.num_kv_heads);
-    const int i0 = qt * C::BM;
-    const int rows_here = min(C::BM, a.T - i0);
-    const int kv_end = a.start + i0 + rows_here;            // positions visible to the last row of the tile
-    const int ntiles = (kv_end + C::BN - 1) / C::BN;
-
-    if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
-        for (int s = 0; s < C::NSTG; ++s) {
-            mbar_init(&kv_full[s], 1);
-            mbar_init(&kv_empty[s], 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&s_full[b], 1);
-            mbar_init(&p_full[b], 128);
-            mbar_init(&ot_full[b], 1);
-            mbar_init(&ot_empty[b], 128);
-        }
-        fence_mbar_init();
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
-
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, C::Q_BYTES);
-            for (int c = 0; c < C::NBOX; ++c) tma_load_2d(q_s + c * (C::BM * 128), &tm_q, h * HD + 32 * c, i0, q_full);
-            for (int j = 0; j < ntiles; ++j) {
-                const int st = j % C::NSTG;
-                if (j >= C::NSTG && !mbar_wait(&kv_empty[st], ((j / C::NSTG) - 1) & 1, a.status, 11)) break;
-                unsigned char* k_s = kv_s + st * C::STAGE_BYTES;
-                unsigned char* v_s = k_s + C::KV_BYTES;
-                mbar_arrive_expect_tx(&kv_full[st], C::STAGE_BYTES);
-                const int y = kv_h * a.capacity + j * C::BN;
-                for (int c = 0; c < C::NBOX; ++c) {
-                    tma_load_2d(k_s + c * (C::BN * 128), &tm_k, 32 * c, y, &kv_full[st]);
-                    tma_load_2d(v_s + c * (C::BN * 128), &tm_v, 32 * c, y, &kv_full[st]);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = idesc_tf32(C::BM, C::BN, 0, 0);
-            constexpr uint32_t idesc_pv = idesc_tf32(C::BM, HD, 0, 1);
-            const uint32_t q_addr = smem_u32(q_s);
-            bool ok = mbar_wait(q_full, 0, a.status, 12);
-            for (int j = 0; ok && j <= ntiles; ++j) {
-                if (j < ntiles) {
-                    const int st = j % C::NSTG;
-                    if (!(ok = mbar_wait(&kv_full[st], (j / C::NSTG) & 1, a.status, 13))) break;
-                    tc_fence_after();
-                    const uint32_t k_addr = smem_u32(kv_s + st * C::STAGE_BYTES);
-                    const uint32_t d = tmem + C::TMEM_S + (j & 1) * C::BN;
-#pragma unroll
-                    for (int kk = 0; kk < HD / 8; ++kk) {
-                        // k-step kk: column block kk/4, 32-byte slice kk%4 inside its 128-byte rows
-                        const uint64_t ad = smem_desc_sw128(q_addr + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
-                        const uint64_t bd = smem_desc_sw128(k_addr + (kk >> 2) * (C::BN * 128) + (kk & 3) * 32, 16, 1024);
-                        mma_ss_tf32(d, ad, bd, idesc_qk, kk > 0);
-                    }
-                    tc_commit(&s_full[j & 1]);
-                }
-                if (j >= 1) {
-                    const int t = j - 1, b = t & 1, st = t % C::NSTG;
-                    if (!(ok = mbar_wait(&p_full[b], (t >> 1) & 1, a.status, 14))) break;
-                    if (t >= 2 && !(ok = mbar_wait(&ot_empty[b], ((t >> 1) - 1) & 1, a.status, 15))) break;
-                    tc_fence_after();
-                    const uint32_t v_addr = smem_u32(kv_s + st * C::STAGE_BYTES + C::KV_BYTES);
-                    const uint32_t d = tmem + C::TMEM_OT + b * HD;
-                    const uint32_t p = tmem + C::TMEM_S + b * C::BN;
-#pragma unroll
-                    for (int kk = 0; kk < C::BN / 8; ++kk) {
-                        // k-step kk: cache rows 8kk..8kk+7 (one 1024-byte group); column blocks every BN*128 bytes
-                        const uint64_t bd = smem_desc(v_addr + kk * 1024, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
-                        mma_ts_tf32(d, p + kk * 8, bd, idesc_pv, kk > 0);
-                    }
-                    tc_commit(&ot_full[b]);
-                    tc_commit(&kv_empty[st]);
-                }
-            }
-        }
-    } else if (warp >= 4) {
-        // ---------------- softmax + output accumulation: one query row per thread ----------------
-        const int quad = warp & 3;
-        const int r = quad * 32 + lane;                 // row inside the tile = TMEM lane
-        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const int row_pos = a.start + i0 + r;           // last visible cache position of this row
-        const float sl2 = a.scale * PF_LOG2E * PF_TRUNC_GAIN;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
-        float m = -INFINITY, l = 0.0f, alpha_prev = 0.0f;
-        bool ok = true;
-        for (int j = 0; ok && j <= ntiles; ++j) {
-            float alpha = 1.0f;
-            if (j < ntiles) {
-                const int b = j & 1;
-                if (!(ok = mbar_wait(&s_full[b], (j >> 1) & 1, a.status, 16))) break;
-                tc_fence_after();
-                uint32_t s0[32], s1[32];
-                const uint32_t sa = tmem + lane_addr + C::TMEM_S + b * C::BN;
-                tmem_ld32(sa, s0);
-                tmem_ld32(sa + 32, s1);
-                tmem_wait_ld();
-                const int c0 = j * C::BN;
-                if (c0 + C::BN - 1 > row_pos) {         // tile crosses this row's causal boundary
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        if (c0 + c > row_pos) s0[c] = 0xff800000u;        // -inf
-                        if (c0 + 32 + c > row_pos) s1[c] = 0xff800000u;
-                    }
-                }
-                float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
-                // scores stay raw; the positive factor sl2 commutes with max
-                const float m_new = fmaxf(m, mx * sl2);
-                alpha = ex2_approx(m - m_new);   // 0 on the first tile
-                float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    // P goes to the tensor core as fp32 bits; its truncation to TF32
-                    // there is covered by PF_TRUNC_GAIN on the output
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(s0[c]), sl2, -m_new));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(s1[c]), sl2, -m_new));
-                    s0[c] = __float_as_uint(p0);
-                    s1[c] = __float_as_uint(p1);
-                    sum0 += p0;
-                    sum1 += p1;
-                }
-                l = fmaf(l, alpha, sum0 + sum1);
-                m = m_new;
-                tmem_st32(sa, s0);
-                tmem_st32(sa + 32, s1);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&p_full[b]);
-            }
-            if (j >= 1) {
-                const int t = j - 1, b = t & 1;
-                if (!(ok = mbar_wait(&ot_full[b], (t >> 1) & 1, a.status, 17))) break;
-                tc_fence_after();
-                const uint32_t oa = tmem + lane_addr + C::TMEM_OT + b * HD;
-#pragma unroll
-                for (int ch = 0; ch < HD / 32; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(oa + ch * 32, v);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[ch * 32 + c] = fmaf(o[ch * 32 + c], alpha_prev, __uint_as_float(v[c]));
-                }
-                tc_fence_before();
-                mbar_arrive(&ot_empty[b]);
-            }
-            // o is now at the scale of tile j-1's maximum; alpha brings it to tile j's
-            alpha_prev = alpha;
-        }
-        if (ok && r < rows_here) {
-            const float inv = PF_TRUNC_GAIN * PF_TRUNC_GAIN / l;   // V and P are both truncated by the tensor core
-            float* dst = a.out + ((size_t)(i0 + r) * a.num_heads + h) * HD;
-#pragma unroll
-            for (int d = 0; d < HD; d += 4)
-                *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
-    }
-}
 
 // ---------------------------------------------------------------------------
 // Two query tiles per CTA.  Both tiles walk the same K/V tiles (two query heads
@@ -696,15 +471,12 @@ bool make_map(CUtensorMap* m, const float* base, uint64_t cols, uint64_t rows, u
 
 template <int HD>
 cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
-    using C1 = PF<HD>;
     using C = PF2<HD>;
     static unsigned long long configured = 0;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 64 || !(configured >> dev & 1ull)) {
-        e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C1::SMEM_BYTES);
-        if (e != cudaSuccess) return e;
         e = cudaFuncSetAttribute(attn_prefill_tc2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
         if (e != cudaSuccess) return e;
         if (dev < 64) configured |= 1ull << dev;
@@ -727,12 +499,6 @@ cudaError_t launch_pf(const AttnArgs& a, cudaStream_t s) {
     p.scale = a.scale;
     p.status = a.status;
     const int row_tiles = (a.T + C::BM - 1) / C::BM;
-    static const bool one_tile = getenv("SHAINET_PF_ONE_TILE") != nullptr;  // development switch
-    if (one_tile) {
-        dim3 grid(row_tiles, H);
-        attn_prefill_tc_kernel<HD><<<grid, C1::THREADS, C1::SMEM_BYTES, s>>>(tq, tk, tv, p);
-        return cudaGetLastError();
-    }
     // two query heads of one kv head share a CTA when the group size is even,
     // otherwise two consecutive row tiles of one head
     pa.pair_heads = (H / KV) % 2 == 0 ? 1 : 0;

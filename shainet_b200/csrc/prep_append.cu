@@ -19,92 +19,103 @@ namespace shainet {
 namespace {
 
 constexpr int PREP_WARPS = 4;
+constexpr int PREP_THREADS = PREP_WARPS * 32;
 
-__global__ void __launch_bounds__(PREP_WARPS * 32) prep_append_kernel(PrepArgs a) {
+// One CTA per new token.  All of the token's q, k and v heads are staged in
+// shared memory (rows padded by one float), so that
+//   * cos/sin of the token's position are computed once and shared by every head,
+//   * the per-head sum of squares keeps the host loop's strictly sequential
+//     order, but 32 heads run their chains side by side (one per lane) instead
+//     of one lane working while 31 wait.
+__global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
     extern __shared__ float prep_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int H = a.hs.num_heads, KV = a.hs.num_kv_heads, hd = a.hs.head_dim;
     const int per_row = H + 2 * KV;
-    const long long item = (long long)blockIdx.x * PREP_WARPS + warp;
-    const long long rows = (long long)a.batch * a.T;
-    if (item >= rows * per_row) return;  // warp-uniform
-    const int r = (int)(item / per_row);
-    const int slot = (int)(item % per_row);
+    const int half = hd >> 1;
+    const int stride = hd + 1;
+    float* cs = prep_smem;               // [half]
+    float* sn = cs + half;               // [half]
+    float* inv = sn + half;              // [H + KV]
+    float* buf = inv + (H + KV);         // [per_row][hd + 1]
+
+    const int r = blockIdx.x;
     const int b = r / a.T, t = r % a.T;
     const SeqDesc sd = a.seqs.many ? a.seqs.many[b] : a.seqs.one;
     const int pos = sd.start + t;
-    const int half = hd >> 1;
-    float* row = prep_smem + warp * hd;
+    const float fpos = (float)pos;
 
-    const float* src;
-    const float* bias;
-    const float* w;
-    float* dst;
-    bool is_v = false;
-    if (slot < H) {
-        src = a.q + (size_t)r * H * hd + (size_t)slot * hd;
-        bias = a.b_q ? a.b_q + (size_t)slot * hd : nullptr;
-        w = a.q_norm;
-        dst = a.q_rot + (size_t)r * H * hd + (size_t)slot * hd;
-    } else if (slot < H + KV) {
-        const int kh = slot - H;
-        src = a.k_new + (size_t)r * KV * hd + (size_t)kh * hd;
-        bias = a.b_k ? a.b_k + (size_t)kh * hd : nullptr;
-        w = a.k_norm;
-        dst = sd.k + ((size_t)kh * sd.capacity + pos) * hd;
-    } else {
-        const int kh = slot - H - KV;
-        src = a.v_new + (size_t)r * KV * hd + (size_t)kh * hd;
-        bias = a.b_v ? a.b_v + (size_t)kh * hd : nullptr;
-        w = nullptr;
-        dst = sd.v + ((size_t)kh * sd.capacity + pos) * hd;
-        is_v = true;
+    for (int i = threadIdx.x; i < half; i += PREP_THREADS) {
+        const float angle = __fmul_rn(fpos, a.inv_freq[i]);
+        float s_, c_;
+        sincosf(angle, &s_, &c_);
+        cs[i] = c_;
+        sn[i] = s_;
     }
-
-    for (int d = lane; d < hd; d += 32) {
-        float x = src[d];
-        if (bias) x = __fadd_rn(x, bias[d]);
-        row[d] = x;
+    for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+        const float* src;
+        const float* bias;
+        if (slot < H) {
+            src = a.q + ((size_t)r * H + slot) * hd;
+            bias = a.b_q ? a.b_q + (size_t)slot * hd : nullptr;
+        } else if (slot < H + KV) {
+            src = a.k_new + ((size_t)r * KV + (slot - H)) * hd;
+            bias = a.b_k ? a.b_k + (size_t)(slot - H) * hd : nullptr;
+        } else {
+            src = a.v_new + ((size_t)r * KV + (slot - H - KV)) * hd;
+            bias = a.b_v ? a.b_v + (size_t)(slot - H - KV) * hd : nullptr;
+        }
+        float* row = buf + (size_t)slot * stride;
+        for (int d = lane; d < hd; d += 32) {
+            float x = src[d];
+            if (bias) x = __fadd_rn(x, bias[d]);
+            row[d] = x;
+        }
     }
-    __syncwarp();
-    if (is_v) {
-        for (int d = lane; d < hd; d += 32) dst[d] = row[d];
-        return;
-    }
-
-    float inv = 1.0f;
-    if (w) {
-        if (lane == 0) {
+    __syncthreads();
+    const bool normed = a.q_norm != nullptr || a.k_norm != nullptr;
+    if (normed) {
+        for (int slot = threadIdx.x; slot < H + KV; slot += PREP_THREADS) {
             // Sequential fp32 sum in ascending d, as the host loop does.
+            const float* row = buf + (size_t)slot * stride;
             float ss = 0.0f;
             for (int d = 0; d < hd; ++d) ss = __fadd_rn(ss, __fmul_rn(row[d], row[d]));
             const float mean = __fdiv_rn(ss, (float)hd);
-            inv = (float)(1.0 / sqrt((double)mean + a.eps));
+            inv[slot] = (float)(1.0 / sqrt((double)mean + a.eps));
         }
-        inv = __shfl_sync(0xffffffffu, inv, 0);
+        __syncthreads();
     }
-    const float fpos = (float)pos;
-    for (int i = lane; i < half; i += 32) {
-        float x0 = row[i], x1 = row[i + half];
-        if (w) {
-            x0 = __fmul_rn(__fmul_rn(x0, inv), w[i]);
-            x1 = __fmul_rn(__fmul_rn(x1, inv), w[i + half]);
+    for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+        const float* row = buf + (size_t)slot * stride;
+        if (slot >= H + KV) {
+            float* dst = sd.v + ((size_t)(slot - H - KV) * sd.capacity + pos) * hd;
+            for (int d = lane; d < hd; d += 32) dst[d] = row[d];
+            continue;
         }
-        const float angle = __fmul_rn(fpos, a.inv_freq[i]);
-        float s, c;
-        sincosf(angle, &s, &c);
-        float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        float y1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
-        if (a.round_q_tf32 && slot < H) {
-            // q only: the cache keeps full fp32 rows
-            unsigned u0, u1;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y0));
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y1));
-            y0 = __uint_as_float(u0);
-            y1 = __uint_as_float(u1);
+        const bool is_q = slot < H;
+        const float* w = is_q ? a.q_norm : a.k_norm;
+        float* dst = is_q ? a.q_rot + ((size_t)r * H + slot) * hd : sd.k + ((size_t)(slot - H) * sd.capacity + pos) * hd;
+        const float iv = normed ? inv[slot] : 1.0f;
+        for (int i = lane; i < half; i += 32) {
+            float x0 = row[i], x1 = row[i + half];
+            if (w) {
+                x0 = __fmul_rn(__fmul_rn(x0, iv), w[i]);
+                x1 = __fmul_rn(__fmul_rn(x1, iv), w[i + half]);
+            }
+            const float c = cs[i], s_ = sn[i];
+            float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s_));
+            float y1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s_));
+            if (a.round_q_tf32 && is_q) {
+                // q only: the cache keeps full fp32 rows
+                unsigned u0, u1;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y0));
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y1));
+                y0 = __uint_as_float(u0);
+                y1 = __uint_as_float(u1);
+            }
+            dst[i] = y0;
+            dst[i + half] = y1;
         }
-        dst[i] = y0;
-        dst[i + half] = y1;
     }
 }
 
@@ -175,11 +186,16 @@ __global__ void fill_normal_kernel(float* base, int num_kv_heads, int capacity, 
 }  // namespace
 
 cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s) {
-    const long long items = (long long)a.batch * a.T * (a.hs.num_heads + 2 * a.hs.num_kv_heads);
-    if (items == 0) return cudaSuccess;
-    const unsigned blocks = (unsigned)((items + PREP_WARPS - 1) / PREP_WARPS);
-    const size_t smem = (size_t)PREP_WARPS * a.hs.head_dim * sizeof(float);
-    prep_append_kernel<<<blocks, PREP_WARPS * 32, smem, s>>>(a);
+    const long long rows = (long long)a.batch * a.T;
+    if (rows == 0) return cudaSuccess;
+    const int per_row = a.hs.num_heads + 2 * a.hs.num_kv_heads;
+    const size_t smem = ((size_t)per_row * (a.hs.head_dim + 1) + a.hs.head_dim + a.hs.num_heads + a.hs.num_kv_heads) * sizeof(float);
+    if (smem > 48 * 1024) {
+        if (smem > 227 * 1024) return cudaErrorInvalidValue;
+        cudaError_t e = cudaFuncSetAttribute(prep_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    prep_append_kernel<<<(unsigned)rows, PREP_THREADS, smem, s>>>(a);
     return cudaGetLastError();
 }
 
