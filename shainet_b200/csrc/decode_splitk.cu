@@ -106,7 +106,11 @@ struct SKDefault {
 };
 
 template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
+#ifdef SK_NOMATH
+          int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = false>
+#else
           int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = true>
+#endif
 struct SK {
     static constexpr int NW = NW_;                     // consumer warps
     static constexpr int CPL = HD / 64;                // 16-byte chunks per lane per K row
@@ -243,7 +247,11 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
     const int i16 = lane & 15, hw = lane >> 4;
     f32x2 acc2[16];
     score_batch<HD, G, C>(ks, 0, hw, i16, q, acc2);
+#ifdef SK_ROLL
+#pragma unroll 1
+#else
 #pragma unroll
+#endif
     for (int bb = 0; bb < C::NB; ++bb) {
         const int base = bb * C::BR;
         f32x2* ps = scratch + (bb & 1) * 48;
@@ -682,7 +690,9 @@ __device__ __forceinline__ bool spin_until_equal(const unsigned* p, unsigned wan
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
             if (ld_acquire(p) == want) return true;
-            __nanosleep(40);
+#ifdef SK_SPIN_SLEEP
+            __nanosleep(SK_SPIN_SLEEP);
+#endif
         }
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
             if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = where;
@@ -859,6 +869,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
 #pragma unroll
         for (int n = 0; n < MAXIT; ++n) {
             const int it = warp + n * C::NW;
+#pragma unroll
+            for (int c = 0; c < 2 * PL; ++c) x[n][c] = 0.0f;
             if (it < items) {
                 const float* src;
                 const float* bias;
@@ -882,7 +894,25 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
         // (2) norm (warp-tree sum of squares; the prefill kernel keeps the reference's
         // sequential order, the two differ by the rounding of the sum), rotation with
-        // the reference's unfused arithmetic, then shared memory and, for k and v, the cache
+        // the reference's unfused arithmetic, then shared memory and, for k and v, the cache.
+        // The rows of a warp go through each stage together (no per-row branches around
+        // the shuffles), so their shuffle and double-precision latencies overlap.
+        float inv[MAXIT];
+        {
+            float ss[MAXIT];
+#pragma unroll
+            for (int n = 0; n < MAXIT; ++n) {
+                ss[n] = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 2 * PL; ++c) ss[n] = fmaf(x[n][c], x[n][c], ss[n]);   // rows past `items` hold zeros
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int n = 0; n < MAXIT; ++n) ss[n] += __shfl_xor_sync(FULL, ss[n], off);
+#pragma unroll
+            for (int n = 0; n < MAXIT; ++n) inv[n] = (float)(1.0 / sqrt((double)(ss[n] / (float)HD) + a.eps));
+        }
 #pragma unroll
         for (int n = 0; n < MAXIT; ++n) {
             const int it = warp + n * C::NW;
@@ -890,21 +920,12 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             float* row = it < G ? sm.qs + it * C::QS_STRIDE : (it == G ? sm.xk : sm.xv);
             if (it <= G) {
                 const bool normed = (it < G ? a.q_norm : a.k_norm) != nullptr;
-                float inv = 1.0f;
-                if (normed) {
-                    float ss = 0.0f;
-#pragma unroll
-                    for (int c = 0; c < 2 * PL; ++c) ss = fmaf(x[n][c], x[n][c], ss);
-#pragma unroll
-                    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(FULL, ss, off);
-                    inv = (float)(1.0 / sqrt((double)(ss / (float)HD) + a.eps));
-                }
 #pragma unroll
                 for (int k = 0; k < PL; ++k) {
                     float x0 = x[n][k], x1 = x[n][k + PL];
                     if (normed) {
-                        x0 = __fmul_rn(__fmul_rn(x0, inv), it < G ? wq0[k] : wk0[k]);
-                        x1 = __fmul_rn(__fmul_rn(x1, inv), it < G ? wq1[k] : wk1[k]);
+                        x0 = __fmul_rn(__fmul_rn(x0, inv[n]), it < G ? wq0[k] : wk0[k]);
+                        x1 = __fmul_rn(__fmul_rn(x1, inv[n]), it < G ? wq1[k] : wk1[k]);
                     }
                     x[n][k] = __fsub_rn(__fmul_rn(x0, rc[k]), __fmul_rn(x1, rs[k]));
                     x[n][k + PL] = __fadd_rn(__fmul_rn(x1, rc[k]), __fmul_rn(x0, rs[k]));
@@ -967,6 +988,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         for (int sidx = threadIdx.x; sidx < nsplit_here; sidx += C::THREADS)
             seen = spin_until_equal(flags + sidx, a.epoch, a.status, 3) && seen;
         if (!__syncthreads_and(seen)) return;   // acquiring loads + barrier: the partials are visible to the CTA
+        TL_MARK(7, 0);
         for (int g = split; g < G; g += nm) {
             const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
             merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
