@@ -274,8 +274,8 @@ def run_ours(args, wl, rank, world, local_rank):
     pay = qd + (Hl if split else 0)        # a rank's contribution per layer: outputs (+ log-sum-exp when the sequence is split)
     out_d = torch.empty(layers, pay, device=dev)
     # Several ranks: every rank's fused kernel stores its head rows straight into all
-    # ranks' exchange buffers over NVLink (layout [layer][rank][pay]) and raises a flag;
-    # a one-warp kernel per layer waits for the flags.  --nccl-gather keeps the
+    # ranks' exchange buffers over NVLink (layout [layer][rank][pay]) as {value, epoch}
+    # words; a small kernel per layer waits for the words of all ranks and unpacks them.  --nccl-gather keeps the
     # torch.distributed all-gather instead (also used when rows are not 16-byte multiples).
     peer = world > 1 and pay % 4 == 0 and not args.nccl_gather
     gathered = torch.empty(layers, world, pay, device=dev) if world > 1 and not peer else None
@@ -317,8 +317,7 @@ def run_ours(args, wl, rank, world, local_rank):
     lse_ptrs = [vp(out_d[l, qd:].data_ptr()) for l in range(layers)] if split else None
     if split:
         gath_ptrs = [vp(comm_base + l * world * pay * 4) if peer else vp(gathered[l].data_ptr()) for l in range(layers)]
-    set_target = ctx.L.shainet_attn_comm_set_target
-    comm_wait = ctx.L.shainet_attn_comm_wait
+    fwd_x = ctx.L.shainet_attn_forward_dev_exchange
     out_offs = [(l * world + rank) * pay for l in range(layers)]
     full_ptrs = [vp(full_d[l].data_ptr()) for l in range(layers)] if split else None
 
@@ -326,41 +325,35 @@ def run_ours(args, wl, rank, world, local_rank):
         args = (all_args or dev_args)[i % NV]
         epoch[0] += 1
         ep = epoch[0]
-        if not split:
+        pos = ctx_len + i                   # the token's position; with a split sequence its k/v row goes to one rank of the group
+        own = 1 if sp.owns_position(pos) else 0
+        if peer:
             for l in range(layers):
-                if peer:
-                    rc = set_target(ctx.h, out_offs[l], -1, l, ep)
+                a = args[l]
+                rc = fwd_x(a[0], a[1], a[2], a[3], a[4], a[5], pos, own, a[7], a[8], out_offs[l],
+                           out_offs[l] + qd if split else -1, l * world * pay, world * pay, ep, a[9])   # head outputs of all ranks, before o_proj
+                if rc:
+                    S.check(rc)
+                if split:
+                    rc = merge(ctx.h, gath_ptrs[l], world, sp.seq_parts, Hl, hd, full_ptrs[l], a[9])
                     if rc:
                         S.check(rc)
+            return
+        if not split:
+            for l in range(layers):
                 rc = fwd_dev(*args[l])
                 if rc:
                     S.check(rc)
-                if peer:
-                    rc = comm_wait(ctx.h, l, ep, args[l][9])              # head outputs of all ranks, before o_proj
-                    if rc:
-                        S.check(rc)
-                elif world > 1:
+                if world > 1:
                     dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
             return
-        pos = ctx_len + i                   # the token's position; its k/v row goes to one rank of the group
-        own = 1 if sp.owns_position(pos) else 0
         for l in range(layers):
             a = args[l]
-            if peer:
-                rc = set_target(ctx.h, out_offs[l], out_offs[l] + qd, l, ep)
-                if rc:
-                    S.check(rc)
-            else:
-                set_lse(ctx.h, lse_ptrs[l])
+            set_lse(ctx.h, lse_ptrs[l])
             rc = fwd_at(a[0], a[1], a[2], a[3], a[4], a[5], pos, own, a[7], a[8], a[9])
             if rc:
                 S.check(rc)
-            if peer:
-                rc = comm_wait(ctx.h, l, ep, a[9])
-                if rc:
-                    S.check(rc)
-            else:
-                dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
+            dist.all_gather_into_tensor(gathered[l].view(-1), out_d[l])
             rc = merge(ctx.h, gath_ptrs[l], world, sp.seq_parts, Hl, hd, full_ptrs[l], a[9])
             if rc:
                 S.check(rc)
@@ -453,7 +446,7 @@ def run_ours(args, wl, rank, world, local_rank):
     barrier()
     t0 = time.perf_counter()
     for i in range(K_e2e):
-        host_step(i)
+        host_step(W_e2e + i)
     barrier()
     e2e_s = time.perf_counter() - t0
     if world > 1:
@@ -480,7 +473,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl["name"], "layers": layers, "num_heads": H, "num_kv_heads": KV, "head_dim": hd,
-                       "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); " + ("no exchange" if world == 1 else ("head outputs stored into every rank's buffer by the decode kernel (peer stores over NVLink), one flag wait per layer" if peer else "torch.distributed all-gather of head outputs per layer")),
+                       "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); " + ("no exchange" if world == 1 else ("head outputs stored into every rank's buffer by the decode kernel (8-byte value+epoch peer stores over NVLink), one wait-and-unpack kernel per layer" if peer else "torch.distributed all-gather of head outputs per layer")),
                        "l2": "working set per step (all layers' K/V) is far larger than L2; no flush needed",
                        "host_enqueue_ms_per_step": t_enq * 1e3 / K,
                        "hbm_gbs_whole_step_per_gpu": bytes_per_launch * layers / (ms / K / 1e3) / 1e9},

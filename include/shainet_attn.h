@@ -162,26 +162,34 @@ int shainet_attn_merge_parts(shainet_attn_ctx* ctx, const float* gathered_dev, i
 
 /* ---- exchange of head outputs between the GPUs of one box, fused into the
  * decode kernel (no counterpart in the reference, which is single-device).
- * Every rank owns one exchange buffer: 16 KB of flag words, then data_floats
- * floats.  comm_create allocates it and returns an inter-process handle
- * (SHAINET_ATTN_COMM_HANDLE_BYTES bytes) that the host code passes around by
- * whatever means it has; comm_open maps the other ranks' buffers (handles: world
- * consecutive handles in rank order).  comm_set_target arms the NEXT fused
- * decode call: the CTAs that merge its split partials store every head row (and,
- * if lse_offset_floats >= 0, every head's log-sum-exp) into ALL ranks' data
- * areas at the given offsets with plain peer stores over NVLink (no multicast,
- * no copy engine), and the last of them stores `epoch` into flag word
- * [flag_index][this rank] of every rank.  comm_wait enqueues a one-warp kernel
- * that waits (bounded, ~1 s, then SHAINET_ATTN_E_DEVICE_WAIT at the next sync) until
- * this rank's flag words [flag_index][0..world) all equal `epoch`.  A slot may
- * be rewritten once its owner's stream has passed the work that read it. */
+ * Every rank owns one exchange buffer of data_floats floats (the same number on
+ * every rank) followed by as many 8-byte {value, epoch} words.  comm_create
+ * allocates it and returns an inter-process handle (SHAINET_ATTN_COMM_HANDLE_BYTES
+ * bytes) that the host code passes around by whatever means it has; comm_open
+ * maps the other ranks' buffers (handles: world consecutive handles in rank
+ * order).  comm_set_target arms the NEXT fused decode call: the CTAs that merge
+ * its split partials store every head row (and, if lse_offset_floats >= 0,
+ * every head's log-sum-exp) into the word areas of ALL ranks at the given
+ * offsets, each float as one indivisible 8-byte store {value, epoch} over NVLink
+ * (no multicast, no copy engine, no fence, no flag).  comm_wait enqueues a kernel
+ * that polls the words [offset, offset + count) of this rank's buffer until each
+ * carries `epoch` (bounded, ~1 s, then SHAINET_ATTN_E_DEVICE_WAIT at the next
+ * sync) and writes the values to the float area, where comm_data_ptr / comm_read
+ * and merge_parts find them.  Epochs are non-zero and differ between successive
+ * uses of a word; a word may be rewritten once its owner's stream has passed the
+ * wait that unpacked it. */
 #define SHAINET_ATTN_COMM_HANDLE_BYTES 64
 int shainet_attn_comm_create(shainet_attn_ctx* ctx, size_t data_floats, void* handle_out);
 int shainet_attn_comm_open(shainet_attn_ctx* ctx, const void* handles, int world, int rank);
-int shainet_attn_comm_set_target(shainet_attn_ctx* ctx, long long out_offset_floats, long long lse_offset_floats,
-                                 int flag_index, unsigned epoch);
-int shainet_attn_comm_wait(shainet_attn_ctx* ctx, int flag_index, unsigned epoch, void* stream);
-/* Asynchronous copy of a range of this rank's data area to host memory. */
+int shainet_attn_comm_set_target(shainet_attn_ctx* ctx, long long out_offset_floats, long long lse_offset_floats, unsigned epoch);
+int shainet_attn_comm_wait(shainet_attn_ctx* ctx, long long offset_floats, long long count_floats, unsigned epoch, void* stream);
+/* comm_set_target + forward_dev_at + comm_wait in one call (one decode token of one
+ * layer on a rank of a sharded model): the host cost of a layer is one foreign call. */
+int shainet_attn_forward_dev_exchange(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                                      const float* v_new, float* out, int position, int append, float scale, unsigned flags,
+                                      long long out_offset_floats, long long lse_offset_floats, long long wait_offset_floats,
+                                      long long wait_count_floats, unsigned epoch, void* stream);
+/* Asynchronous copy of a range of this rank's float area to host memory. */
 int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream);
 int shainet_attn_comm_data_ptr(shainet_attn_ctx* ctx, float** data_dev);
 

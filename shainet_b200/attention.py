@@ -88,13 +88,15 @@ class AttnContext:
         assert len(blob) == _lib.COMM_HANDLE_BYTES * len(handles)
         check(self.L.shainet_attn_comm_open(self.h, blob, len(handles), rank))
 
-    def comm_set_target(self, out_offset: int, lse_offset: int, flag_index: int, epoch: int):
+    def comm_set_target(self, out_offset: int, lse_offset: int, epoch: int):
         """Arm the next fused decode call to store its head rows (and log-sum-exp values when
-        lse_offset >= 0) into every rank's buffer and then raise flag [flag_index][rank] = epoch."""
-        check(self.L.shainet_attn_comm_set_target(self.h, out_offset, lse_offset, flag_index, epoch))
+        lse_offset >= 0) into every rank's buffer as {value, epoch} words."""
+        check(self.L.shainet_attn_comm_set_target(self.h, out_offset, lse_offset, epoch))
 
-    def comm_wait(self, flag_index: int, epoch: int, stream=None):
-        check(self.L.shainet_attn_comm_wait(self.h, flag_index, epoch, _stream_arg(stream)))
+    def comm_wait(self, offset: int, count: int, epoch: int, stream=None):
+        """Enqueue the wait for the words [offset, offset + count) of this rank's buffer to carry
+        `epoch`; it also unpacks them into the float area."""
+        check(self.L.shainet_attn_comm_wait(self.h, offset, count, epoch, _stream_arg(stream)))
 
     def comm_data_ptr(self) -> int:
         p = C.c_void_p()
@@ -243,6 +245,17 @@ class LlamaAttention:
         `position`; this rank stores and sees the token's k/v row only if `append`."""
         check(self.ctx.L.shainet_attn_forward_dev_at(self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, position,
                                                      int(append), self.scale, flags, _stream_arg(stream)))
+
+    def forward_cached_dev_exchange(self, q_ptr: int, k_ptr, v_ptr, out_ptr: int, position: int, append: bool,
+                                    out_offset: int, lse_offset: int, wait_offset: int, wait_count: int, epoch: int,
+                                    stream=None, flags: int = 0):
+        """One decode token on a rank of a sharded model: attention over this rank's rows, head
+        rows (and log-sum-exp values when lse_offset >= 0) delivered into every rank's exchange
+        buffer by the kernel, then the wait for (and unpacking of) the float range
+        [wait_offset, wait_offset + wait_count) of this rank's buffer, in one foreign call."""
+        check(self.ctx.L.shainet_attn_forward_dev_exchange(
+            self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, position, int(append), self.scale, flags,
+            out_offset, lse_offset, wait_offset, wait_count, epoch, _stream_arg(stream)))
 
     def close(self):
         self.cache.close()

@@ -46,7 +46,6 @@ int fail_cuda(cudaError_t e, const char* what) {
 constexpr int SEQ_RING = 8;           // in-flight descriptor uploads of batched decode
 constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
 constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
-constexpr size_t COMM_FLAG_BYTES = 16384;  // flag words at the start of an exchange buffer
 constexpr int TENSOR_MIN_T = 64;      // rows per call from which the tensor-core prefill kernel takes over
 
 struct DevBuf {
@@ -79,15 +78,14 @@ struct shainet_attn_ctx {
     size_t flags_offset = ~(size_t)0;   // where the flags start inside `tickets` (they move with the head shape)
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
     float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
-    // exchange buffer shared with the other ranks of the box (IPC); flags first, then data
+    // exchange buffer shared with the other ranks of the box (IPC): comm_data_floats
+    // floats, then as many 8-byte {value, epoch} words
     unsigned char* comm_base = nullptr;
     size_t comm_data_floats = 0;
     int comm_world = 0, comm_rank = 0;
     unsigned char* comm_peer[MAX_PEERS] = {};
-    unsigned* comm_done_ticket = nullptr;
     bool gather_armed = false;          // the next fused decode call delivers to the peers
     long long gather_out_off = 0, gather_lse_off = -1;
-    int gather_flag = 0;
     unsigned gather_epoch = 0;
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
@@ -208,7 +206,6 @@ int check_status(shainet_attn_ctx* ctx) {
         ctx->status_host->code = DEV_OK;
         ctx->status_host->where = 0;
         if (ctx->tickets) cudaMemset(ctx->tickets, 0, ctx->tickets_cap * sizeof(unsigned));  // an unwound kernel may leave counts
-        if (ctx->comm_done_ticket) cudaMemset(ctx->comm_done_ticket, 0, sizeof(unsigned));
         return fail(SHAINET_ATTN_E_DEVICE_WAIT, "a kernel gave up on a bounded wait (site %d)", where);
     }
     return SHAINET_ATTN_OK;
@@ -447,16 +444,11 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
             return fail(SHAINET_ATTN_E_INVALID, "peer delivery target outside the exchange buffer");
         GatherTarget& gt = f.gather;
         gt.world = ctx->comm_world;
-        gt.rank = ctx->comm_rank;
-        for (int p = 0; p < ctx->comm_world; ++p) {
-            gt.peer[p] = reinterpret_cast<float*>(ctx->comm_peer[p] + COMM_FLAG_BYTES);
-            gt.peer_flags[p] = reinterpret_cast<unsigned*>(ctx->comm_peer[p]);
-        }
+        for (int p = 0; p < ctx->comm_world; ++p)
+            gt.peer_words[p] = reinterpret_cast<unsigned long long*>(ctx->comm_peer[p] + ctx->comm_data_floats * sizeof(float));
         gt.out_offset = ctx->gather_out_off;
         gt.lse_offset = ctx->gather_lse_off;
-        gt.flag_index = ctx->gather_flag;
         gt.epoch = ctx->gather_epoch;
-        gt.done_ticket = ctx->comm_done_ticket;
     }
     std::pair<cudaEvent_t, cudaEvent_t> ev{};
     if (ctx->timing) {
@@ -562,7 +554,6 @@ int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
     for (int p = 0; p < c->comm_world; ++p)
         if (p != c->comm_rank && c->comm_peer[p]) cudaIpcCloseMemHandle(c->comm_peer[p]);
     if (c->comm_base) cudaFree(c->comm_base);
-    if (c->comm_done_ticket) cudaFree(c->comm_done_ticket);
     for (int i = 0; i < SEQ_RING; ++i)
         if (c->seq_ev[i]) cudaEventDestroy(c->seq_ev[i]);
     for (auto* v : {&c->timed, &c->ev_pool})
@@ -875,12 +866,11 @@ int shainet_attn_merge_parts(shainet_attn_ctx* ctx, const float* gathered_dev, i
 int shainet_attn_comm_create(shainet_attn_ctx* ctx, size_t data_floats, void* handle_out) {
     if (!ctx || !handle_out) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
     if (ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "exchange buffer already created");
+    if (data_floats == 0 || data_floats % 4 != 0) return fail(SHAINET_ATTN_E_INVALID, "exchange buffer size must be a positive multiple of 4 floats");
     DeviceGuard g(ctx->device);
-    const size_t bytes = COMM_FLAG_BYTES + data_floats * sizeof(float);
+    const size_t bytes = data_floats * (sizeof(float) + sizeof(unsigned long long));
     CU(cudaMalloc(&ctx->comm_base, bytes));
-    CU(cudaMemset(ctx->comm_base, 0, bytes));
-    CU(cudaMalloc(&ctx->comm_done_ticket, sizeof(unsigned)));
-    CU(cudaMemset(ctx->comm_done_ticket, 0, sizeof(unsigned)));
+    CU(cudaMemset(ctx->comm_base, 0, bytes));   // epoch 0 = nothing delivered
     ctx->comm_data_floats = data_floats;
     cudaIpcMemHandle_t h;
     CU(cudaIpcGetMemHandle(&h, ctx->comm_base));
@@ -911,31 +901,44 @@ int shainet_attn_comm_open(shainet_attn_ctx* ctx, const void* handles, int world
     return SHAINET_ATTN_OK;
 }
 
-int shainet_attn_comm_set_target(shainet_attn_ctx* ctx, long long out_offset_floats, long long lse_offset_floats,
-                                 int flag_index, unsigned epoch) {
+int shainet_attn_comm_set_target(shainet_attn_ctx* ctx, long long out_offset_floats, long long lse_offset_floats, unsigned epoch) {
     if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
     if (!ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers are not opened");
     if (out_offset_floats < 0 || out_offset_floats % 4 != 0) return fail(SHAINET_ATTN_E_INVALID, "output offset must be a non-negative multiple of 4 floats");
-    if (flag_index < 0 || (size_t)(flag_index + 1) * ctx->comm_world * sizeof(unsigned) > COMM_FLAG_BYTES)
-        return fail(SHAINET_ATTN_E_INVALID, "flag index %d out of range", flag_index);
+    if (epoch == 0) return fail(SHAINET_ATTN_E_INVALID, "epoch 0 is the empty state of the exchange buffer");
     ctx->gather_out_off = out_offset_floats;
     ctx->gather_lse_off = lse_offset_floats;
-    ctx->gather_flag = flag_index;
     ctx->gather_epoch = epoch;
     ctx->gather_armed = true;
     return SHAINET_ATTN_OK;
 }
 
-int shainet_attn_comm_wait(shainet_attn_ctx* ctx, int flag_index, unsigned epoch, void* stream) {
+int shainet_attn_comm_wait(shainet_attn_ctx* ctx, long long offset_floats, long long count_floats, unsigned epoch, void* stream) {
     if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
     if (!ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers are not opened");
-    if (flag_index < 0 || (size_t)(flag_index + 1) * ctx->comm_world * sizeof(unsigned) > COMM_FLAG_BYTES)
-        return fail(SHAINET_ATTN_E_INVALID, "flag index %d out of range", flag_index);
+    if (offset_floats < 0 || count_floats < 0 || (size_t)(offset_floats + count_floats) > ctx->comm_data_floats)
+        return fail(SHAINET_ATTN_E_INVALID, "range outside the exchange buffer");
+    if (epoch == 0) return fail(SHAINET_ATTN_E_INVALID, "epoch 0 is the empty state of the exchange buffer");
     DeviceGuard g(ctx->device);
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
-    CU(launch_gather_wait(reinterpret_cast<const unsigned*>(ctx->comm_base) + (size_t)flag_index * ctx->comm_world,
-                          ctx->comm_world, epoch, ctx->status_dev, s));
+    float* data = reinterpret_cast<float*>(ctx->comm_base);
+    const unsigned long long* words = reinterpret_cast<const unsigned long long*>(ctx->comm_base + ctx->comm_data_floats * sizeof(float));
+    CU(launch_gather_wait(words + offset_floats, data + offset_floats, count_floats, epoch, ctx->status_dev, s));
     return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_forward_dev_exchange(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                                      const float* v_new, float* out, int position, int append, float scale, unsigned flags,
+                                      long long out_offset_floats, long long lse_offset_floats, long long wait_offset_floats,
+                                      long long wait_count_floats, unsigned epoch, void* stream) {
+    int rc = shainet_attn_comm_set_target(ctx, out_offset_floats, lse_offset_floats, epoch);
+    if (rc) return rc;
+    rc = shainet_attn_forward_dev_at(ctx, kv, q, k_new, v_new, out, position, append, scale, flags, stream);
+    if (rc) {
+        ctx->gather_armed = false;
+        return rc;
+    }
+    return shainet_attn_comm_wait(ctx, wait_offset_floats, wait_count_floats, epoch, stream);
 }
 
 int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream) {
@@ -945,15 +948,15 @@ int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float
         return fail(SHAINET_ATTN_E_INVALID, "range outside the exchange buffer");
     DeviceGuard g(ctx->device);
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
-    CU(cudaMemcpyAsync(host_dst, reinterpret_cast<const float*>(ctx->comm_base + COMM_FLAG_BYTES) + offset_floats,
-                       floats * sizeof(float), cudaMemcpyDeviceToHost, s));
+    CU(cudaMemcpyAsync(host_dst, reinterpret_cast<const float*>(ctx->comm_base) + offset_floats, floats * sizeof(float),
+                       cudaMemcpyDeviceToHost, s));
     return SHAINET_ATTN_OK;
 }
 
 int shainet_attn_comm_data_ptr(shainet_attn_ctx* ctx, float** data_dev) {
     if (!ctx || !data_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
     if (!ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "no exchange buffer");
-    *data_dev = reinterpret_cast<float*>(ctx->comm_base + COMM_FLAG_BYTES);
+    *data_dev = reinterpret_cast<float*>(ctx->comm_base);
     return SHAINET_ATTN_OK;
 }
 

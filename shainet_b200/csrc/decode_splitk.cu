@@ -770,10 +770,20 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
         const float4 res = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
         *(reinterpret_cast<float4*>(out_row) + d4) = res;
         if (lse_out && d4 == 0) *lse_out = Mt + logf(Lt);
-        // the same row into every rank's exchange buffer: plain stores to peer memory
-        for (int p = 0; p < gt.world; ++p) {
-            *(reinterpret_cast<float4*>(gt.peer[p] + gt.out_offset + head_index * HD) + d4) = res;
-            if (gt.lse_offset >= 0 && d4 == 0) gt.peer[p][gt.lse_offset + head_index] = Mt + logf(Lt);
+        // the same row into every rank's exchange buffer as {value, epoch} words:
+        // plain 8-byte stores to peer memory, nothing to fence and nobody to wait for
+        if (gt.world > 0) {
+            const unsigned long long e = (unsigned long long)gt.epoch << 32;
+            const unsigned long long w0 = e | __float_as_uint(res.x), w1 = e | __float_as_uint(res.y);
+            const unsigned long long w2 = e | __float_as_uint(res.z), w3 = e | __float_as_uint(res.w);
+            const unsigned long long wl = e | __float_as_uint(Mt + logf(Lt));
+            for (int p = 0; p < gt.world; ++p) {
+                unsigned long long* dst = gt.peer_words[p] + gt.out_offset + head_index * HD + d4 * 4;
+                asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(w0), "l"(w1) : "memory");
+                asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(w2), "l"(w3) : "memory");
+                if (gt.lse_offset >= 0 && d4 == 0)
+                    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(gt.peer_words[p] + gt.lse_offset + head_index), "l"(wl) : "memory");
+            }
         }
     }
     __syncthreads();
@@ -994,27 +1004,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
                                            a.lse_out ? a.lse_out + hrow : nullptr, a.gather, hrow);
         }
-        if (a.gather.world > 0) {
-            // The merging CTA that finishes last raises this rank's flag in every
-            // peer's buffer.  The CTA barrier orders all threads' peer stores before
-            // thread 0's system-scope fence (fences are cumulative); the ticket is
-            // the local rendezvous (nobody waits), and the last taker's releasing
-            // store publishes every CTA's rows to the peers.
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                unsigned t;
-                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(a.gather.done_ticket) : "memory");
-                if (t == (unsigned)(nm * KV * a.batch - 1)) {
-                    *a.gather.done_ticket = 0u;
-                    asm volatile("fence.acq_rel.sys;" ::: "memory");
-                    for (int p = 0; p < a.gather.world; ++p)
-                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.gather.peer_flags[p] + (size_t)a.gather.flag_index * a.gather.world + a.gather.rank),
-                                     "r"(a.gather.epoch)
-                                     : "memory");
-                }
-            }
-        }
         TL_MARK(6, 0);
         return;
     }
@@ -1098,26 +1087,37 @@ cudaError_t dispatch_g(const A& a, F&& f) {
     }
 }
 
-// One thread per source rank polls this rank's own flag words (bounded).
-// Launched with programmatic stream serialization: the kernel behind it in the
-// stream may become resident at once and prefetch what does not depend on this
-// wait; its own grid-dependency wait then covers this kernel's completion.
-__global__ void gather_wait_kernel(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status) {
+// Receiver side of the exchange: every thread polls its {value, epoch} words until
+// they carry this epoch (bounded) and writes the values to the float area.
+// Launched with programmatic stream serialization: it polls while the kernel ahead
+// of it still runs, and the kernel behind it in the stream may become resident at
+// once and prefetch what does not depend on this wait; that kernel's own
+// grid-dependency wait then covers this kernel's completion.  The wait limit
+// therefore has to cover the run time of the kernel ahead as well.
+constexpr int GATHER_WAIT_THREADS = 256;
+__global__ void __launch_bounds__(GATHER_WAIT_THREADS) gather_wait_kernel(const unsigned long long* words, float* data,
+                                                                          long long count, unsigned epoch,
+                                                                          AttnStatus* status) {
     grid_launch_dependents();
-    grid_dependency_wait();
-    if ((int)threadIdx.x >= world) return;
-    const unsigned* p = flags_row + threadIdx.x;
     const unsigned long long t0 = globaltimer_ns();
-    while (true) {
-        unsigned v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-        if (v == epoch) return;
-        __nanosleep(100);
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 21;
-            return;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        while (true) {
+            unsigned long long w;
+            asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(words + i) : "memory");
+            if ((unsigned)(w >> 32) == epoch) {
+                data[i] = __uint_as_float((unsigned)w);
+                break;
+            }
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 21;
+                return;
+            }
         }
     }
+    // The words may arrive while the kernel ahead in the stream (this rank's own
+    // decode kernel) is still finishing; completing only after it keeps the
+    // stream's order for whatever follows.
+    grid_dependency_wait();
 }
 
 // out_full[(g*Hr + h)*hd + d] = sum_p w_p o_p / sum_p w_p with w_p = exp(lse_p - max lse)
@@ -1143,10 +1143,14 @@ __global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_p
 
 }  // namespace
 
-cudaError_t launch_gather_wait(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status, cudaStream_t s) {
+cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
+                               AttnStatus* status, cudaStream_t s) {
+    if (count <= 0) return cudaSuccess;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(32);
+    long long blocks = (count + 2 * GATHER_WAIT_THREADS - 1) / (2 * GATHER_WAIT_THREADS);   // two words per thread
+    if (blocks > 64) blocks = 64;
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(GATHER_WAIT_THREADS);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -1154,7 +1158,7 @@ cudaError_t launch_gather_wait(const unsigned* flags_row, int world, unsigned ep
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_wait_kernel, flags_row, world, epoch, status);
+    return cudaLaunchKernelEx(&cfg, gather_wait_kernel, words, data, count, epoch, status);
 }
 
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,

@@ -66,16 +66,16 @@ struct AttnArgs {
 // are spread over GPUs: every rank's exchange buffer (plain peer stores over
 // NVLink, no multicast), at this rank's slot, followed by a release flag.
 constexpr int MAX_PEERS = 16;
+// Delivery of the merged head rows into every rank's exchange buffer.  Each float
+// travels as one 8-byte word {value, epoch}: an aligned 8-byte store is indivisible,
+// so the receiver needs no fence and no separate flag; it polls the words
+// themselves and unpacks them.
 struct GatherTarget {
-    float* peer[MAX_PEERS];   // base of every rank's exchange buffer (this rank's own included)
-    unsigned* peer_flags[MAX_PEERS];  // flag words inside those buffers: [flag_index][source rank]
-    int world;                // 0 = no exchange
-    int rank;
-    long long out_offset;     // floats from a buffer's base to this rank's [heads*head_dim] slot
-    long long lse_offset;     // floats to this rank's [heads] log-sum-exp slot, or -1
-    int flag_index;
-    unsigned epoch;           // value stored to flags[flag_index][rank] of every peer once all heads are written
-    unsigned* done_ticket;    // local counter of merging CTAs that finished their peer stores (zero between launches)
+    unsigned long long* peer_words[MAX_PEERS];  // word area of every rank's exchange buffer (this rank's own included)
+    int world;
+    long long out_offset;     // in floats (= words): this rank's block of head rows
+    long long lse_offset;     // this rank's block of log-sum-exp values, or -1
+    unsigned epoch;           // never 0
 };
 
 // One decode token per sequence, everything in one launch (T == 1).
@@ -148,7 +148,8 @@ cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, 
                                float* out_full, cudaStream_t s);
 
 // Bounded wait until flags[flag_index][p] == epoch for every source rank p.
-cudaError_t launch_gather_wait(const unsigned* flags_row, int world, unsigned epoch, AttnStatus* status, cudaStream_t s);
+cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
+                               AttnStatus* status, cudaStream_t s);
 
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,

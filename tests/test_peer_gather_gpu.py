@@ -26,8 +26,8 @@ def ctx():
 
 def test_self_delivery_matches_the_plain_output(ctx):
     """world = 1: the kernel stores every head row and log-sum-exp into its own
-    exchange buffer at the armed offsets and raises its own flag; the values equal
-    what the same call leaves in `out`, and the oracle."""
+    exchange buffer at the armed offsets as {value, epoch} words, the wait kernel
+    unpacks them; the values equal what the same call leaves in `out`, and the oracle."""
     import torch
     import shainet_b200 as S
     rng = np.random.default_rng(6001)
@@ -52,9 +52,9 @@ def test_self_delivery_matches_the_plain_output(ctx):
         tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (q, k, v))
         off = step * slot
         ctx.set_lse_out(lse.data_ptr())
-        ctx.comm_set_target(off, off + H * hd, flag_index=step, epoch=step + 7)
+        ctx.comm_set_target(off, off + H * hd, epoch=step + 7)
         g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
-        ctx.comm_wait(step, step + 7, stream)
+        ctx.comm_wait(off, slot, step + 7, stream)
         got = np.empty(slot, np.float32)
         ctx.comm_read(off, got, stream)
         torch.cuda.synchronize()
@@ -67,13 +67,13 @@ def test_self_delivery_matches_the_plain_output(ctx):
     q, k, v = qkv(rng, shape, 4)
     tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (q, k, v))
     out4 = torch.empty(4 * H * hd, device=dev)
-    ctx.comm_set_target(0, -1, 0, 99)
+    ctx.comm_set_target(0, -1, 99)
     with pytest.raises(S.ShainetAttnError) as ei:
         g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out4.data_ptr(), 4, stream=stream)
     assert ei.value.code == _lib.E_UNSUPPORTED
     g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out4.data_ptr(), 4, stream=stream)
     ctx.sync()
-    ctx.comm_set_target(3 * slot, -1, 0, 1)   # one slot past the end of the buffer
+    ctx.comm_set_target(3 * slot, -1, 1)   # one slot past the end of the buffer
     with pytest.raises(S.ShainetAttnError) as ei:
         g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
     assert ei.value.code == _lib.E_INVALID
@@ -81,12 +81,12 @@ def test_self_delivery_matches_the_plain_output(ctx):
 
 
 def test_wait_for_a_flag_nobody_raises_reports_a_timeout():
-    """The flag wait is bounded: with no producer it gives up after about a second
+    """The wait for delivered words is bounded: with no producer it gives up after about a second
     and the next sync reports SHAINET_ATTN_E_DEVICE_WAIT; the context stays usable."""
     import shainet_b200 as S
     c = S.AttnContext(0)
     c.comm_open([c.comm_create(64)], 0)
-    c.comm_wait(2, 12345)
+    c.comm_wait(8, 16, 12345)
     with pytest.raises(S.ShainetAttnError) as ei:
         c.sync()
     assert ei.value.code == _lib.E_DEVICE_WAIT
@@ -137,9 +137,14 @@ for step in range(6):
     vl = v.reshape(1, KV, hd)[:, sp.kv_begin:sp.kv_begin + KVl].reshape(1, -1).copy()
     tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
     slot = step % layers_slots
-    ctx.comm_set_target((slot * world + rank) * pay, -1, slot, step + 1)
-    g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
-    ctx.comm_wait(slot, step + 1, stream)
+    if step % 2 == 0:
+        ctx.comm_set_target((slot * world + rank) * pay, -1, step + 1)
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
+        ctx.comm_wait(slot * world * pay, world * pay, step + 1, stream)
+    else:   # the same three steps as one call
+        g.forward_cached_dev_exchange(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), L0 + step, True,
+                                      (slot * world + rank) * pay, -1, slot * world * pay, world * pay, step + 1,
+                                      stream=stream)
     full = np.empty(world * pay, np.float32)
     ctx.comm_read(slot * world * pay, full, stream)
     torch.cuda.synchronize(); ctx.sync()
