@@ -42,7 +42,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_fused_kernel launch on the cfg5 shape at L = 32770
 # (ncu capture summarised in profiles/attn_decode_fused_kernel__cfg5_ctx32k.md): 138.3 MB for 134.26 MB algorithmic.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 138.3 / 134.26
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.37 / 134.26   # profiles/attn_decode_fused_kernel__cfg5_ctx32k.md, section 2
 
 
 def decode_bytes(wl, L, kv_heads=None):
@@ -385,6 +385,15 @@ def run_ours(args, wl, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
 
+    # ---- host cost of a layer call, measured on a burst short enough not to fill the launch queue ----
+    reset()
+    barrier()
+    t_burst = time.perf_counter()
+    for i in range(4):
+        step(i)
+    host_call_us = (time.perf_counter() - t_burst) * 1e6 / (4 * layers)
+    barrier()
+
     # ---- same region with F_INPUTS_READY: this bench's inputs are resident long before the
     # launches, so consecutive layers may overlap fully (reported beside the headline) ----
     ready_args = build_args(S.F_INPUTS_READY)
@@ -475,7 +484,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "config": {"workload": wl["name"], "layers": layers, "num_heads": H, "num_kv_heads": KV, "head_dim": hd,
                        "ctx": ctx_len, "sharding": f"{sp.groups} kv-head group(s) x {sp.seq_parts} sequence part(s) over {world} rank(s); " + ("no exchange" if world == 1 else ("head outputs stored into every rank's buffer by the decode kernel (8-byte value+epoch peer stores over NVLink), one wait-and-unpack kernel per layer" if peer else "torch.distributed all-gather of head outputs per layer")),
                        "l2": "working set per step (all layers' K/V) is far larger than L2; no flush needed",
-                       "host_enqueue_ms_per_step": t_enq * 1e3 / K,
+                       "host_enqueue_ms_per_step": t_enq * 1e3 / K, "host_us_per_layer_call": host_call_us,
                        "hbm_gbs_whole_step_per_gpu": bytes_per_launch * layers / (ms / K / 1e3) / 1e9},
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel", "achieved": achieved,
