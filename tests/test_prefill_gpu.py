@@ -75,3 +75,24 @@ def test_default_dispatch_uses_tensor_kernel_for_long_chunks(ctx):
     assert rel_err(a, ref) <= PREFILL_TOL
     assert not np.array_equal(a, b)
     g.close(); g2.close()
+
+
+@pytest.mark.parametrize("H,KV,hd,T", [(8, 8, 64, 300), (6, 2, 128, 520), (4, 4, 128, 128)],
+                         ids=["mha_3_row_tiles", "group3_5_row_tiles", "mha_one_row_tile"])
+def test_prefill_pairs_row_tiles_when_the_group_size_is_odd(ctx, H, KV, hd, T):
+    """With an odd group size a CTA takes two consecutive row tiles of one head instead of
+    two heads of a kv group; the tiles then see different numbers of K/V tiles, and with an
+    odd number of row tiles the last CTA has one empty tile."""
+    import shainet_b200 as S
+    rng = np.random.default_rng(3003)
+    shape = dict(H=H, KV=KV, hd=hd, theta=10000.0, qk_norm=False)
+    o, g = make_pair(ctx, shape, rng)
+    q, k, v = qkv(rng, shape, T)
+    ref = o.attend_cached(q, k, v, threads=8)
+    got = g.forward_cached(q, k, v, S.F_TENSOR)
+    assert rel_err(got, ref) <= PREFILL_TOL, rel_err(got, ref)
+    q, k, v = qkv(rng, shape, 70)      # a second chunk over the first
+    ref = o.attend_cached(q, k, v, threads=8)
+    got = g.forward_cached(q, k, v, S.F_TENSOR)
+    assert rel_err(got, ref) <= PREFILL_TOL, rel_err(got, ref)
+    g.close()
