@@ -533,6 +533,8 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (debugging / profiling)")
     ap.add_argument("--ctx", type=int, default=None, help="override the context length (debugging / profiling)")
+    ap.add_argument("--heads", type=str, default=None,
+                    help="override 'query_heads,kv_heads' (debugging: e.g. 8,1 on 2 ranks runs the sequence-split path)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="several ranks: gather head outputs with torch.distributed instead of the kernel's peer stores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -545,6 +547,9 @@ def main():
     if args.ctx:
         wl["ctx"] = args.ctx
         wl["name"] += f" [ctx={args.ctx}]"
+    if args.heads:
+        wl["H"], wl["KV"] = (int(x) for x in args.heads.split(","))
+        wl["name"] += f" [heads={args.heads}]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -795,10 +795,15 @@ int shainet_attn_forward_host(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const 
         CU(cudaMemcpyAsync(dk, k_new, kn * sizeof(float), cudaMemcpyHostToDevice, s));
         CU(cudaMemcpyAsync(dv, v_new, kn * sizeof(float), cudaMemcpyHostToDevice, s));
     }
-    rc = forward_device(ctx, kv, dq, dk, dv, ctx->dev_out.p, T, scale, flags, s);
+    // One decode token through the fused kernel: its merging CTAs store the few result
+    // rows straight into the pinned (device-visible) host buffer, which saves the
+    // device-to-host copy operation and its latency.
+    const bool direct_out = small && T == 1 && splitk_supported(kv->hs) &&
+                            !(flags & (SHAINET_ATTN_F_GENERIC | SHAINET_ATTN_F_UNFUSED | SHAINET_ATTN_F_TENSOR));
+    rc = forward_device(ctx, kv, dq, dk, dv, direct_out ? ctx->pin_out : ctx->dev_out.p, T, scale, flags, s);
     if (rc) return rc;
     if (small) {
-        CU(cudaMemcpyAsync(ctx->pin_out, ctx->dev_out.p, qn * sizeof(float), cudaMemcpyDeviceToHost, s));
+        if (!direct_out) CU(cudaMemcpyAsync(ctx->pin_out, ctx->dev_out.p, qn * sizeof(float), cudaMemcpyDeviceToHost, s));
         CU(cudaStreamSynchronize(s));
         memcpy(out, ctx->pin_out, qn * sizeof(float));
     } else {

@@ -103,68 +103,87 @@ from oracle import oracle as O
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
 dist.init_process_group("gloo")
-shape = Q30
+# "heads": two kv-head groups, one per rank.  "split": one kv head, the two ranks hold alternate positions.
+shape = Q30 if sys.argv[2] == "heads" else dict(H=8, KV=1, hd=128, theta=1e6, qk_norm=True)
 H, KV, hd = shape["H"], shape["KV"], shape["hd"]
 sp = S.sharding.plan(world, rank, H, KV)
 Hl, KVl = sp.head_count, sp.kv_count
+split = sp.seq_parts > 1
 rng = np.random.default_rng(6100)            # same stream on every rank: identical full inputs
 qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
 kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
 o = O.OracleAttention(H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn)
 ctx = S.AttnContext(rank)
 g = S.LlamaAttention(ctx, Hl, KVl, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn, initial_capacity=4096)
-L0 = 3000
+L0 = 3001
 q, k, v = qkv(rng, shape, L0)
 o.attend_cached(q, k, v, threads=8)
 kc, vc = o.export_cache()
-g.cache.import_(kc[sp.kv_begin:sp.kv_begin + KVl], vc[sp.kv_begin:sp.kv_begin + KVl])
-layers_slots = 2
-pay = Hl * hd
-mine = ctx.comm_create(layers_slots * world * pay)
+g.cache.import_(kc[sp.kv_begin:sp.kv_begin + KVl, sp.seq_part::sp.seq_parts],
+                vc[sp.kv_begin:sp.kv_begin + KVl, sp.seq_part::sp.seq_parts])
+assert len(g.cache) == sp.local_rows(L0)
+slots = 2
+pay = Hl * hd + (Hl if split else 0)
+mine = ctx.comm_create(slots * world * pay)
 handles = [None] * world
 dist.all_gather_object(handles, mine)
 ctx.comm_open(handles, rank)
 dist.barrier()
 dev = torch.device("cuda", rank)
 stream = torch.cuda.current_stream().cuda_stream
-out = torch.empty(pay, device=dev)
+out = torch.empty(Hl * hd, device=dev)
+merged = torch.empty(H * hd, device=dev)
 worst = 0.0
 for step in range(6):
+    pos = L0 + step
     q, k, v = qkv(rng, shape, 1)
     ref = o.attend_cached(q, k, v, threads=8)[0]
     ql = q.reshape(1, H, hd)[:, sp.head_begin:sp.head_begin + Hl].reshape(1, -1).copy()
     kl = k.reshape(1, KV, hd)[:, sp.kv_begin:sp.kv_begin + KVl].reshape(1, -1).copy()
     vl = v.reshape(1, KV, hd)[:, sp.kv_begin:sp.kv_begin + KVl].reshape(1, -1).copy()
     tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
-    slot = step % layers_slots
-    if step % 2 == 0:
-        ctx.comm_set_target((slot * world + rank) * pay, -1, step + 1)
+    slot = step % slots
+    mine_off = (slot * world + rank) * pay
+    lse_off = mine_off + Hl * hd if split else -1
+    own = sp.owns_position(pos)
+    if step % 2 == 0 and not split:
+        ctx.comm_set_target(mine_off, lse_off, step + 1)
         g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
         ctx.comm_wait(slot * world * pay, world * pay, step + 1, stream)
     else:   # the same three steps as one call
-        g.forward_cached_dev_exchange(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), L0 + step, True,
-                                      (slot * world + rank) * pay, -1, slot * world * pay, world * pay, step + 1,
-                                      stream=stream)
-    full = np.empty(world * pay, np.float32)
-    ctx.comm_read(slot * world * pay, full, stream)
-    torch.cuda.synchronize(); ctx.sync()
+        g.forward_cached_dev_exchange(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), pos, own,
+                                      mine_off, lse_off, slot * world * pay, world * pay, step + 1, stream=stream)
+    if split:
+        ctx.merge_parts(ctx.comm_data_ptr() + slot * world * pay * 4, world, sp.seq_parts, Hl, hd, merged.data_ptr(), stream)
+        torch.cuda.synchronize(); ctx.sync()
+        full = merged.cpu().numpy()
+    else:
+        full = np.empty(world * pay, np.float32)
+        ctx.comm_read(slot * world * pay, full, stream)
+        torch.cuda.synchronize(); ctx.sync()
     worst = max(worst, rel_err(full, ref))
     dist.barrier()       # a slot is rewritten two steps later; the host barrier keeps this test's reads simple
 assert worst <= DECODE_TOL, worst
+assert len(g.cache) == sp.local_rows(L0 + 6)
 dist.barrier()
 g.close(); ctx.close()
 print("RANK_OK", rank, worst)
 """
 
 
-def test_two_ranks_deliver_to_each_other(tmp_path):
+@pytest.mark.parametrize("mode", ["heads", "split"])
+def test_two_ranks_deliver_to_each_other(tmp_path, mode):
+    """Two processes, one GPU each.  "heads": each rank owns two of the four kv-head groups.
+    "split": one kv head, the ranks hold alternate positions, exchange (output, log-sum-exp)
+    and merge.  Both against the unsharded oracle at the decode tolerance."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = tmp_path / "worker.py"
     script.write_text(WORKER)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29541", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
-    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+    port = "29541" if mode == "heads" else "29542"
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=port, WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, mode], env=dict(env, RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
     outs = []
     for p in procs:
