@@ -95,18 +95,14 @@ template <int HD, int G>
 struct SKDefault {
     static constexpr int BR = 2 * (16 / G);
     static constexpr int TW = BR > 8 ? BR : 8;                         // rows per warp tile
-#ifdef SK_NW5
-    static constexpr int NW = G >= SK_NW5 ? 5 : 4;                     // consumer warps
-#else
-    static constexpr int NW = 4;                                       // consumer warps
-#endif
+    static constexpr int NW = 4;                                       // consumer warps (5, or 3 x 3 CTAs, measured slower)
     static constexpr bool BIG = 2 * TW * HD * 4 > 16 * 1024;           // ring + extras would not fit twice per SM
     static constexpr int SMEM_KB = BIG ? 216 : 110;                    // 2 x (110 + 1 KB reserved) fits 227 KB
     static constexpr int CTAS_PER_SM = BIG ? 1 : 2;
 };
 
 template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
-#ifdef SK_NOMATH
+#ifdef SK_NOMATH  // measurement build: the consumers release every tile untouched (results are wrong)
           int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = false>
 #else
           int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = true>
@@ -247,11 +243,7 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
     const int i16 = lane & 15, hw = lane >> 4;
     f32x2 acc2[16];
     score_batch<HD, G, C>(ks, 0, hw, i16, q, acc2);
-#ifdef SK_ROLL
-#pragma unroll 1
-#else
 #pragma unroll
-#endif
     for (int bb = 0; bb < C::NB; ++bb) {
         const int base = bb * C::BR;
         f32x2* ps = scratch + (bb & 1) * 48;
@@ -485,12 +477,9 @@ __device__ __forceinline__ void consume_slice(Smem<C>& sm, int ntiles, int rows,
         const float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
         const float* vs = ks + C::TILE_FLOATS;
         const int nrows = min(C::TW, rows - i * C::TW);
-#ifndef SK_NO_FULL_TILE_PATH
         if (C::MATH && nrows == C::TW) {
             consume_full_tile<HD, G, C>(ks, vs, q, st, ps, lane, scale);
-        } else
-#endif
-        {
+        } else {
             __syncwarp();
             consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::MATH ? C::NB : 0);
         }
@@ -690,9 +679,6 @@ __device__ __forceinline__ bool spin_until_equal(const unsigned* p, unsigned wan
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
             if (ld_acquire(p) == want) return true;
-#ifdef SK_SPIN_SLEEP
-            __nanosleep(SK_SPIN_SLEEP);
-#endif
         }
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
             if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = where;
