@@ -59,7 +59,7 @@ struct shainet_attn_ctx {
     int device = 0;
     int sm_count = 148;
     cudaStream_t stream = nullptr;
-    DevBuf q_rot, part, dev_in, dev_out;
+    DevBuf q_rot, part, part_words, dev_in, dev_out;   // part_words: {value, epoch} partials of single-sequence decode
     float* pin_in = nullptr;
     size_t pin_in_cap = 0;
     float* pin_out = nullptr;
@@ -74,8 +74,7 @@ struct shainet_attn_ctx {
     int live_caches = 0;
     unsigned* tickets = nullptr;        // split-merge tickets of the fused decode kernel, zero between launches
     size_t tickets_cap = 0;
-    unsigned epoch = 0;                 // flag value of the newest streaming-merge launch
-    size_t flags_offset = ~(size_t)0;   // where the flags start inside `tickets` (they move with the head shape)
+    unsigned epoch = 0;                 // tag of the newest word-merged decode launch
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
     float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
     // exchange buffer shared with the other ranks of the box (IPC): comm_data_floats
@@ -395,7 +394,22 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     f.status = ctx->status_dev;
     plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits);
     f.max_groups = fused_merge_groups(f.max_splits);
-    if (f.max_splits > 1) {
+    // A single sequence whose grid is fully resident merges through {value, epoch} words
+    // (8 bytes per partial float) polled by the merging CTAs; batched decode keeps float
+    // partials and the two-level tickets.
+    f.stream_merge = batch == 1 && f.max_splits > 1 && !(flags & SHAINET_ATTN_F_TICKET_MERGE) &&
+                     (long long)f.max_splits * hs.num_kv_heads <= (long long)ctx->sm_count * splitk_ctas_per_sm(hs);
+    if (f.max_splits > 1 && f.stream_merge) {
+        // a buffer of its own, written by nothing but this merge: a stale word can then
+        // only carry an older epoch
+        const size_t nw = 2 * splitk_scratch_floats(hs, batch, f.max_splits);
+        float* before = ctx->part_words.p;
+        rc = grow(ctx->part_words, nw, s);
+        if (rc) return rc;
+        if (ctx->part_words.p != before) CU(cudaMemsetAsync(ctx->part_words.p, 0, ctx->part_words.cap * sizeof(float), s));
+        f.part_o = ctx->part_words.p;
+        f.part_ml = f.part_o + 2 * (size_t)batch * hs.num_heads * f.max_splits * hs.head_dim;
+    } else if (f.max_splits > 1) {
         const size_t n1 = (splitk_scratch_floats(hs, batch, f.max_splits) + 3) & ~(size_t)3;  // keeps the second table 16-byte aligned
         const size_t n2 = splitk_scratch_floats(hs, batch, f.max_groups);
         rc = grow(ctx->part, n1 + n2, s);
@@ -405,25 +419,16 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
         f.part2_o = ctx->part.p + n1;
         f.part2_ml = f.part2_o + (size_t)batch * hs.num_heads * f.max_groups * hs.head_dim;
     }
-    // tickets (two levels), then the streaming-merge flags
+    // tickets (two levels) for the batched merge
     const size_t n_tickets = (size_t)batch * hs.num_kv_heads * (1 + f.max_groups);
-    const size_t n_flags = (size_t)batch * hs.num_kv_heads * f.max_splits;
-    const size_t cap_before = ctx->tickets_cap;
-    rc = ensure_tickets(ctx, n_tickets + n_flags, s);
+    rc = ensure_tickets(ctx, n_tickets, s);
     if (rc) return rc;
     f.tickets = ctx->tickets;
-    f.flags = ctx->tickets + n_tickets;
-    // Streaming merge needs every CTA of the grid resident at once and flags that
-    // cannot hold this launch's value yet: a fresh epoch per launch, and a wipe
-    // whenever the layout of the buffer changes or the counter wraps.
-    f.stream_merge = batch == 1 && f.max_splits > 1 && !(flags & SHAINET_ATTN_F_TICKET_MERGE) &&
-                     (long long)f.max_splits * hs.num_kv_heads <= (long long)ctx->sm_count * splitk_ctas_per_sm(hs);
     if (f.stream_merge) {
-        const bool relayout = ctx->tickets_cap != cap_before || ctx->flags_offset != n_tickets;
-        if (relayout || ctx->epoch == 0xffffffffu) {
-            CU(cudaMemsetAsync(ctx->tickets, 0, ctx->tickets_cap * sizeof(unsigned), s));
+        // a fresh epoch per launch; at the wrap of the counter every old word is wiped
+        if (ctx->epoch == 0xffffffffu) {
+            CU(cudaMemsetAsync(ctx->part_words.p, 0, ctx->part_words.cap * sizeof(float), s));
             ctx->epoch = 0;
-            ctx->flags_offset = n_tickets;
         }
         f.epoch = ++ctx->epoch;
     }
@@ -543,7 +548,7 @@ int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
     if (c->live_caches != 0) return fail(SHAINET_ATTN_E_STATE, "%d caches still alive", c->live_caches);
     DeviceGuard g(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    for (DevBuf* b : {&c->q_rot, &c->part, &c->dev_in, &c->dev_out})
+    for (DevBuf* b : {&c->q_rot, &c->part, &c->part_words, &c->dev_in, &c->dev_out})
         if (b->p) cudaFree(b->p);
     if (c->pin_in) cudaFreeHost(c->pin_in);
     if (c->pin_out) cudaFreeHost(c->pin_out);
@@ -599,7 +604,7 @@ int shainet_attn_ctx_timing_read(shainet_attn_ctx* c, double* total_ms, int* lau
 
 size_t shainet_attn_ctx_scratch_bytes(shainet_attn_ctx* c) {
     if (!c) return 0;
-    return (c->q_rot.cap + c->part.cap + c->dev_in.cap + c->dev_out.cap) * sizeof(float);
+    return (c->q_rot.cap + c->part.cap + c->part_words.cap + c->dev_in.cap + c->dev_out.cap) * sizeof(float);
 }
 
 int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,

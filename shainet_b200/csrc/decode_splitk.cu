@@ -654,61 +654,81 @@ __device__ void merge_partials(const float* po, const float* pml, size_t stride,
     }
 }
 
-// ---- streaming merge (single sequence, whole grid co-resident) ----
-// Every CTA publishes its partial and raises a flag (the launch's epoch value,
-// so flags never need clearing).  The first min(G, splits) CTAs of a kv head
-// each take one query head: they wait - bounded - for all flags of the kv head
-// and fold that head's partials.  Compared with the ticket scheme this removes
-// one fence + atomic + L2 round trip from the end of the kernel and spreads the
-// merge over G CTAs.  It needs all CTAs of the grid to be resident at once,
-// which the host guarantees before selecting it.
-__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ void st_release(unsigned* p, unsigned v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ bool spin_until_equal(const unsigned* p, unsigned want, AttnStatus* status, int where) {
-    if (ld_acquire(p) == want) return true;
-    const unsigned long long t0 = globaltimer_ns();
-    while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 16; ++i) {
-            if (ld_acquire(p) == want) return true;
-        }
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-            if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = where;
-            return false;
-        }
-    }
-}
-
-// All partials [first .. first+count) of one query head, folded by the whole CTA.
+// Split partials that travel as {value, epoch} words: a CTA publishes its partial with
+// plain 8-byte stores (each indivisible), and the merging CTA polls the words
+// themselves, so the last partial costs one store and one load on the critical
+// path instead of fence + flag + flag poll + load.  One call folds all `count`
+// partials of 64 columns of one query head: 16 threads per partial, THREADS/16
+// partials side by side, 8 partials requested per thread before the first is used.
 template <int HD, int THREADS>
-__device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int count, float* smem, float* out_row,
-                               float* lse_out, const GatherTarget& gt, size_t head_index) {
-    constexpr int D4 = HD / 4;
-    constexpr int NPG = THREADS / D4;   // partial groups walking the splits in parallel
-    constexpr int MAXB = 16;            // partials a thread requests before it uses any: one L2 round trip for <= NPG*16 splits
+__device__ bool merge_head_words(const unsigned long long* po, const unsigned long long* pml, size_t e0, int count,
+                                 unsigned epoch, float* smem, float* out_row, float* lse_out, const GatherTarget& gt,
+                                 size_t head_index, int half, AttnStatus* status) {
+    constexpr int D4 = 16;
+    constexpr int NPG = THREADS / D4;
+    constexpr int MAXB = 8;
     const int pg = threadIdx.x / D4, d4 = threadIdx.x - pg * D4;
-    const float2* ml = reinterpret_cast<const float2*>(pml) + e0;
-    const float4* src = reinterpret_cast<const float4*>(po + e0 * HD) + d4;
+    const int col = half * 64 + d4 * 4;
+    const unsigned long long* src = po + e0 * HD + col;
+    const unsigned long long* ml = pml + e0 * 2;
     float M = -INFINITY, L = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool ok = true;
+    const unsigned long long t0 = globaltimer_ns();
+    auto ld2 = [](const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+        asm volatile("ld.relaxed.gpu.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    };
     if (pg < NPG) {
-        for (int s0 = pg; s0 < count; s0 += NPG * MAXB) {
+        for (int s0 = pg; s0 < count && ok; s0 += NPG * MAXB) {
+            unsigned long long w[MAXB][6];
+#pragma unroll
+            for (int k = 0; k < MAXB; ++k) {
+                const int sidx = s0 + k * NPG;
+                if (sidx < count) {
+                    ld2(src + (size_t)sidx * HD, w[k][0], w[k][1]);
+                    ld2(src + (size_t)sidx * HD + 2, w[k][2], w[k][3]);
+                    ld2(ml + (size_t)sidx * 2, w[k][4], w[k][5]);
+                }
+            }
+            // words that do not carry this launch's epoch yet are requested again, all of
+            // them in one round, until none is left (bounded)
+            while (true) {
+                bool all = true;
+#pragma unroll
+                for (int k = 0; k < MAXB; ++k) {
+                    const int sidx = s0 + k * NPG;
+                    if (sidx < count) {
+                        bool good = true;
+#pragma unroll
+                        for (int j = 0; j < 6; ++j) good = good && (unsigned)(w[k][j] >> 32) == epoch;
+                        if (!good) {
+                            all = false;
+                            ld2(src + (size_t)sidx * HD, w[k][0], w[k][1]);
+                            ld2(src + (size_t)sidx * HD + 2, w[k][2], w[k][3]);
+                            ld2(ml + (size_t)sidx * 2, w[k][4], w[k][5]);
+                        }
+                    }
+                }
+                if (all) break;
+                if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                    if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 3;
+                    ok = false;
+                    break;
+                }
+            }
             float2 mv[MAXB];
             float4 v[MAXB];
 #pragma unroll
             for (int k = 0; k < MAXB; ++k) {
                 const int sidx = s0 + k * NPG;
-                const bool in = sidx < count;
-                mv[k] = in ? __ldcg(ml + sidx) : make_float2(-INFINITY, 0.f);
-                v[k] = in ? __ldcg(src + (size_t)sidx * D4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (sidx < count) {
+                    v[k] = make_float4(__uint_as_float((unsigned)w[k][0]), __uint_as_float((unsigned)w[k][1]),
+                                       __uint_as_float((unsigned)w[k][2]), __uint_as_float((unsigned)w[k][3]));
+                    mv[k] = make_float2(__uint_as_float((unsigned)w[k][4]), __uint_as_float((unsigned)w[k][5]));
+                } else {
+                    v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    mv[k] = make_float2(-INFINITY, 0.f);
+                }
             }
             float Mc = M;
 #pragma unroll
@@ -732,8 +752,8 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
         sa[pg * D4 + d4] = acc;
         sm2[pg * D4 + d4] = make_float2(M, L);
     }
-    __syncthreads();
-    if (pg == 0) {
+    ok = __syncthreads_and(ok);
+    if (ok && pg == 0) {
         const float4* sa = reinterpret_cast<const float4*>(smem);
         const float2* sm2 = reinterpret_cast<const float2*>(smem + NPG * D4 * 4);
         float Mt = -INFINITY;
@@ -754,8 +774,9 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
         }
         const float inv = 1.0f / Lt;
         const float4 res = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
-        *(reinterpret_cast<float4*>(out_row) + d4) = res;
-        if (lse_out && d4 == 0) *lse_out = Mt + logf(Lt);
+        *reinterpret_cast<float4*>(out_row + col) = res;
+        const bool writes_lse = half == 0 && d4 == 0;
+        if (lse_out && writes_lse) *lse_out = Mt + logf(Lt);
         // the same row into every rank's exchange buffer as {value, epoch} words:
         // plain 8-byte stores to peer memory, nothing to fence and nobody to wait for
         if (gt.world > 0) {
@@ -764,15 +785,16 @@ __device__ void merge_head_cta(const float* po, const float* pml, size_t e0, int
             const unsigned long long w2 = e | __float_as_uint(res.z), w3 = e | __float_as_uint(res.w);
             const unsigned long long wl = e | __float_as_uint(Mt + logf(Lt));
             for (int p = 0; p < gt.world; ++p) {
-                unsigned long long* dst = gt.peer_words[p] + gt.out_offset + head_index * HD + d4 * 4;
+                unsigned long long* dst = gt.peer_words[p] + gt.out_offset + head_index * HD + col;
                 asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(w0), "l"(w1) : "memory");
                 asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(w2), "l"(w3) : "memory");
-                if (gt.lse_offset >= 0 && d4 == 0)
+                if (gt.lse_offset >= 0 && writes_lse)
                     asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(gt.peer_words[p] + gt.lse_offset + head_index), "l"(wl) : "memory");
             }
         }
     }
     __syncthreads();
+    return ok;
 }
 
 // The calling CTA has published something and takes a ticket; true for the
@@ -953,6 +975,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
     __syncthreads();
     const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
+    const bool words = a.stream_merge && nsplit_here > 1;   // partials as {value, epoch} words
+    unsigned long long* pw = reinterpret_cast<unsigned long long*>(a.part_o);
+    unsigned long long* pmlw = reinterpret_cast<unsigned long long*>(a.part_ml);
+    const unsigned long long ew = (unsigned long long)a.epoch << 32;
     for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
         const int g = e / HD, d = e - g * HD;
         float acc, M, L;
@@ -963,32 +989,39 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             if (a.lse_out && d == 0) a.lse_out[(size_t)r * H + h] = M + logf(L);
         } else {
             const size_t pidx = ((size_t)r * H + h) * a.max_splits + split;
-            a.part_o[pidx * HD + d] = acc;
-            if (d == 0) {
-                a.part_ml[pidx * 2] = M;
-                a.part_ml[pidx * 2 + 1] = L;
+            if (words) {
+                asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(pw + pidx * HD + d), "l"(ew | __float_as_uint(acc)) : "memory");
+                if (d == 0) {
+                    asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(pmlw + pidx * 2), "l"(ew | __float_as_uint(M)),
+                                 "l"(ew | __float_as_uint(L))
+                                 : "memory");
+                }
+            } else {
+                a.part_o[pidx * HD + d] = acc;
+                if (d == 0) {
+                    a.part_ml[pidx * 2] = M;
+                    a.part_ml[pidx * 2 + 1] = L;
+                }
             }
         }
     }
     TL_MARK(4, 0);
     if (nsplit_here == 1) return;
     if (a.stream_merge) {
-        unsigned* flags = a.flags + ((size_t)r * KV + kv_h) * a.max_splits;
-        // The CTA barrier orders every thread's partial stores before thread 0's
-        // releasing store (release is cumulative), so no per-thread fence is needed.
-        __syncthreads();
-        if (threadIdx.x == 0) st_release(flags + split, a.epoch);
-        const int nm = min(G, nsplit_here);
+        // The first CTAs of the kv head fold the partials, 64 columns of one query head at
+        // a time; they poll the words themselves (bounded), nobody else waits for anything.
+        constexpr int HALVES = HD / 64;
+        const int nm = min(G * HALVES, nsplit_here);
         if (split >= nm) return;
-        bool seen = true;
-        for (int sidx = threadIdx.x; sidx < nsplit_here; sidx += C::THREADS)
-            seen = spin_until_equal(flags + sidx, a.epoch, a.status, 3) && seen;
-        if (!__syncthreads_and(seen)) return;   // acquiring loads + barrier: the partials are visible to the CTA
+        __syncthreads();   // the ring area is reused as merge scratch: every thread is done with merge_warps
         TL_MARK(7, 0);
-        for (int g = split; g < G; g += nm) {
+        for (int m = split; m < G * HALVES; m += nm) {
+            const int g = m / HALVES, half = m - g * HALVES;
             const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
-            merge_head_cta<HD, C::THREADS>(a.part_o, a.part_ml, hrow * a.max_splits, nsplit_here, sm.stages, a.out + hrow * HD,
-                                           a.lse_out ? a.lse_out + hrow : nullptr, a.gather, hrow);
+            if (!merge_head_words<HD, C::THREADS>(pw, pmlw, hrow * a.max_splits, nsplit_here, a.epoch, sm.stages,
+                                                  a.out + hrow * HD, a.lse_out ? a.lse_out + hrow : nullptr, a.gather, hrow,
+                                                  half, a.status))
+                return;
         }
         TL_MARK(6, 0);
         return;

@@ -103,9 +103,9 @@ struct FusedArgs {
     int chunk_rows;
     int max_splits;
     int max_groups;
-    unsigned* flags;       // [batch*num_kv_heads, max_splits] streaming-merge flags (epoch values)
-    unsigned epoch;        // this launch's flag value, never 0, never reused while old flags exist
-    int stream_merge;      // merge by flag-polling CTAs (single sequence, grid fully resident) instead of tickets
+    unsigned epoch;        // this launch's tag in the {value, epoch} partial words: never 0, never reused while old words exist
+    int stream_merge;      // partials travel as {value, epoch} words and are folded by CTAs that poll them (single
+                           // sequence, grid fully resident); part_o / part_ml then point at 8-byte words, not floats
     int unsafe_tail;       // newest cache rows a still-running previous grid may be writing
     int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
     int pos_delta;         // RoPE position of the new token minus the rows already cached (0 unless the sequence is split over ranks)
@@ -147,7 +147,7 @@ cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s);
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
                                float* out_full, cudaStream_t s);
 
-// Bounded wait until flags[flag_index][p] == epoch for every source rank p.
+// Bounded wait until `count` exchange words carry `epoch`; unpacks them into `data`.
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
                                AttnStatus* status, cudaStream_t s);
 
