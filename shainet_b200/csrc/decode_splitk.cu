@@ -880,8 +880,19 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             wk0[k] = a.k_norm ? a.k_norm[i] : 1.0f;
             wk1[k] = a.k_norm ? a.k_norm[i + HD / 2] : 1.0f;
         }
-        if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
         const int items = G + (owns_new ? 2 : 0);   // q rows of the group, then the new k row, then the new v row
+        // Ask L2 for this warp's input rows now: whoever still writes them does so through
+        // L2, so the loads after the wait see the final values and no longer go to DRAM.
+#pragma unroll
+        for (int n = 0; n < MAXIT; ++n) {
+            const int it = warp + n * C::NW;
+            if (it < items && lane < HD / 32) {
+                const float* src = it < G ? a.q + ((size_t)r * H + kv_h * G + it) * HD
+                                          : (it == G ? a.k_new : a.v_new) + ((size_t)r * KV + kv_h) * HD;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(src + lane * 32));
+            }
+        }
+        if (!a.inputs_ready) grid_dependency_wait();   // q, k_new, v_new may come from the previous grid
         // (1) all of this warp's rows in one round of loads: x[n][c] = column lane + 32c
         float x[MAXIT][2 * PL];
 #pragma unroll
