@@ -80,15 +80,18 @@ int main(int argc, char** argv) {
     typedef int (*tl_t)(unsigned long long*);
     auto tl = (tl_t)dlsym(h, "shainet_debug_timeline");
     if (tl) {
-        const int NCTA = 320, NMARK = 8;
+        const int NCTA = 320, NMARK = 16;
         std::vector<unsigned long long> buf((size_t)64 * NCTA * NMARK);
         if (tl(buf.data()) != 0) { printf("timeline read failed\n"); return 1; }
-        // marks: 0 CTA resident, 2 consumers start, 3 consumers done, 4 partial written, 7 flags seen, 6 merged
+        // marks: 0 CTA resident, 2 consumers start, 3 first consumer warp done, 8 .. its state folded, 9 all warps done,
+        // 10 states parked, 4 partial written, 7 merging CTAs start polling, 6 merged
         const char* names[] = {"CTA resident: mean", "CTA resident: last", "consumers start: mean", "consumers start: last",
                                "consumers done: first", "consumers done: mean", "consumers done: last",
-                               "partial written: mean", "partial written: last", "flags seen: first", "flags seen: last",
-                               "merged: first", "merged: last", "period"};
-        double acc[14] = {0};
+                               "partial written: mean", "partial written: last", "merge starts: first", "merge starts: last",
+                               "merged: first", "merged: last", "period", "warp 0 done -> all warps done: mean",
+                               "all warps done -> parked: mean", "parked -> partial written: mean",
+                               "warp 0 done -> all warps done: max"};
+        double acc[18] = {0};
         int used = 0;
         unsigned long long prev_t0 = 0;
         for (int L = 8; L < 56; ++L) {
@@ -98,7 +101,7 @@ int main(int argc, char** argv) {
             if (n == 0) { prev_t0 = 0; continue; }
             unsigned long long t0 = ~0ull;
             for (int c = 0; c < n; ++c) t0 = std::min(t0, t[c * NMARK]);
-            double v[14] = {0, 0, 0, 0, 1e30, 0, 0, 0, 0, 1e30, 0, 1e30, 0, 0};
+            double v[18] = {0, 0, 0, 0, 1e30, 0, 0, 0, 0, 1e30, 0, 1e30, 0, 0, 0, 0, 0, 0};
             for (int c = 0; c < n; ++c) {
                 auto rel = [&](int k) { return (double)(long long)(t[c * NMARK + k] - t0) * 1e-3; };
                 v[0] += rel(0) / n; v[1] = std::max(v[1], rel(0));
@@ -107,15 +110,17 @@ int main(int argc, char** argv) {
                 v[7] += rel(4) / n; v[8] = std::max(v[8], rel(4));
                 if (t[c * NMARK + 7]) { v[9] = std::min(v[9], rel(7)); v[10] = std::max(v[10], rel(7)); }
                 if (t[c * NMARK + 6]) { v[11] = std::min(v[11], rel(6)); v[12] = std::max(v[12], rel(6)); }
+                v[14] += (rel(9) - rel(3)) / n; v[15] += (rel(10) - rel(9)) / n; v[16] += (rel(4) - rel(10)) / n;
+                v[17] = std::max(v[17], rel(9) - rel(3));
             }
             if (prev_t0 == 0) { prev_t0 = t0; continue; }
             v[13] = (double)(long long)(t0 - prev_t0) * 1e-3;
             prev_t0 = t0;
-            for (int k = 0; k < 14; ++k) acc[k] += v[k];
+            for (int k = 0; k < 18; ++k) acc[k] += v[k];
             ++used;
         }
         printf("device timeline, us after the first CTA of a launch became resident (mean over %d launches)\n", used);
-        for (int k = 0; k < 14 && used; ++k) printf("  %-26s %7.2f\n", names[k], acc[k] / used);
+        for (int k = 0; k < 18 && used; ++k) printf("  %-40s %7.2f\n", names[k], acc[k] / used);
     }
     return 0;
 }

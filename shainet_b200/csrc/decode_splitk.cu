@@ -43,10 +43,10 @@ namespace shainet {
 namespace {
 
 #ifdef SK_TIMELINE
-// debug builds only: per-CTA timestamps of the fused kernel, [launch % 64][cta][8]
-__device__ unsigned long long g_timeline[64 * 320 * 8];
+// debug builds only: per-CTA timestamps of the fused kernel, [launch % 64][cta][16]
+__device__ unsigned long long g_timeline[64 * 320 * 16];
 __device__ unsigned g_timeline_launch;
-#define TL_MARK(k, tid) do { if (threadIdx.x == (tid)) g_timeline[((a.epoch & 63) * 320 + blockIdx.y * gridDim.x + blockIdx.x) * 8 + (k)] = globaltimer_ns(); } while (0)
+#define TL_MARK(k, tid) do { if (threadIdx.x == (tid)) g_timeline[((a.epoch & 63) * 320 + blockIdx.y * gridDim.x + blockIdx.x) * 16 + (k)] = globaltimer_ns(); } while (0)
 #else
 #define TL_MARK(k, tid) do { } while (0)
 #endif
@@ -981,37 +981,81 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
         finish_warp<HD, G, C>(st);
     }
+    TL_MARK(8, 0);
     __syncthreads();  // every issued copy has landed; the ring is free
+    TL_MARK(9, 0);
     if (a.inputs_ready) grid_dependency_wait();  // the shared scratch below may still be in use by the previous grid
     if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
     __syncthreads();
+    TL_MARK(10, 0);
     const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
     const bool words = a.stream_merge && nsplit_here > 1;   // partials as {value, epoch} words
     unsigned long long* pw = reinterpret_cast<unsigned long long*>(a.part_o);
     unsigned long long* pmlw = reinterpret_cast<unsigned long long*>(a.part_ml);
     const unsigned long long ew = (unsigned long long)a.epoch << 32;
-    for (int e = threadIdx.x; e < G * HD; e += C::THREADS) {
-        const int g = e / HD, d = e - g * HD;
-        float acc, M, L;
-        merge_warps<HD, G, C>(sm.stages, g, d, acc, M, L);
-        const int h = kv_h * G + g;
-        if (nsplit_here == 1) {
-            a.out[((size_t)r * H + h) * HD + d] = acc / L;
-            if (a.lse_out && d == 0) a.lse_out[(size_t)r * H + h] = M + logf(L);
-        } else {
-            const size_t pidx = ((size_t)r * H + h) * a.max_splits + split;
-            if (words) {
-                asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(pw + pidx * HD + d), "l"(ew | __float_as_uint(acc)) : "memory");
-                if (d == 0) {
-                    asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(pmlw + pidx * 2), "l"(ew | __float_as_uint(M)),
-                                 "l"(ew | __float_as_uint(L))
-                                 : "memory");
-                }
+    // Fold the NW warp states: the per-head weights once (G threads), then four
+    // columns per thread and iteration.
+    {
+        const float* mo = sm.stages;                              // [NW][G][HD]
+        const float* mm = mo + (size_t)C::NW * G * HD;            // [NW][G]
+        const float* ml = mm + C::NW * G;                         // [NW][G]
+        float* wts = sm.warp_scratch;                             // [NW][G] weights, then max[G], sum[G]
+        if (threadIdx.x < G) {
+            const int g = threadIdx.x;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < C::NW; ++w) M = fmaxf(M, mm[w * G + g]);
+            float L = 0.0f;
+#pragma unroll
+            for (int w = 0; w < C::NW; ++w) {
+                const float mw = mm[w * G + g];
+                const float wt = (mw == -INFINITY) ? 0.0f : exp2f((mw - M) * LOG2E);
+                wts[w * G + g] = wt;
+                L = fmaf(wt, ml[w * G + g], L);
+            }
+            wts[C::NW * G + g] = M;
+            wts[C::NW * G + G + g] = L;
+        }
+        __syncthreads();
+        for (int e4 = threadIdx.x; e4 < G * HD / 4; e4 += C::THREADS) {
+            const int g = e4 / (HD / 4), d = (e4 - g * (HD / 4)) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < C::NW; ++w) {
+                const float wt = wts[w * G + g];
+                const float4 o = *reinterpret_cast<const float4*>(mo + ((size_t)w * G + g) * HD + d);
+                acc.x = fmaf(wt, o.x, acc.x);
+                acc.y = fmaf(wt, o.y, acc.y);
+                acc.z = fmaf(wt, o.z, acc.z);
+                acc.w = fmaf(wt, o.w, acc.w);
+            }
+            const float M = wts[C::NW * G + g], L = wts[C::NW * G + G + g];
+            const int h = kv_h * G + g;
+            if (nsplit_here == 1) {
+                *reinterpret_cast<float4*>(a.out + ((size_t)r * H + h) * HD + d) =
+                    make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
+                if (a.lse_out && d == 0) a.lse_out[(size_t)r * H + h] = M + logf(L);
             } else {
-                a.part_o[pidx * HD + d] = acc;
-                if (d == 0) {
-                    a.part_ml[pidx * 2] = M;
-                    a.part_ml[pidx * 2 + 1] = L;
+                const size_t pidx = ((size_t)r * H + h) * a.max_splits + split;
+                if (words) {
+                    unsigned long long* dst = pw + pidx * HD + d;
+                    asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(ew | __float_as_uint(acc.x)),
+                                 "l"(ew | __float_as_uint(acc.y))
+                                 : "memory");
+                    asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(ew | __float_as_uint(acc.z)),
+                                 "l"(ew | __float_as_uint(acc.w))
+                                 : "memory");
+                    if (d == 0) {
+                        asm volatile("st.relaxed.gpu.global.v2.b64 [%0], {%1, %2};" ::"l"(pmlw + pidx * 2), "l"(ew | __float_as_uint(M)),
+                                     "l"(ew | __float_as_uint(L))
+                                     : "memory");
+                    }
+                } else {
+                    *reinterpret_cast<float4*>(a.part_o + pidx * HD + d) = acc;
+                    if (d == 0) {
+                        a.part_ml[pidx * 2] = M;
+                        a.part_ml[pidx * 2 + 1] = L;
+                    }
                 }
             }
         }
@@ -1364,6 +1408,6 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
 
 #ifdef SK_TIMELINE
 extern "C" int shainet_debug_timeline(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, shainet::g_timeline, sizeof(unsigned long long) * 64 * 320 * 8);
+    return (int)cudaMemcpyFromSymbol(host_out, shainet::g_timeline, sizeof(unsigned long long) * 64 * 320 * 16);
 }
 #endif
