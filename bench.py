@@ -42,7 +42,7 @@ WORKLOADS = {
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_fused_kernel launch on the cfg5 shape at L = 32770
 # (ncu capture summarised in profiles/attn_decode_fused_kernel__cfg5_ctx32k.md): 138.3 MB for 134.26 MB algorithmic.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.37 / 134.26   # profiles/attn_decode_fused_kernel__cfg5_ctx32k.md, section 2
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.3 / 134.26   # profiles/attn_decode_fused_kernel__cfg5_ctx32k.md, section 2
 
 
 def decode_bytes(wl, L, kv_heads=None):
