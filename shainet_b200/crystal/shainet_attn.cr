@@ -39,6 +39,46 @@ module SHAInet
     fun forward_dev = shainet_attn_forward_dev(ctx : Ctx, kv : Kv, q : Float32*, k_new : Float32*, v_new : Float32*,
                                                out_ptr : Float32*, new_tokens : Int32, scale : Float32, flags : UInt32,
                                                stream : Void*) : Int32
+    fun forward_batched_dev = shainet_attn_forward_batched_dev(ctx : Ctx, kvs : Kv*, batch : Int32, q : Float32*,
+                                                               k_new : Float32*, v_new : Float32*, out_ptr : Float32*,
+                                                               scale : Float32, flags : UInt32, stream : Void*) : Int32
+
+    # measurement and bookkeeping
+    fun ctx_scratch_bytes = shainet_attn_ctx_scratch_bytes(ctx : Ctx) : LibC::SizeT
+    fun ctx_timing_enable = shainet_attn_ctx_timing_enable(ctx : Ctx, enable : Int32) : Int32
+    fun ctx_timing_read = shainet_attn_ctx_timing_read(ctx : Ctx, total_ms : Float64*, launches : Int32*) : Int32
+    fun kv_fill_normal = shainet_attn_kv_fill_normal(kv : Kv, len : Int32, seed : UInt64) : Int32
+    fun kv_device_ptrs = shainet_attn_kv_device_ptrs(kv : Kv, k_dev : Float32**, v_dev : Float32**) : Int32
+
+    # a block sharded over the GPUs of one box (one process per GPU)
+    fun ctx_set_lse_out = shainet_attn_ctx_set_lse_out(ctx : Ctx, lse_dev : Float32*) : Int32
+    fun forward_dev_at = shainet_attn_forward_dev_at(ctx : Ctx, kv : Kv, q : Float32*, k_new : Float32*, v_new : Float32*,
+                                                     out_ptr : Float32*, position : Int32, append : Int32, scale : Float32,
+                                                     flags : UInt32, stream : Void*) : Int32
+    fun merge_parts = shainet_attn_merge_parts(ctx : Ctx, gathered_dev : Float32*, world : Int32, seq_parts : Int32,
+                                               heads_per_rank : Int32, head_dim : Int32, out_full_dev : Float32*,
+                                               stream : Void*) : Int32
+    fun comm_create = shainet_attn_comm_create(ctx : Ctx, data_floats : LibC::SizeT, handle_out : Void*) : Int32
+    fun comm_open = shainet_attn_comm_open(ctx : Ctx, handles : Void*, world : Int32, rank : Int32) : Int32
+    fun comm_set_target = shainet_attn_comm_set_target(ctx : Ctx, out_offset_floats : Int64, lse_offset_floats : Int64,
+                                                       epoch : UInt32) : Int32
+    fun comm_wait = shainet_attn_comm_wait(ctx : Ctx, offset_floats : Int64, count_floats : Int64, epoch : UInt32,
+                                           stream : Void*) : Int32
+    fun forward_dev_exchange = shainet_attn_forward_dev_exchange(ctx : Ctx, kv : Kv, q : Float32*, k_new : Float32*,
+                                                                 v_new : Float32*, out_ptr : Float32*, position : Int32,
+                                                                 append : Int32, scale : Float32, flags : UInt32,
+                                                                 out_offset_floats : Int64, lse_offset_floats : Int64,
+                                                                 wait_offset_floats : Int64, wait_count_floats : Int64,
+                                                                 epoch : UInt32, stream : Void*) : Int32
+    fun comm_read = shainet_attn_comm_read(ctx : Ctx, offset_floats : Int64, host_dst : Float32*, floats : LibC::SizeT,
+                                           stream : Void*) : Int32
+    fun comm_data_ptr = shainet_attn_comm_data_ptr(ctx : Ctx, data_dev : Float32**) : Int32
+
+    # one decode token with the split partials in a fixed array inside the library (no allocation)
+    fun decode_noalloc = shainet_attn_decode_noalloc(q : Float32*, k_cache : Float32*, v_cache : Float32*, out_ptr : Float32*,
+                                                     start_pos : Int32, num_heads : Int32, heads_per_kv : Int32,
+                                                     head_dim : Int32, capacity : Int32, scale : Float32,
+                                                     stream : Void*) : Int32
   end
 
   # Thin, exception-raising wrapper in the style of SHAInet::CUDA (src/shainet/cuda.cr).

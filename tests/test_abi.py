@@ -77,3 +77,14 @@ def test_product_does_not_touch_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cr")):
                 text = open(os.path.join(base, f), errors="replace").read()
                 assert "oracle" not in text.lower(), f"{f} mentions the oracle"
+
+
+def test_crystal_binding_declares_every_entry_point():
+    """The Crystal `lib` block (unexecuted here: no compiler) names every shainet_attn_*
+    function the header declares."""
+    import re
+    hdr = open(os.path.join(ROOT, "include", "shainet_attn.h")).read()
+    cr = open(os.path.join(ROOT, "shainet_b200", "crystal", "shainet_attn.cr")).read()
+    declared = set(re.findall(r"\b(shainet_attn_[a-z_0-9]+)\s*\(", hdr))
+    bound = set(re.findall(r"=\s*(shainet_attn_[a-z_0-9]+)", cr))
+    assert declared - bound == set(), sorted(declared - bound)
