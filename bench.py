@@ -380,6 +380,7 @@ def run_ours(args, wl, rank, world, local_rank):
     if split:
         gath_ptrs = [vp(comm_base + l * world * pay * 4) if peer else vp(gathered[l].data_ptr()) for l in range(layers)]
     fwd_x = ctx.L.shainet_attn_forward_dev_exchange
+    fwd_xm = ctx.L.shainet_attn_forward_dev_exchange_merge
     out_offs = [(l * world + rank) * pay for l in range(layers)]
     full_ptrs = [vp(full_d[l].data_ptr()) for l in range(layers)] if split else None
 
@@ -389,6 +390,14 @@ def run_ours(args, wl, rank, world, local_rank):
         ep = epoch[0]
         pos = ctx_len + i                   # the token's position; with a split sequence its k/v row goes to one rank of the group
         own = 1 if sp.owns_position(pos) else 0
+        if peer and split:
+            for l in range(layers):                 # deliver, wait for all ranks and merge the sequence parts: one call
+                a = args[l]
+                rc = fwd_xm(a[0], a[1], a[2], a[3], a[4], a[5], pos, own, a[7], a[8], l * world * pay, sp.seq_parts, ep,
+                            full_ptrs[l], a[9])
+                if rc:
+                    S.check(rc)
+            return
         if peer:
             for l in range(layers):
                 a = args[l]
@@ -563,7 +572,7 @@ def run_ours(args, wl, rank, world, local_rank):
             "e2e": {"value": K_e2e / e2e_s, "unit": "tokens/s", "steps": K_e2e,
                     "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz,
                     "d2h_bytes_per_step": layers * (qd if world == 1 else H * hd) * esz},
-            "gpu_launches": layers * K * (2 if peer else 1) + (layers * K if split else 0),
+            "gpu_launches": layers * K * (2 if peer else 1) + (layers * K if split and not peer else 0),
         }
         if prefill is not None:
             line["prefill"] = prefill

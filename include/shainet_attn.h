@@ -189,6 +189,16 @@ int shainet_attn_forward_dev_exchange(shainet_attn_ctx* ctx, shainet_attn_kv* kv
                                       const float* v_new, float* out, int position, int append, float scale, unsigned flags,
                                       long long out_offset_floats, long long lse_offset_floats, long long wait_offset_floats,
                                       long long wait_count_floats, unsigned epoch, void* stream);
+/* The same for a sequence that is split over the ranks of a head group (more ranks than
+ * kv heads): every rank delivers its head rows and log-sum-exp values into the slot
+ * [slot_offset, slot_offset + world * heads * (head_dim + 1)) of every rank, laid out
+ * [rank][heads * head_dim rows | heads log-sum-exp]; one kernel then waits for the words
+ * of all ranks and merges the seq_parts ranks of each head group straight into
+ * out_full_dev [world / seq_parts * heads * head_dim] (what merge_parts would produce). */
+int shainet_attn_forward_dev_exchange_merge(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                                            const float* v_new, float* out, int position, int append, float scale,
+                                            unsigned flags, long long slot_offset_floats, int seq_parts, unsigned epoch,
+                                            float* out_full_dev, void* stream);
 /* Asynchronous copy of a range of this rank's float area to host memory. */
 int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream);
 int shainet_attn_comm_data_ptr(shainet_attn_ctx* ctx, float** data_dev);

@@ -257,6 +257,16 @@ class LlamaAttention:
             self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, position, int(append), self.scale, flags,
             out_offset, lse_offset, wait_offset, wait_count, epoch, _stream_arg(stream)))
 
+    def forward_cached_dev_exchange_merge(self, q_ptr: int, k_ptr, v_ptr, out_ptr: int, position: int, append: bool,
+                                          slot_offset: int, seq_parts: int, epoch: int, out_full_ptr: int, stream=None,
+                                          flags: int = 0):
+        """forward_cached_dev_exchange for a sequence split over the ranks of a head group: the slot
+        [slot_offset, slot_offset + world * heads * (head_dim + 1)) holds [rank][rows | log-sum-exp]; one
+        kernel waits for all ranks and merges each group's parts into out_full_ptr."""
+        check(self.ctx.L.shainet_attn_forward_dev_exchange_merge(
+            self.ctx.h, self.cache.h, q_ptr, k_ptr, v_ptr, out_ptr, position, int(append), self.scale, flags,
+            slot_offset, seq_parts, epoch, out_full_ptr, _stream_arg(stream)))
+
     def close(self):
         self.cache.close()
 

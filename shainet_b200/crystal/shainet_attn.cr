@@ -70,6 +70,13 @@ module SHAInet
                                                                  out_offset_floats : Int64, lse_offset_floats : Int64,
                                                                  wait_offset_floats : Int64, wait_count_floats : Int64,
                                                                  epoch : UInt32, stream : Void*) : Int32
+    fun forward_dev_exchange_merge = shainet_attn_forward_dev_exchange_merge(ctx : Ctx, kv : Kv, q : Float32*,
+                                                                             k_new : Float32*, v_new : Float32*,
+                                                                             out_ptr : Float32*, position : Int32,
+                                                                             append : Int32, scale : Float32, flags : UInt32,
+                                                                             slot_offset_floats : Int64, seq_parts : Int32,
+                                                                             epoch : UInt32, out_full_dev : Float32*,
+                                                                             stream : Void*) : Int32
     fun comm_read = shainet_attn_comm_read(ctx : Ctx, offset_floats : Int64, host_dst : Float32*, floats : LibC::SizeT,
                                            stream : Void*) : Int32
     fun comm_data_ptr = shainet_attn_comm_data_ptr(ctx : Ctx, data_dev : Float32**) : Int32

@@ -951,6 +951,34 @@ int shainet_attn_forward_dev_exchange(shainet_attn_ctx* ctx, shainet_attn_kv* kv
     return shainet_attn_comm_wait(ctx, wait_offset_floats, wait_count_floats, epoch, stream);
 }
 
+int shainet_attn_forward_dev_exchange_merge(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new,
+                                            const float* v_new, float* out, int position, int append, float scale,
+                                            unsigned flags, long long slot_offset_floats, int seq_parts, unsigned epoch,
+                                            float* out_full_dev, void* stream) {
+    if (!ctx || !kv || !out_full_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (!ctx->comm_world) return fail(SHAINET_ATTN_E_STATE, "exchange buffers are not opened");
+    if (seq_parts <= 0 || seq_parts > MAX_PEERS || ctx->comm_world % seq_parts != 0)
+        return fail(SHAINET_ATTN_E_INVALID, "bad partition: %d ranks in groups of %d", ctx->comm_world, seq_parts);
+    const long long heads = kv->hs.num_heads, hd = kv->hs.head_dim;
+    const long long pay = heads * (hd + 1);            // a rank's block: head rows, then log-sum-exp values
+    if (slot_offset_floats < 0 || (size_t)(slot_offset_floats + ctx->comm_world * pay) > ctx->comm_data_floats)
+        return fail(SHAINET_ATTN_E_INVALID, "exchange slot outside the buffer");
+    const long long mine = slot_offset_floats + ctx->comm_rank * pay;
+    int rc = shainet_attn_comm_set_target(ctx, mine, mine + heads * hd, epoch);
+    if (rc) return rc;
+    rc = shainet_attn_forward_dev_at(ctx, kv, q, k_new, v_new, out, position, append, scale, flags, stream);
+    if (rc) {
+        ctx->gather_armed = false;
+        return rc;
+    }
+    DeviceGuard g(ctx->device);
+    cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+    const unsigned long long* words = reinterpret_cast<const unsigned long long*>(ctx->comm_base + ctx->comm_data_floats * sizeof(float));
+    CU(launch_gather_merge(words + slot_offset_floats, ctx->comm_world, seq_parts, (int)heads, (int)hd, epoch, out_full_dev,
+                           ctx->status_dev, s));
+    return SHAINET_ATTN_OK;
+}
+
 int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream) {
     if (!ctx || !host_dst) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
     if (!ctx->comm_base) return fail(SHAINET_ATTN_E_STATE, "no exchange buffer");

@@ -1215,6 +1215,50 @@ __global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_p
     }
 }
 
+// Wait and merge in one kernel, for a sequence that is split over the ranks of a head
+// group: block (h, g) polls the {value, epoch} words of head h of the seq_parts ranks of
+// group g (rows and log-sum-exp values, bounded) and writes the merged row; nothing is
+// unpacked in between.  Launched like gather_wait_kernel.
+__global__ void __launch_bounds__(128) gather_merge_kernel(const unsigned long long* words, int seq_parts,
+                                                           int heads_per_rank, int head_dim, unsigned epoch,
+                                                           float* __restrict__ out_full, AttnStatus* status) {
+    grid_launch_dependents();
+    const int g = blockIdx.y, h = blockIdx.x;
+    const size_t rank_stride = (size_t)heads_per_rank * (head_dim + 1);
+    const unsigned long long t0 = globaltimer_ns();
+    bool ok = true;
+    auto take = [&](const unsigned long long* p) -> float {
+        while (true) {
+            unsigned long long w;
+            asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+            if ((unsigned)(w >> 32) == epoch) return __uint_as_float((unsigned)w);
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 22;
+                ok = false;
+                return 0.0f;
+            }
+        }
+    };
+    constexpr int MAXP = 16;   // ranks per head group (MAX_PEERS)
+    float lse[MAXP];
+    float mx = -INFINITY;
+    for (int p = 0; p < seq_parts && p < MAXP; ++p) {
+        lse[p] = take(words + (size_t)(g * seq_parts + p) * rank_stride + (size_t)heads_per_rank * head_dim + h);
+        mx = fmaxf(mx, lse[p]);
+    }
+    for (int d = threadIdx.x; d < head_dim && ok; d += blockDim.x) {
+        float acc = 0.0f, wsum = 0.0f;
+        for (int p = 0; p < seq_parts && p < MAXP; ++p) {
+            const float o = take(words + (size_t)(g * seq_parts + p) * rank_stride + (size_t)h * head_dim + d);
+            const float w = (lse[p] == -INFINITY) ? 0.0f : expf(lse[p] - mx);
+            wsum += w;
+            acc = fmaf(w, o, acc);
+        }
+        if (ok) out_full[((size_t)g * heads_per_rank + h) * head_dim + d] = acc / wsum;
+    }
+    grid_dependency_wait();
+}
+
 }  // namespace
 
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
@@ -1233,6 +1277,22 @@ cudaError_t launch_gather_wait(const unsigned long long* words, float* data, lon
     cfg.attrs = at;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, gather_wait_kernel, words, data, count, epoch, status);
+}
+
+cudaError_t launch_gather_merge(const unsigned long long* words, int world, int seq_parts, int heads_per_rank, int head_dim,
+                                unsigned epoch, float* out_full, AttnStatus* status, cudaStream_t s) {
+    if (seq_parts <= 0 || seq_parts > MAX_PEERS || world % seq_parts != 0) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(heads_per_rank, world / seq_parts);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gather_merge_kernel, words, seq_parts, heads_per_rank, head_dim, epoch, out_full, status);
 }
 
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,

@@ -64,7 +64,7 @@ struct AttnArgs {
 
 // Where the fused decode kernel also delivers its result when kv-head groups
 // are spread over GPUs: every rank's exchange buffer (plain peer stores over
-// NVLink, no multicast), at this rank's slot, followed by a release flag.
+// NVLink, no multicast), at this rank's slot.
 constexpr int MAX_PEERS = 16;
 // Delivery of the merged head rows into every rank's exchange buffer.  Each float
 // travels as one 8-byte word {value, epoch}: an aligned 8-byte store is indivisible,
@@ -147,6 +147,9 @@ cudaError_t launch_attn_prefill_tc(const AttnArgs& a, cudaStream_t s);
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
                                float* out_full, cudaStream_t s);
 
+// Bounded wait for the words of all ranks' (row, log-sum-exp) pairs of one exchange slot, merged per head group.
+cudaError_t launch_gather_merge(const unsigned long long* words, int world, int seq_parts, int heads_per_rank, int head_dim,
+                                unsigned epoch, float* out_full, AttnStatus* status, cudaStream_t s);
 // Bounded wait until `count` exchange words carry `epoch`; unpacks them into `data`.
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
                                AttnStatus* status, cudaStream_t s);

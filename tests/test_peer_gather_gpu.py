@@ -146,6 +146,13 @@ for step in range(6):
     mine_off = (slot * world + rank) * pay
     lse_off = mine_off + Hl * hd if split else -1
     own = sp.owns_position(pos)
+    if split and step % 2 == 0:   # deliver + wait + merge of the sequence parts in one call
+        g.forward_cached_dev_exchange_merge(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), pos, own,
+                                            slot * world * pay, sp.seq_parts, step + 1, merged.data_ptr(), stream=stream)
+        torch.cuda.synchronize(); ctx.sync()
+        worst = max(worst, rel_err(merged.cpu().numpy(), ref))
+        dist.barrier()
+        continue
     if step % 2 == 0 and not split:
         ctx.comm_set_target(mine_off, lse_off, step + 1)
         g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), 1, stream=stream)
