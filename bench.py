@@ -40,9 +40,9 @@ WORKLOADS = {
                  H=32, KV=8, hd=64, theta=5e5, qk_norm=False, layers=16, ctx=4096),
 }
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_fused_kernel launch on the cfg5 shape at L = 32770
-# (ncu capture summarised in profiles/attn_decode_fused_kernel__cfg5_ctx32k.md): 138.3 MB for 134.26 MB algorithmic.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.3 / 134.26   # profiles/attn_decode_fused_kernel__cfg5_ctx32k.md, section 2
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_decode_fused_kernel launch on the cfg5 shape at
+# L = 32770, from an ncu capture of a 4-layer case of the same shape: 139.3 MB for 134.26 MB algorithmic.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.3 / 134.26
 
 
 def decode_bytes(wl, L, kv_heads=None):
@@ -107,6 +107,16 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def host_threads():
+    """Host cores this process may run on.  Asked of the scheduler, not of OpenMP: a launcher
+    may have set OMP_NUM_THREADS=1 for its ranks, which would turn the CPU baseline into a
+    one-core figure at some rank counts and an all-core figure at others."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_port_rate(wl, threads, layers_sampled, steps, seed=5001):
     """Decode tokens/s of the CPU oracle: `steps` steps of `layers_sampled` layers at
     the workload's context, scaled to the full layer count."""
@@ -136,17 +146,18 @@ def cpu_port_rate(wl, threads, layers_sampled, steps, seed=5001):
 def run_reference(args, wl, rank, world):
     if rank != 0:
         return
-    from oracle import oracle as O
-    threads = O.max_threads()
-    layers_sampled = 1
-    cpu_port_rate(wl, threads, 1, max(1, min(args.warmup, 2)))            # warm-up (page in, thread pool)
+    threads = host_threads()
+    warm = cpu_port_rate(wl, threads, 1, max(1, min(args.warmup, 2)))     # warm-up (page in, thread pool)
+    # as many of the layers per step as keep the whole run within about two minutes
+    layers_sampled = int(max(1, min(wl["layers"], 120.0 / (max(args.steps, 1) * max(min(warm), 1e-4)))))
     t0 = time.perf_counter()
     per_step = cpu_port_rate(wl, threads, layers_sampled, args.steps)
     wall = time.perf_counter() - t0
     sec_per_token = float(np.sum(per_step)) / args.steps * wl["layers"] / layers_sampled
     value = 1.0 / sec_per_token
-    sample = (f"{args.steps} decode steps x {layers_sampled} of {wl['layers']} layers at ctx {wl['ctx']}, "
-              f"scaled to all layers; OpenMP over query heads")
+    sample = (f"{args.steps} decode steps x {layers_sampled} of {wl['layers']} layers at ctx {wl['ctx']}"
+              + ("" if layers_sampled == wl["layers"] else ", scaled to all layers")
+              + "; OpenMP over (query head, row block) work items")
     line = {
         "impl": "reference", "metric": "decode_attn_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_token * 1e3,
@@ -286,6 +297,135 @@ def batched_block(S, ctx, dev, stream_obj):
             "tokens_per_s_36_layers": B / (ms_layer * w["layers_total"] / 1e3), "layers_timed": len(layers), "steps": steps,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel (batched)", "achieved": gbs, "peak": peak,
                          "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "bytes_per_launch": bytes_layer}}
+
+
+def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
+    """The metric's ctx-4k point: BASELINE config 2's attention (LLaMA-3.2-1B: 16 layers, 32 query /
+    8 kv heads, head_dim 64, batch 1, fp32 cache at ctx 4096), one fused launch per layer-step, timed
+    with CUDA events on the launching stream.  The 16 layers' K/V (268 MB) are cycled, which is more
+    than L2 holds, so every launch streams from HBM."""
+    import torch
+    wl = WORKLOADS["cfg2"]
+    H, KV, hd, layers, L = wl["H"], wl["KV"], wl["hd"], wl["layers"], wl["ctx"]
+    blocks = []
+    for l in range(layers):
+        b = S.LlamaAttention(ctx, H, KV, hd, wl["theta"], 1e-5, initial_capacity=L + steps + warm + 8)
+        b.cache.fill_normal(L, 2101 + l)
+        blocks.append(b)
+    g = torch.Generator(device=dev)
+    g.manual_seed(2102)
+    q = torch.randn(layers, H * hd, device=dev, generator=g)
+    k = torch.randn(layers, KV * hd, device=dev, generator=g)
+    v = torch.randn(layers, KV * hd, device=dev, generator=g)
+    out = torch.empty_like(q)
+    fwd = ctx.L.shainet_attn_forward_dev
+    vp = C.c_void_p
+    call = [(ctx.h, b.cache.h, vp(q[l].data_ptr()), vp(k[l].data_ptr()), vp(v[l].data_ptr()), vp(out[l].data_ptr()), 1,
+             C.c_float(b.scale), 0, vp(stream_obj.cuda_stream)) for l, b in enumerate(blocks)]
+
+    def run(n):
+        for _ in range(n):
+            for a in call:
+                rc = fwd(*a)
+                if rc:
+                    S.check(rc)
+    run(warm)
+    torch.cuda.synchronize()
+    for b in blocks:
+        b.cache.truncate(L)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.sync()
+    ms = e0.elapsed_time(e1)
+    for b in blocks:
+        b.close()
+    peak, kind = measured_peak()
+    bytes_launch = decode_bytes(wl, L + (steps + 1) / 2.0)
+    us = ms * 1e3 / (steps * layers)
+    gbs = bytes_launch / (us * 1e-6) / 1e9
+    return {"workload": wl["name"], "tokens_per_s": steps / (ms / 1e3), "ms_per_step": ms / steps, "steps": steps,
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel", "achieved": gbs, "peak": peak,
+                         "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "bytes_per_launch": bytes_launch,
+                         "avg_launch_us": us, "launches_timed": steps * layers}}
+
+
+PARITY_TOL = 1e-5
+
+
+def parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, comm_slot_floats, epoch):
+    """One checked layer-step on the very path the timed region used (same entry points, same sharding,
+    same exchange): every rank imports its part of one seeded cache of 2053 positions, attends for one
+    new token, and rank 0 compares the gathered (and, for a split sequence, merged) head outputs of all
+    ranks with the CPU oracle's unsharded result.  Returns the dictionary for the JSON line."""
+    import torch
+    H, KV, hd = wl["H"], wl["KV"], wl["hd"]
+    Hl, KVl = sp.head_count, sp.kv_count
+    split = sp.seq_parts > 1
+    Lc = 2053
+    rng = np.random.default_rng(777)          # the same stream on every rank: identical full inputs
+    kw = {}
+    if wl["qk_norm"]:
+        kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
+                  k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
+    kc = rng.standard_normal((KV, Lc, hd), dtype=np.float32)
+    vc = rng.standard_normal((KV, Lc, hd), dtype=np.float32)
+    q = rng.standard_normal((1, H * hd)).astype(np.float32)
+    k = rng.standard_normal((1, KV * hd)).astype(np.float32)
+    v = rng.standard_normal((1, KV * hd)).astype(np.float32)
+    g = S.LlamaAttention(ctx, Hl, KVl, hd, wl["theta"], 1e-6, initial_capacity=Lc + 8, **kw)
+    kvs = slice(sp.kv_begin, sp.kv_begin + KVl)
+    g.cache.import_(kc[kvs, sp.seq_part::sp.seq_parts], vc[kvs, sp.seq_part::sp.seq_parts])
+    ql = q.reshape(1, H, hd)[:, sp.head_begin:sp.head_begin + Hl].reshape(1, -1).copy()
+    kl = k.reshape(1, KV, hd)[:, kvs].reshape(1, -1).copy()
+    vl = v.reshape(1, KV, hd)[:, kvs].reshape(1, -1).copy()
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
+    pay = Hl * hd + (Hl if split else 0)
+    out = torch.zeros(pay, device=dev)
+    full = torch.zeros(H * hd, device=dev)
+    pos, own = Lc, sp.owns_position(Lc)
+    if world > 1:
+        dist.barrier()
+    if world == 1:
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), full.data_ptr(), 1, stream)
+    elif peer and split:
+        g.forward_cached_dev_exchange_merge(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), pos, own, 0,
+                                            sp.seq_parts, epoch, full.data_ptr(), stream)
+    elif peer:
+        g.forward_cached_dev_exchange(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), pos, own,
+                                      rank * pay, -1, 0, world * pay, epoch, stream)
+        host = np.empty(world * pay, np.float32)
+        ctx.comm_read(0, host, stream)
+    else:
+        gathered = torch.empty(world, pay, device=dev)
+        if split:
+            ctx.set_lse_out(out[Hl * hd:].data_ptr())
+        g.forward_cached_dev_at(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(), pos, own, stream)
+        ctx.set_lse_out(None)
+        dist.all_gather_into_tensor(gathered.view(-1), out)
+        if split:
+            ctx.merge_parts(gathered.data_ptr(), world, sp.seq_parts, Hl, hd, full.data_ptr(), stream)
+        else:
+            full = gathered.view(-1)
+    torch.cuda.synchronize()
+    ctx.sync()
+    got = host if (peer and not split and world > 1) else full.cpu().numpy()
+    g.close()
+    res = None
+    if rank == 0:
+        from oracle import oracle as O
+        o = O.OracleAttention(H, KV, hd, wl["theta"], 1e-6, **kw)
+        o.import_cache(kc, vc)
+        ref = o.attend_cached(q, k, v, threads=host_threads())[0]
+        err = float(np.abs(got.astype(np.float64) - ref).max() / np.abs(ref).max())
+        res = {"max_rel_err": err, "tol": PARITY_TOL, "ok": bool(err <= PARITY_TOL), "ctx": Lc, "ranks": world,
+               "what": "one layer-step of this run's path (sharding and exchange included) against the CPU oracle's "
+                       "unsharded attention on the same seeded cache"}
+    if world > 1:
+        dist.barrier()
+    return res
 
 
 def run_ours(args, wl, rank, world, local_rank):
@@ -534,10 +674,13 @@ def run_ours(args, wl, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
-    prefill = batched = None
+    prefill = batched = short_ctx = None
     if world == 1 and not args.no_prefill:
         prefill = prefill_block(S, ctx, dev, tstream)
         batched = batched_block(S, ctx, dev, tstream)
+    if world == 1 and not args.no_prefill and args.workload != "cfg2":
+        short_ctx = short_context_block(S, ctx, dev, tstream)
+    parity = parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, layers * world * pay, epoch[0] + 1)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -571,23 +714,32 @@ def run_ours(args, wl, rank, world, local_rank):
                                   "note": "same region with SHAINET_ATTN_F_INPUTS_READY (q/k/v not produced by the previous launch)"},
             "e2e": {"value": K_e2e / e2e_s, "unit": "tokens/s", "steps": K_e2e,
                     "h2d_bytes_per_step": layers * (qd + 2 * kd) * esz,
-                    "d2h_bytes_per_step": layers * (qd if world == 1 else H * hd) * esz},
+                    "d2h_bytes_per_step": layers * (qd if world == 1 else H * hd) * esz,
+                    "method": ("one blocking shainet_attn_forward_host call per layer: pinned host q/k/v in, host "
+                               "output row back, stream synchronised every layer (the reference block's call pattern)"
+                               if world == 1 else
+                               "per step: three bulk copies of all layers' q/k/v from pinned host memory, the layers "
+                               "queued asynchronously (forward_dev_exchange), one copy of all layers' gathered head "
+                               "outputs back, one synchronisation; not comparable with the per-layer blocking method "
+                               "used at one GPU")},
+            "parity_check": parity,
             "gpu_launches": layers * K * (2 if peer else 1) + (layers * K if split and not peer else 0),
         }
         if prefill is not None:
             line["prefill"] = prefill
         if batched is not None:
             line["batched_decode"] = batched
+        if short_ctx is not None:
+            line["decode_ctx4k"] = short_ctx
         if world == 1 and not args.no_cpu_baseline:
-            from oracle import oracle as O
-            threads = O.max_threads()
+            threads = host_threads()
             cpu_port_rate(wl, threads, 1, 1)
             per_step = cpu_port_rate(wl, threads, 2, 4)
             spt = float(np.mean(per_step)) * layers / 2
             one = cpu_port_rate(wl, 1, 1, 1)
             line["cpu_baseline"] = {"value": 1.0 / spt, "unit": "tokens/s", "cores": threads, "kind": "port",
                                     "sample": f"4 decode steps x 2 of {layers} layers at ctx {ctx_len}, scaled to all "
-                                              "layers; OpenMP over query heads",
+                                              "layers; OpenMP over (query head, row block) work items",
                                     "single_thread_value": 1.0 / (float(one[0]) * layers)}
         print(json.dumps(line), flush=True)
     for b in blocks:
@@ -596,6 +748,8 @@ def run_ours(args, wl, rank, world, local_rank):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if rank == 0 and not parity["ok"]:
+        sys.exit(f"parity check failed: max relative error {parity['max_rel_err']:.3e} > {PARITY_TOL}")
 
 
 def main():

@@ -199,6 +199,17 @@ int shainet_attn_forward_dev_exchange_merge(shainet_attn_ctx* ctx, shainet_attn_
                                             const float* v_new, float* out, int position, int append, float scale,
                                             unsigned flags, long long slot_offset_floats, int seq_parts, unsigned epoch,
                                             float* out_full_dev, void* stream);
+/* How long comm_wait and forward_dev_exchange[_merge] let their kernel poll for the
+ * other ranks' words before giving up (default 1000 ms).  The poll starts when the
+ * waiting kernel starts, so the limit has to cover how late the slowest rank's host
+ * thread may be with the matching call (a first-call set-up, paging, a garbage
+ * collection pause in the host language) plus its kernel's run time.  A rank that is
+ * later than this makes every other rank's next sync return
+ * SHAINET_ATTN_E_DEVICE_WAIT; their contexts stay usable, but the token's exchanged
+ * rows are incomplete and the step has to be redone (roll the caches back with
+ * kv_truncate and call again with a fresh epoch).  Waits between the CTAs of one
+ * kernel on one GPU are not affected (fixed, ~1 s). */
+int shainet_attn_comm_set_wait_limit_ms(shainet_attn_ctx* ctx, int milliseconds);
 /* Asynchronous copy of a range of this rank's float area to host memory. */
 int shainet_attn_comm_read(shainet_attn_ctx* ctx, long long offset_floats, float* host_dst, size_t floats, void* stream);
 int shainet_attn_comm_data_ptr(shainet_attn_ctx* ctx, float** data_dev);
@@ -231,9 +242,8 @@ void attention_kv_f32(const float* q, const float* kc, const float* vc, float* o
  * because they synchronise the whole device.  It computes what
  * attention_kv_f32 computes for new_tokens == 1 - q [num_heads*head_dim] already
  * rotated, the new K/V row already appended at start_pos, visible rows
- * 0..start_pos - on the caller's stream, and returns a status like the other
- * shainet_attn_* calls.  Its split partials live in a fixed 4 MiB array inside
- * the library image (held by every GPU that loads the library, until exit)
+ * 0..start_pos - on the caller's stream, and returns a status code.  Its split
+ * partials live in a fixed 4 MiB array inside the library image (held by every GPU that loads the library, until exit)
  * instead of a buffer grown on demand; it calls no cudaMalloc, cudaFree or
  * allocating library routine.  Limits: head_dim 64 or 128; 1/2/4/8/16 query
  * heads per kv head; num_heads * splits * (head_dim + 2) <= 1,048,576 floats
@@ -241,7 +251,11 @@ void attention_kv_f32(const float* q, const float* kc, const float* vc, float* o
  * heads) - anything larger is refused with SHAINET_ATTN_E_UNSUPPORTED.  All calls
  * share the array: calls that overlap on the GPU race and must be ordered by
  * the caller.  The first call made with a given device current looks up the
- * array's device address; make that call before any stream capture starts. */
+ * array's device address (thread-safe); make that call before any stream
+ * capture starts.  The returned status covers argument checks, the set-up and
+ * the launch.  Without a context there is no device status word, so a
+ * kernel-side bounded wait that runs out (SHAINET_ATTN_E_DEVICE_WAIT elsewhere)
+ * is NOT reported by this entry; the same holds for attention_kv_f32 above. */
 int shainet_attn_decode_noalloc(const float* q_dev, const float* k_cache_dev, const float* v_cache_dev,
                                 float* out_dev, int start_pos, int num_heads, int heads_per_kv, int head_dim,
                                 int capacity, float scale, void* stream);

@@ -44,7 +44,9 @@ def build_oracle(force: bool = False) -> str:
 def build_reference_kernels(reference_root: str | None = None, force: bool = False) -> str | None:
     """Compile the reference's CUDA file; returns the .so path, or None when the
     reference tree is not mounted (the prebuilt .so, if any, is then used)."""
-    reference_root = reference_root or os.environ.get("SHAINET_REFERENCE_ROOT", "/root/reference")
+    # the argument, else $SHAINET_REFERENCE_ROOT, else a checkout named "reference" beside this repository
+    reference_root = (reference_root or os.environ.get("SHAINET_REFERENCE_ROOT")
+                      or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
     src = os.path.join(reference_root, REF_CU_REL)
     if not os.path.exists(src):
         return REF_SO if os.path.exists(REF_SO) else None

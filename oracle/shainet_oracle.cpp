@@ -13,7 +13,7 @@
 // (2) the reference's cached-vs-uncached consistency relation on its
 // tiny-llama fixture, (3) its nil-bias == zero-bias relation, and (4) a
 // GPU-side comparison with the reference's own CUDA attention kernel compiled
-// unmodified from its source (see oracle/build_oracle.py, tests/test_reference_kernel.py).
+// unmodified from its source (see oracle/build_oracle.py, tests/test_reference_kernel_gpu.py).
 // Behaviours the reference's specs never exercise (QK-norm, head_dim 64/128,
 // theta 5e5/1e6, LLaMA-3 scaled frequencies) are "parity unpinned": the source
 // lines cited below are their only specification.
@@ -107,7 +107,7 @@ inline void rope_row(const Block& b, const float* x, int pos, float* out) {
 // mode 0: the reference's fp32 sequential arithmetic.
 // mode 1: the same visible set with every sum carried in f64 ("truth" for
 //         judging summation error; not a reference behaviour).
-void attend_head(const Block& b, int h, const float* q_full, float* output, int new_tokens,
+void attend_head(const Block& b, int h, const float* q_full, float* output, int row_begin, int row_end,
                  int start_pos, int total_len, float scale, int mode) {
     const int hd = b.head_dim;
     const int heads_per_kv = b.num_heads / b.num_kv_heads;
@@ -120,7 +120,7 @@ void attend_head(const Block& b, int h, const float* q_full, float* output, int 
     std::vector<double> sd, od;
     if (mode == 1) { sd.assign(total_len, 0.0); od.assign(hd, 0.0); }
 
-    for (int i = 0; i < new_tokens; ++i) {
+    for (int i = row_begin; i < row_end; ++i) {
         int pos = start_pos + i;
         const float* qrow = q_full + (size_t)i * dm + q_col;
         rope_row(b, qrow, pos, q_rot.data());
@@ -171,6 +171,26 @@ void attend_head(const Block& b, int h, const float* q_full, float* output, int 
             float* orow = output + (size_t)i * dm + q_col;
             for (int d = 0; d < hd; ++d) orow[d] = (float)od[d];
         }
+    }
+}
+
+// The reference runs the (head, new token) pairs one after another on one thread
+// (llama_block.cr:322-399).  Every pair is independent of every other, so with
+// threads > 1 they are handed out as (head, block of 32 rows) work items under
+// OpenMP; the arithmetic of each pair is unchanged, so results are identical.
+void attend_all_heads(const Block& b, const float* q, float* out, int new_tokens, int start_pos, int total_len,
+                      float scale, int threads, int mode) {
+    const int ROWS = 32;
+    const int chunks = (new_tokens + ROWS - 1) / ROWS;
+    const int items = b.num_heads * chunks;
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : 1;
+#pragma omp parallel for num_threads(nt) schedule(dynamic, 1)
+#endif
+    for (int it = items - 1; it >= 0; --it) {   // the costliest rows (largest visible length) first
+        const int h = it % b.num_heads, c = it / b.num_heads;
+        const int r0 = c * ROWS, r1 = std::min(new_tokens, r0 + ROWS);
+        attend_head(b, h, q, out, r0, r1, start_pos, total_len, scale, mode);
     }
 }
 
@@ -296,12 +316,7 @@ void oracle_block_attend_cached(void* p, const float* q_in, const float* k_in, c
     const int total_len = b->cache_len + new_tokens;
     b->cache_len = total_len;
 
-#ifdef _OPENMP
-    int nt = threads > 0 ? threads : 1;
-#pragma omp parallel for num_threads(nt) schedule(dynamic, 1)
-#endif
-    for (int h = 0; h < b->num_heads; ++h)
-        attend_head(*b, h, q.data(), out, new_tokens, start_pos, total_len, scale, mode);
+    attend_all_heads(*b, q.data(), out, new_tokens, start_pos, total_len, scale, threads, mode);
 }
 
 // Attention only, over the caches as they stand, with q rows that are already
@@ -312,12 +327,7 @@ void oracle_block_attend_only(void* p, const float* q, int new_tokens, int start
     Block* b = (Block*)p;
     const float scale = (float)(1.0 / std::sqrt((double)b->head_dim));
     const int total_len = start_pos + new_tokens;
-#ifdef _OPENMP
-    int nt = threads > 0 ? threads : 1;
-#pragma omp parallel for num_threads(nt) schedule(dynamic, 1)
-#endif
-    for (int h = 0; h < b->num_heads; ++h)
-        attend_head(*b, h, q, out, new_tokens, start_pos, total_len, scale, mode);
+    attend_all_heads(*b, q, out, new_tokens, start_pos, total_len, scale, threads, mode);
 }
 
 // attention_full_cpu between the projections and o_proj

@@ -57,6 +57,7 @@ SIGNATURES = {
                                                     C.c_longlong, C.c_longlong, C.c_longlong, C.c_longlong, C.c_uint, _P]),
     "shainet_attn_forward_dev_exchange_merge": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_float, C.c_uint,
                                                           C.c_longlong, C.c_int, C.c_uint, _P, _P]),
+    "shainet_attn_comm_set_wait_limit_ms": (C.c_int, [_P, C.c_int]),
     "shainet_attn_comm_read": (C.c_int, [_P, C.c_longlong, C.POINTER(C.c_float), C.c_size_t, _P]),
     "shainet_attn_comm_data_ptr": (C.c_int, [_P, C.POINTER(_P)]),
     "shainet_attn_forward_batched_dev": (C.c_int, [_P, C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_float,

@@ -98,6 +98,10 @@ class AttnContext:
         `epoch`; it also unpacks them into the float area."""
         check(self.L.shainet_attn_comm_wait(self.h, offset, count, epoch, _stream_arg(stream)))
 
+    def comm_set_wait_limit_ms(self, ms: int):
+        """Limit of the device-side polls for other ranks' exchange words (default 1000 ms)."""
+        check(self.L.shainet_attn_comm_set_wait_limit_ms(self.h, ms))
+
     def comm_data_ptr(self) -> int:
         p = C.c_void_p()
         check(self.L.shainet_attn_comm_data_ptr(self.h, C.byref(p)))

@@ -77,6 +77,7 @@ module SHAInet
                                                                              slot_offset_floats : Int64, seq_parts : Int32,
                                                                              epoch : UInt32, out_full_dev : Float32*,
                                                                              stream : Void*) : Int32
+    fun comm_set_wait_limit_ms = shainet_attn_comm_set_wait_limit_ms(ctx : Ctx, milliseconds : Int32) : Int32
     fun comm_read = shainet_attn_comm_read(ctx : Ctx, offset_floats : Int64, host_dst : Float32*, floats : LibC::SizeT,
                                            stream : Void*) : Int32
     fun comm_data_ptr = shainet_attn_comm_data_ptr(ctx : Ctx, data_dev : Float32**) : Int32

@@ -76,6 +76,9 @@ struct shainet_attn_ctx {
     size_t tickets_cap = 0;
     unsigned epoch = 0;                 // tag of the newest word-merged decode launch
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
+    bool rows_rewound = false;          // a cache was truncated or reset since: the next launch may rewrite rows the
+                                        // previous one still reads, so it must not run ahead of it (F_INPUTS_READY is ignored once)
+    unsigned long long peer_wait_ns = WAIT_LIMIT_NS;   // limit of the waits for other ranks' exchange words
     float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
     // exchange buffer shared with the other ranks of the box (IPC): comm_data_floats
     // floats, then as many 8-byte {value, epoch} words
@@ -124,13 +127,14 @@ struct DeviceGuard {
 
 int grow(DevBuf& b, size_t floats, cudaStream_t s) {
     if (b.cap >= floats && b.p) return SHAINET_ATTN_OK;
+    const size_t old_cap = b.cap;
     if (b.p) {
         CU(cudaStreamSynchronize(s));
         CU(cudaFree(b.p));
         b.p = nullptr;
         b.cap = 0;
     }
-    size_t want = std::max(floats, b.cap * 2);
+    size_t want = std::max(floats, old_cap * 2);
     want = (want + 63) & ~(size_t)63;
     CU(cudaMalloc(&b.p, want * sizeof(float)));
     b.cap = want;
@@ -179,17 +183,26 @@ int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
     }
     // Rows past the appended length are read (and masked) by the tensor-core
     // prefill kernel; they must be finite, so fresh buffers start at zero.
-    CU(cudaMemsetAsync(nk, 0, bytes, s));
-    CU(cudaMemsetAsync(nv, 0, bytes, s));
-    if (kv->k && kv->len > 0) {
+    e = cudaMemsetAsync(nk, 0, bytes, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(nv, 0, bytes, s);
+    if (e == cudaSuccess && kv->k && kv->len > 0) {
         const size_t row_bytes = (size_t)kv->len * kv->hs.head_dim * sizeof(float);
         const size_t src_pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
         const size_t dst_pitch = (size_t)new_cap * kv->hs.head_dim * sizeof(float);
-        CU(cudaMemcpy2DAsync(nk, dst_pitch, kv->k, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s));
-        CU(cudaMemcpy2DAsync(nv, dst_pitch, kv->v, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s));
+        e = cudaMemcpy2DAsync(nk, dst_pitch, kv->k, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(nv, dst_pitch, kv->v, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s);
+    }
+    // The old buffers are freed below, and a first allocation may be followed by work on
+    // another stream (a cache created on the context's stream, then used on the caller's):
+    // either way the zero fill and the move have to be complete when this returns.
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        cudaFree(nk);
+        cudaFree(nv);
+        return fail_cuda(e, "cache growth (zero fill / move of the live rows)");
     }
     if (kv->k) {
-        CU(cudaStreamSynchronize(s));
         CU(cudaFree(kv->k));
         CU(cudaFree(kv->v));
     }
@@ -435,7 +448,8 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     // A fused kernel may start while the previous fused kernel still runs; that
     // one can be appending the newest row of this very cache.
     f.unsafe_tail = ctx->last_fused ? 1 : 0;
-    f.inputs_ready = (flags & SHAINET_ATTN_F_INPUTS_READY) ? 1 : 0;
+    f.inputs_ready = ((flags & SHAINET_ATTN_F_INPUTS_READY) && !ctx->rows_rewound) ? 1 : 0;
+    ctx->rows_rewound = false;
     f.pos_delta = pos_delta;
     f.no_append = no_append;
     f.lse_out = ctx->lse_out;
@@ -651,12 +665,14 @@ int shainet_attn_kv_destroy(shainet_attn_kv* kv) {
 int shainet_attn_kv_reset(shainet_attn_kv* kv) {
     if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
     kv->len = 0;  // buffers stay; stale rows are rewritten before they become visible
+    kv->ctx->rows_rewound = true;
     return SHAINET_ATTN_OK;
 }
 
 int shainet_attn_kv_truncate(shainet_attn_kv* kv, int len) {
     if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
     if (len < 0 || len > kv->len) return fail(SHAINET_ATTN_E_STATE, "truncate to %d of a cache of %d", len, kv->len);
+    if (len < kv->len) kv->ctx->rows_rewound = true;
     kv->len = len;
     return SHAINET_ATTN_OK;
 }
@@ -933,7 +949,7 @@ int shainet_attn_comm_wait(shainet_attn_ctx* ctx, long long offset_floats, long 
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
     float* data = reinterpret_cast<float*>(ctx->comm_base);
     const unsigned long long* words = reinterpret_cast<const unsigned long long*>(ctx->comm_base + ctx->comm_data_floats * sizeof(float));
-    CU(launch_gather_wait(words + offset_floats, data + offset_floats, count_floats, epoch, ctx->status_dev, s));
+    CU(launch_gather_wait(words + offset_floats, data + offset_floats, count_floats, epoch, ctx->peer_wait_ns, ctx->status_dev, s));
     return SHAINET_ATTN_OK;
 }
 
@@ -974,8 +990,15 @@ int shainet_attn_forward_dev_exchange_merge(shainet_attn_ctx* ctx, shainet_attn_
     DeviceGuard g(ctx->device);
     cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
     const unsigned long long* words = reinterpret_cast<const unsigned long long*>(ctx->comm_base + ctx->comm_data_floats * sizeof(float));
-    CU(launch_gather_merge(words + slot_offset_floats, ctx->comm_world, seq_parts, (int)heads, (int)hd, epoch, out_full_dev,
-                           ctx->status_dev, s));
+    CU(launch_gather_merge(words + slot_offset_floats, ctx->comm_world, seq_parts, (int)heads, (int)hd, epoch,
+                           ctx->peer_wait_ns, out_full_dev, ctx->status_dev, s));
+    return SHAINET_ATTN_OK;
+}
+
+int shainet_attn_comm_set_wait_limit_ms(shainet_attn_ctx* ctx, int milliseconds) {
+    if (!ctx) return fail(SHAINET_ATTN_E_INVALID, "null context");
+    if (milliseconds < 1 || milliseconds > 600000) return fail(SHAINET_ATTN_E_INVALID, "wait limit %d ms outside [1, 600000]", milliseconds);
+    ctx->peer_wait_ns = (unsigned long long)milliseconds * 1000000ull;
     return SHAINET_ATTN_OK;
 }
 

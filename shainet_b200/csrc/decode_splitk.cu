@@ -35,21 +35,14 @@
 // word and the kernel unwinds.
 #include <math.h>
 #include <stdio.h>
+#include <atomic>
+#include <mutex>
 #include <type_traits>
 #include "kernels.h"
 
 namespace shainet {
 
 namespace {
-
-#ifdef SK_TIMELINE
-// debug builds only: per-CTA timestamps of the fused kernel, [launch % 64][cta][16]
-__device__ unsigned long long g_timeline[64 * 320 * 16];
-__device__ unsigned g_timeline_launch;
-#define TL_MARK(k, tid) do { if (threadIdx.x == (tid)) g_timeline[((a.epoch & 63) * 320 + blockIdx.y * gridDim.x + blockIdx.x) * 16 + (k)] = globaltimer_ns(); } while (0)
-#else
-#define TL_MARK(k, tid) do { } while (0)
-#endif
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -102,11 +95,7 @@ struct SKDefault {
 };
 
 template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
-#ifdef SK_NOMATH  // measurement build: the consumers release every tile untouched (results are wrong)
-          int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = false>
-#else
-          int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM, bool MATH_ = true>
-#endif
+          int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM>
 struct SK {
     static constexpr int NW = NW_;                     // consumer warps
     static constexpr int CPL = HD / 64;                // 16-byte chunks per lane per K row
@@ -120,7 +109,6 @@ struct SK {
     static constexpr int WARP_SCRATCH = 2 * 2 * (32 + 16); // two buffers of (p,p)[BR*G = 32] + (alpha,alpha)[G <= 16], as floats
     static constexpr int THREADS = (NW + 1) * 32;
     static constexpr int CTAS_PER_SM = CTAS_;
-    static constexpr bool MATH = MATH_;
     // fused kernel extras: rotated q of the group (rows padded by 4 floats so that
     // lanes walking different rows hit different banks), a one-batch tile for the
     // new k row, the new v row, per-row inverse RMS values
@@ -477,11 +465,11 @@ __device__ __forceinline__ void consume_slice(Smem<C>& sm, int ntiles, int rows,
         const float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
         const float* vs = ks + C::TILE_FLOATS;
         const int nrows = min(C::TW, rows - i * C::TW);
-        if (C::MATH && nrows == C::TW) {
+        if (nrows == C::TW) {
             consume_full_tile<HD, G, C>(ks, vs, q, st, ps, lane, scale);
         } else {
             __syncwarp();
-            consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::MATH ? C::NB : 0);
+            consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::NB);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty_bar[s]);
@@ -571,10 +559,7 @@ __global__ void __launch_bounds__(HD) attn_combine_kernel(AttnArgs a) {
 // (row r, kv head kv_h), entries first..first+count-1 of a [row][head][stride]
 // table, by the whole CTA.  `final` writes the normalised output row; otherwise
 // the merged partial goes to entry dst_index of a second table.
-#ifndef SK_MERGE_GROUP
-#define SK_MERGE_GROUP 8
-#endif
-constexpr int MERGE_GROUP = SK_MERGE_GROUP;  // splits merged by the last CTA of each group
+constexpr int MERGE_GROUP = 8;  // splits merged by the last CTA of each group
 
 template <int HD, int G, int THREADS>
 __device__ void merge_partials(const float* po, const float* pml, size_t stride, int first, int count, int r, int kv_h,
@@ -847,7 +832,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
     const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    TL_MARK(0, 0);
     init_barriers(sm);
 
     WarpState<G> st;
@@ -857,10 +841,8 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         if (lane == 0) {
             const bool ok = produce_tiles<HD, C>(sm, kbase, vbase, rows, 0, n_early, a.status);
             grid_dependency_wait();
-            TL_MARK(1, C::NW * 32);
             grid_launch_dependents();
             if (ok) produce_tiles<HD, C>(sm, kbase, vbase, rows, n_early, ntiles, a.status);
-            TL_MARK(5, C::NW * 32);
         }
     } else {
         // ---------------- consumers ----------------
@@ -971,9 +953,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");  // consumers only: qs/xk/xv complete
         ulonglong2 q[G][C::CPL];
         load_q<HD, G, C>(q, sm.qs, C::QS_STRIDE, lane & 15);
-        TL_MARK(2, 0);
         consume_slice<HD, G, C>(sm, ntiles, rows, q, st, warp, lane, a.scale, a.status);
-        TL_MARK(3, 0);
         if (owns_new && warp == (ntiles % C::NW)) {
             // the new token's own row, from shared memory (one valid row)
             f32x2* ps = reinterpret_cast<f32x2*>(sm.warp_scratch + warp * C::WARP_SCRATCH);
@@ -981,13 +961,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         }
         finish_warp<HD, G, C>(st);
     }
-    TL_MARK(8, 0);
     __syncthreads();  // every issued copy has landed; the ring is free
-    TL_MARK(9, 0);
     if (a.inputs_ready) grid_dependency_wait();  // the shared scratch below may still be in use by the previous grid
     if (warp < C::NW) park_state<HD, G, C>(st, sm.stages, warp, lane);
     __syncthreads();
-    TL_MARK(10, 0);
     const int nsplit_here = (visible + a.chunk_rows - 1) / a.chunk_rows;
     const bool words = a.stream_merge && nsplit_here > 1;   // partials as {value, epoch} words
     unsigned long long* pw = reinterpret_cast<unsigned long long*>(a.part_o);
@@ -1060,7 +1037,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
             }
         }
     }
-    TL_MARK(4, 0);
     if (nsplit_here == 1) return;
     if (a.stream_merge) {
         // The first CTAs of the kv head fold the partials, 64 columns of one query head at
@@ -1069,7 +1045,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         const int nm = min(G * HALVES, nsplit_here);
         if (split >= nm) return;
         __syncthreads();   // the ring area is reused as merge scratch: every thread is done with merge_warps
-        TL_MARK(7, 0);
         for (int m = split; m < G * HALVES; m += nm) {
             const int g = m / HALVES, half = m - g * HALVES;
             const size_t hrow = (size_t)r * H + (size_t)kv_h * G + g;
@@ -1078,7 +1053,6 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
                                                   half, a.status))
                 return;
         }
-        TL_MARK(6, 0);
         return;
     }
     // ---- two-level merge by "last finisher" tickets: the last CTA of each group
@@ -1101,21 +1075,22 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
 }
 
 template <class K>
-cudaError_t set_smem_once(K kernel, size_t smem, unsigned long long& configured) {
+cudaError_t set_smem_once(K kernel, size_t smem, std::atomic<unsigned long long>& configured) {
+    // one bit per device; two threads that race here both set the attribute, which is harmless
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev >= 64 || !(configured >> dev & 1ull)) {
+    if (dev >= 64 || !(configured.load(std::memory_order_acquire) >> dev & 1ull)) {
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        if (dev < 64) configured |= 1ull << dev;
+        if (dev < 64) configured.fetch_or(1ull << dev, std::memory_order_release);
     }
     return cudaSuccess;
 }
 
 template <int HD, int G, class C = SK<HD, G>>
 cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
-    static unsigned long long configured = 0;  // bit per device
+    static std::atomic<unsigned long long> configured{0};  // bit per device
     cudaError_t e = set_smem_once(attn_splitk_kernel<HD, G, C>, C::SMEM_BYTES, configured);
     if (e != cudaSuccess) return e;
     const int rows = a.batch * a.T;
@@ -1133,7 +1108,7 @@ cudaError_t launch_sk(const AttnArgs& a, cudaStream_t s) {
 
 template <int HD, int G, class C = SK<HD, G>>
 cudaError_t launch_fused(const FusedArgs& a, cudaStream_t s) {
-    static unsigned long long configured = 0;
+    static std::atomic<unsigned long long> configured{0};
     cudaError_t e = set_smem_once(attn_decode_fused_kernel<HD, G, C>, C::SMEM_BYTES, configured);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg{};
@@ -1171,7 +1146,7 @@ cudaError_t dispatch_g(const A& a, F&& f) {
 constexpr int GATHER_WAIT_THREADS = 256;
 __global__ void __launch_bounds__(GATHER_WAIT_THREADS) gather_wait_kernel(const unsigned long long* words, float* data,
                                                                           long long count, unsigned epoch,
-                                                                          AttnStatus* status) {
+                                                                          unsigned long long limit_ns, AttnStatus* status) {
     grid_launch_dependents();
     const unsigned long long t0 = globaltimer_ns();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
@@ -1182,7 +1157,7 @@ __global__ void __launch_bounds__(GATHER_WAIT_THREADS) gather_wait_kernel(const 
                 data[i] = __uint_as_float((unsigned)w);
                 break;
             }
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 21;
                 return;
             }
@@ -1221,7 +1196,8 @@ __global__ void merge_parts_kernel(const float* __restrict__ gathered, int seq_p
 // unpacked in between.  Launched like gather_wait_kernel.
 __global__ void __launch_bounds__(128) gather_merge_kernel(const unsigned long long* words, int seq_parts,
                                                            int heads_per_rank, int head_dim, unsigned epoch,
-                                                           float* __restrict__ out_full, AttnStatus* status) {
+                                                           unsigned long long limit_ns, float* __restrict__ out_full,
+                                                           AttnStatus* status) {
     grid_launch_dependents();
     const int g = blockIdx.y, h = blockIdx.x;
     const size_t rank_stride = (size_t)heads_per_rank * (head_dim + 1);
@@ -1232,7 +1208,7 @@ __global__ void __launch_bounds__(128) gather_merge_kernel(const unsigned long l
             unsigned long long w;
             asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
             if ((unsigned)(w >> 32) == epoch) return __uint_as_float((unsigned)w);
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 if (status != nullptr && atomicCAS(&status->code, DEV_OK, DEV_WAIT_TIMEOUT) == DEV_OK) status->where = 22;
                 ok = false;
                 return 0.0f;
@@ -1262,7 +1238,7 @@ __global__ void __launch_bounds__(128) gather_merge_kernel(const unsigned long l
 }  // namespace
 
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
-                               AttnStatus* status, cudaStream_t s) {
+                               unsigned long long limit_ns, AttnStatus* status, cudaStream_t s) {
     if (count <= 0) return cudaSuccess;
     cudaLaunchConfig_t cfg{};
     long long blocks = (count + 2 * GATHER_WAIT_THREADS - 1) / (2 * GATHER_WAIT_THREADS);   // two words per thread
@@ -1276,11 +1252,12 @@ cudaError_t launch_gather_wait(const unsigned long long* words, float* data, lon
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_wait_kernel, words, data, count, epoch, status);
+    return cudaLaunchKernelEx(&cfg, gather_wait_kernel, words, data, count, epoch, limit_ns, status);
 }
 
 cudaError_t launch_gather_merge(const unsigned long long* words, int world, int seq_parts, int heads_per_rank, int head_dim,
-                                unsigned epoch, float* out_full, AttnStatus* status, cudaStream_t s) {
+                                unsigned epoch, unsigned long long limit_ns, float* out_full, AttnStatus* status,
+                                cudaStream_t s) {
     if (seq_parts <= 0 || seq_parts > MAX_PEERS || world % seq_parts != 0) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(heads_per_rank, world / seq_parts);
@@ -1292,7 +1269,8 @@ cudaError_t launch_gather_merge(const unsigned long long* words, int world, int 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, gather_merge_kernel, words, seq_parts, heads_per_rank, head_dim, epoch, out_full, status);
+    return cudaLaunchKernelEx(&cfg, gather_merge_kernel, words, seq_parts, heads_per_rank, head_dim, epoch, limit_ns, out_full,
+                              status);
 }
 
 cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, int heads_per_rank, int head_dim,
@@ -1368,7 +1346,13 @@ cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s) {
 //  * the address of the array is looked up once per device, by the first call
 //    made with that device current (cudaGetSymbolAddress; the symbol's name is
 //    only a host-side handle, never a device address).  Make that first call
-//    before any stream capture begins.
+//    before any stream capture begins.  The look-up is serialised by a mutex, so
+//    threads may make their first calls concurrently;
+//  * there is no context and therefore no device status word: should one of the
+//    kernel's bounded waits on its shared-memory pipeline ever run out (~1 s;
+//    only a programming error can cause it), the kernel leaves its loop and the
+//    call has long returned 0.  A device-side wait failure is NOT reported by
+//    this entry; callers that need the report use a context and forward_dev.
 // ---------------------------------------------------------------------------
 namespace shainet {
 namespace {
@@ -1381,6 +1365,7 @@ struct NoAllocDevice {
     int sm_count = 0;
 };
 NoAllocDevice g_noalloc_dev[64];
+std::mutex g_noalloc_mutex;   // guards the one-time set-up per device
 
 }  // namespace
 }  // namespace shainet
@@ -1414,19 +1399,26 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
         set_last_error_message("shainet_attn_decode_noalloc: no usable current device");
         return -2;  // SHAINET_ATTN_E_CUDA
     }
-    NoAllocDevice& nd = g_noalloc_dev[dev];
-    if (!nd.scratch) {
-        // One-time set-up for this device: resolve the array's device address.
-        float* ptr = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
-        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&nd.sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess || !ptr) {
-            cudaGetLastError();
-            snprintf(msg, sizeof msg, "shainet_attn_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
-            set_last_error_message(msg);
-            return -2;
+    NoAllocDevice nd;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        NoAllocDevice& slot = g_noalloc_dev[dev];
+        if (!slot.scratch) {
+            // One-time set-up for this device: resolve the array's device address.
+            float* ptr = nullptr;
+            int sms = 0;
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess || !ptr) {
+                cudaGetLastError();
+                snprintf(msg, sizeof msg, "shainet_attn_decode_noalloc: set-up failed: %s", cudaGetErrorString(e));
+                set_last_error_message(msg);
+                return -2;
+            }
+            slot.sm_count = sms;
+            slot.scratch = ptr;
         }
-        nd.scratch = ptr;
+        nd = slot;
     }
     AttnArgs a{};
     a.q_rot = q_dev;
@@ -1465,9 +1457,3 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
     }
     return 0;
 }
-
-#ifdef SK_TIMELINE
-extern "C" int shainet_debug_timeline(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, shainet::g_timeline, sizeof(unsigned long long) * 64 * 320 * 16);
-}
-#endif

@@ -149,10 +149,11 @@ cudaError_t launch_merge_parts(const float* gathered, int world, int seq_parts, 
 
 // Bounded wait for the words of all ranks' (row, log-sum-exp) pairs of one exchange slot, merged per head group.
 cudaError_t launch_gather_merge(const unsigned long long* words, int world, int seq_parts, int heads_per_rank, int head_dim,
-                                unsigned epoch, float* out_full, AttnStatus* status, cudaStream_t s);
+                                unsigned epoch, unsigned long long limit_ns, float* out_full, AttnStatus* status,
+                                cudaStream_t s);
 // Bounded wait until `count` exchange words carry `epoch`; unpacks them into `data`.
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
-                               AttnStatus* status, cudaStream_t s);
+                               unsigned long long limit_ns, AttnStatus* status, cudaStream_t s);
 
 // Standard-normal fill of `len` positions per kv head (benchmark caches).
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,

@@ -37,7 +37,9 @@ def read_safetensors(path):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("SHAINET_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_tiny_llama_slice.py <path of a SHAInet checkout> (or set SHAINET_REFERENCE_ROOT)")
     d = os.path.join(root, "spec", "test_data", "tiny-llama")
     cfg = json.load(open(os.path.join(d, "config.json")))
     t = read_safetensors(os.path.join(d, "model.safetensors"))

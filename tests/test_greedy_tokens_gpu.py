@@ -1,35 +1,48 @@
-"""Greedy decode through a LLaMA-3.2-1B-shaped decoder: the token sequence produced
+"""Greedy decode through LLaMA-3.2-1B-shaped decoders: the token sequence produced
 with the library's attention equals the one produced with the CPU oracle's attention,
 everything outside attention (embedding, RMSNorm, projections, SwiGLU, lm_head,
-argmax) being the same numpy code on both sides.
+argmax) being the SAME code on both sides, so only the attention call differs.
 
 Shapes follow the benchmark configurations: hidden 2048, 32 query / 8 kv heads,
 head_dim 64, RoPE theta 500000, weights N(0, 0.02) from a seed, uniform-random
-prompt ids.  Config 1: one layer, 512-token prefill, 128 greedy steps.  Config 2 is run
-reduced (4 of 16 layers, FFN 4096, 1024-token prefill, 64 steps) so that the CPU side
-finishes in seconds.  The prefill goes through the library's default dispatch (TF32
-tensor-core kernel), the decode steps through the fused fp32 kernel."""
+prompt ids.
+
+* Config 1: one layer, fp32 weights, 512-token prefill, 128 greedy steps (numpy outside
+  attention, vocabulary 4096).
+* Config 2 as named: 16 layers, FFN 8192, vocabulary 128256, RMSNorm eps 1e-5, every
+  projection / FFN / lm_head weight Q8_0-quantised (int8 with one fp32 scale per 32
+  input elements of an output column: scale = max|w|/127, q = clamp(round(w/scale), +-127),
+  src/shainet/math/quantized_cuda_matrix.cr:84-110) and used dequantised, 4096-token
+  prefill of uniform-random ids, 256 greedy steps.  The non-attention arithmetic runs in
+  torch on the GPU (fp32, TF32 off) for both sides; it is not the code under test.
+
+The prefill goes through the library's default dispatch (TF32 tensor-core kernel), the
+decode steps through the fused fp32 kernel.  With random weights the logits over 128256
+entries are nearly flat, so the first position at which the two runs could differ is
+judged by the oracle side's top-2 margin: a difference at a margin below the attention
+tolerance's effect on the logits is a tie, not a failure, and ends the comparison there
+(the two runs no longer see the same tokens)."""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
 
 HID, H, KV, HD, THETA, EPS = 2048, 32, 8, 64, 500000.0, 1e-5
-VOCAB = 4096
 
 
+# ---------------------------------------------------------------- config 1 (numpy)
 def _rmsnorm(x, w):
     x = x.astype(np.float32)
     ms = np.mean(x.astype(np.float64) ** 2, axis=-1, keepdims=True)
     return (x * (1.0 / np.sqrt(ms + EPS)).astype(np.float32) * w).astype(np.float32)
 
 
-def _weights(rng, layers, ffn):
+def _weights(rng, layers, ffn, vocab):
     f = lambda *s: (0.02 * rng.standard_normal(s)).astype(np.float32)
     blocks = [dict(norm1=np.ones(HID, np.float32), norm2=np.ones(HID, np.float32), wq=f(HID, H * HD), wk=f(HID, KV * HD),
                    wv=f(HID, KV * HD), wo=f(H * HD, HID), gate=f(HID, ffn), up=f(HID, ffn), down=f(ffn, HID))
               for _ in range(layers)]
-    return dict(emb=f(VOCAB, HID), norm=np.ones(HID, np.float32), blocks=blocks)
+    return dict(emb=f(vocab, HID), norm=np.ones(HID, np.float32), blocks=blocks)
 
 
 def _generate(w, attn, prompt, steps):
@@ -55,14 +68,13 @@ def _generate(w, attn, prompt, steps):
     return out, margins
 
 
-@pytest.mark.parametrize("layers,ffn,prefill,steps", [(1, 8192, 512, 128), (4, 4096, 1024, 64)],
-                         ids=["config1_one_layer", "config2_reduced"])
-def test_greedy_tokens_match_the_oracle(layers, ffn, prefill, steps):
+def test_greedy_tokens_config1_one_layer():
     import shainet_b200 as S
     from oracle import oracle as O
+    layers, ffn, prefill, steps, vocab = 1, 8192, 512, 128, 4096
     rng = np.random.default_rng(1001)
-    w = _weights(rng, layers, ffn)
-    prompt = rng.integers(0, VOCAB, prefill)
+    w = _weights(rng, layers, ffn, vocab)
+    prompt = rng.integers(0, vocab, prefill)
     oracle_attn = [O.OracleAttention(H, KV, HD, THETA, EPS) for _ in range(layers)]
     ref, margins = _generate(w, [lambda q, k, v, o=o: o.attend_cached(q, k, v, threads=8) for o in oracle_attn], prompt, steps)
     ctx = S.AttnContext(0)
@@ -73,7 +85,102 @@ def test_greedy_tokens_match_the_oracle(layers, ffn, prefill, steps):
         g.close()
     ctx.close()
     assert len(set(ref)) > 1, "degenerate generation"
-    # a tie in the oracle's own logits would make the comparison meaningless
     assert min(margins) > 0.0
     assert got == ref, (f"first difference at step {next(i for i, (a, b) in enumerate(zip(got, ref)) if a != b)}; "
                         f"smallest top-2 logit margin on the oracle side {min(margins):.3e}")
+
+
+# ---------------------------------------------------------------- config 2 as named (torch outside attention)
+def _q8_0(w):
+    """Q8_0 of a weight [K, N] (input-major, as the reference holds it after the loader's
+    transpose), dequantised again: per output column and block of 32 consecutive K."""
+    import torch
+    K, N = w.shape
+    assert K % 32 == 0
+    blk = w.reshape(K // 32, 32, N)
+    max_abs = blk.abs().amax(dim=1, keepdim=True)
+    scale = torch.where(max_abs > 0, max_abs / 127.0, torch.ones_like(max_abs))
+    inv = 1.0 / scale
+    q = torch.clamp(torch.round(blk * inv), -127.0, 127.0)   # round half to even, like Crystal's Float32#round
+    return (q * scale).reshape(K, N).contiguous()
+
+
+class _Q8Decoder:
+    def __init__(self, layers, ffn, vocab, seed, dev):
+        import torch
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        f = lambda *s: _q8_0(0.02 * torch.randn(*s, device=dev, generator=g))
+        self.emb = 0.02 * torch.randn(vocab, HID, device=dev, generator=g)       # the embedding gather stays fp32
+        self.lm_head = _q8_0(self.emb.t().contiguous())                          # tied, quantised as a [2048, vocab] weight
+        self.blocks = [dict(wq=f(HID, H * HD), wk=f(HID, KV * HD), wv=f(HID, KV * HD), wo=f(H * HD, HID),
+                            gate=f(HID, ffn), up=f(HID, ffn), down=f(ffn, HID)) for _ in range(layers)]
+        self.dev = dev
+
+    @staticmethod
+    def _norm(x):
+        import torch
+        ms = (x.double() ** 2).mean(dim=-1, keepdim=True)
+        return (x.double() / torch.sqrt(ms + EPS)).float()      # gamma = 1 (rms_norm.cr:29-34)
+
+    def forward(self, ids, attn):
+        """attn[l](q, k, v) with numpy rows in and out; returns the last row's logits (torch, device)."""
+        import torch
+        x = self.emb[torch.as_tensor(ids, device=self.dev)]
+        for l, b in enumerate(self.blocks):
+            n = self._norm(x)
+            q, k, v = n @ b["wq"], n @ b["wk"], n @ b["wv"]
+            a = attn[l](q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy())
+            x = x + torch.from_numpy(a).to(self.dev) @ b["wo"]
+            n = self._norm(x)
+            gt = n @ b["gate"]
+            x = x + ((gt / (1.0 + torch.exp(-gt))) * (n @ b["up"])) @ b["down"]
+        return (self._norm(x[-1:]) @ self.lm_head)[0]
+
+    def generate(self, attn, prompt, steps):
+        """Greedy tokens, the logits' top-2 margin at every step and their spread."""
+        import torch
+        toks, margins, spreads = [], [], []
+        logits = self.forward(prompt, attn)
+        for _ in range(steps):
+            top = torch.topk(logits, 2).values
+            margins.append(float(top[0] - top[1]))
+            spreads.append(float(logits.max() - logits.min()))
+            tok = int(torch.argmax(logits))      # first index of the maximum (sampler.cr:38-53)
+            toks.append(tok)
+            logits = self.forward([tok], attn)
+        return toks, margins, spreads
+
+
+def test_greedy_tokens_config2_as_named():
+    import torch
+    import shainet_b200 as S
+    from oracle import oracle as O
+    layers, ffn, vocab, prefill, steps = 16, 8192, 128256, 4096, 256
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dev = torch.device("cuda:0")
+    model = _Q8Decoder(layers, ffn, vocab, 2001, dev)
+    prompt = np.random.default_rng(2002).integers(0, vocab, prefill)
+    threads = max(1, O.max_threads())
+    oracle_attn = [O.OracleAttention(H, KV, HD, THETA, EPS) for _ in range(layers)]
+    ref, margins, spreads = model.generate([lambda q, k, v, o=o: o.attend_cached(q, k, v, threads=threads)
+                                            for o in oracle_attn], prompt, steps)
+    ctx = S.AttnContext(0)
+    lib_attn = [S.LlamaAttention(ctx, H, KV, HD, THETA, EPS) for _ in range(layers)]
+    got, _, _ = model.generate([lambda q, k, v, g=g: g.forward_cached(q, k, v) for g in lib_attn], prompt, steps)
+    for g in lib_attn:
+        assert g.cache_len == prefill + steps
+        g.close()
+    ctx.close()
+    assert len(set(ref)) > 1, "degenerate generation"
+    diff = next((i for i, (a, b) in enumerate(zip(got, ref)) if a != b), None)
+    print(f"config 2: {steps} greedy tokens, first difference: {diff}; smallest top-2 margin {min(margins):.3e}, "
+          f"logit spread {np.mean(spreads):.3e}")
+    if diff is not None:
+        # The attention outputs of the two runs differ by up to 2e-3 (TF32 prefill) relative to their
+        # scale; a margin below that fraction of the logits' spread cannot be resolved by either.
+        tie_bound = 2e-3 * spreads[diff]
+        assert margins[diff] <= tie_bound, (f"tokens differ at step {diff} where the oracle's top-2 margin "
+                                            f"{margins[diff]:.3e} exceeds the tie bound {tie_bound:.3e}")
+    del model
+    torch.cuda.empty_cache()

@@ -94,6 +94,29 @@ def test_wait_for_a_flag_nobody_raises_reports_a_timeout():
     c.close()
 
 
+def test_the_cross_rank_wait_limit_is_a_context_setting():
+    """A host whose ranks may be late by more (or must fail faster) than the default second sets the
+    limit itself: 50 ms here, observed through the time the abandoned wait took."""
+    import time
+    import shainet_b200 as S
+    c = S.AttnContext(0)
+    c.comm_open([c.comm_create(64)], 0)
+    with pytest.raises(S.ShainetAttnError) as ei:
+        c.comm_set_wait_limit_ms(0)
+    assert ei.value.code == _lib.E_INVALID
+    c.comm_set_wait_limit_ms(50)
+    c.sync()
+    t0 = time.perf_counter()
+    c.comm_wait(0, 16, 777)
+    with pytest.raises(S.ShainetAttnError) as ei:
+        c.sync()
+    waited = time.perf_counter() - t0
+    assert ei.value.code == _lib.E_DEVICE_WAIT
+    assert 0.04 <= waited < 0.6, waited
+    c.sync()
+    c.close()
+
+
 WORKER = r"""
 import os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, os.path.join(sys.argv[1], "tests")); sys.path.insert(0, sys.argv[1])
