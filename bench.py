@@ -352,6 +352,72 @@ def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
                          "avg_launch_us": us, "launches_timed": steps * layers}}
 
 
+def model_decode_block(S, ctx, dev, steps=96, warm=8):
+    """BASELINE config 2 as a whole model on the device: 16 LLaMA-3.2-1B-shaped blocks (hidden 2048, 32/8
+    heads, head_dim 64, FFN 8192), vocabulary 128256, every projection / FFN / lm_head weight Q8_0, fp32
+    KV cache at ctx 4096, greedy decode.  One call generates `steps` tokens; the only host traffic is the
+    first token id in and the generated ids out, so the wall clock of the call is the end-to-end figure.
+    Weights are random int8 with random scales created on the device (distinct memory per layer, 1.4 GB in
+    all, far more than L2 holds); bytes per token = all weights and scales once + the K/V of every layer."""
+    import torch
+    wl = WORKLOADS["cfg2"]
+    H, KV, hd, layers, L = wl["H"], wl["KV"], wl["hd"], wl["layers"], wl["ctx"]
+    d, ffn, vocab, eps = 2048, 8192, 128256, 1e-5
+    g = torch.Generator(device=dev)
+    g.manual_seed(2201)
+    keep, weight_bytes = [], 0
+
+    def q8(K, N):
+        nonlocal weight_bytes
+        q = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8, generator=g)
+        sc = (0.02 / 127.0) * (0.5 + torch.rand(N, K // 32, device=dev, generator=g))
+        keep.extend([q, sc])
+        weight_bytes += q.numel() + 4 * sc.numel()
+        return S.Q8Weight.wrap(ctx, q.data_ptr(), sc.data_ptr(), K, N)
+
+    ones = np.ones(d, np.float32)
+    blocks, attns, weights = [], [], []
+    for l in range(layers):
+        a = S.LlamaAttention(ctx, H, KV, hd, wl["theta"], eps, initial_capacity=L + steps + warm + 8)
+        a.cache.fill_normal(L, 2301 + l)
+        w = dict(wq=q8(d, H * hd), wk=q8(d, KV * hd), wv=q8(d, KV * hd), wo=q8(H * hd, d), gate=q8(d, ffn), up=q8(d, ffn),
+                 down=q8(ffn, d))
+        blocks.append(S.LlamaBlock(ctx, a, d, eps, ones, w["wq"], w["wk"], w["wv"], w["wo"], ones, w["gate"], w["up"], w["down"]))
+        attns.append(a)
+        weights.extend(w.values())
+    head = q8(d, vocab)
+    weights.append(head)
+    emb = (0.02 * np.random.default_rng(2202).standard_normal((vocab, d), dtype=np.float32))
+    dec = S.Decoder(ctx, blocks, emb, ones, head, None, eps)
+    del emb
+    dec.generate([1], warm)
+    for a in attns:
+        a.cache.truncate(L)
+    t0 = time.perf_counter()
+    toks = dec.generate([1], steps)
+    wall = time.perf_counter() - t0
+    dec.close()
+    for b in blocks:
+        b.close()
+    for a in attns:
+        a.close()
+    for w in weights:
+        w.close()
+    kv_bytes = layers * decode_bytes(wl, L + (steps + 1) / 2.0)
+    per_token = weight_bytes + kv_bytes + d * 4
+    peak, kind = measured_peak()
+    gbs = per_token * steps / wall / 1e9
+    return {"workload": "cfg2: LLaMA-3.2-1B-shaped decoder, 16 layers, vocabulary 128256, Q8_0 weights, fp32 KV cache ctx 4096, "
+                        "greedy decode on the device (shainet_attn_decoder_generate)",
+            "tokens_per_s": steps / wall, "ms_per_token": wall / steps * 1e3, "steps": steps,
+            "distinct_tokens": int(len(set(toks.tolist()))),
+            "h2d_bytes_per_call": 4, "d2h_bytes_per_call": 4 * steps, "launches_per_token": 5 * layers + 3,
+            "timing": "wall clock of one blocking generate call (prompt of one token, then steps - 1 device-fed steps)",
+            "roofline": {"bound": "hbm", "kernel": "q8_gemv_kernel + attn_decode_fused_kernel chain", "achieved": gbs, "peak": peak,
+                         "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "bytes_per_token": per_token,
+                         "weight_bytes": weight_bytes, "kv_bytes": kv_bytes}}
+
+
 PARITY_TOL = 1e-5
 
 
@@ -678,8 +744,10 @@ def run_ours(args, wl, rank, world, local_rank):
     if world == 1 and not args.no_prefill:
         prefill = prefill_block(S, ctx, dev, tstream)
         batched = batched_block(S, ctx, dev, tstream)
+    model = None
     if world == 1 and not args.no_prefill and args.workload != "cfg2":
         short_ctx = short_context_block(S, ctx, dev, tstream)
+        model = model_decode_block(S, ctx, dev)
     parity = parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, layers * world * pay, epoch[0] + 1)
 
     if rank == 0:
@@ -731,6 +799,8 @@ def run_ours(args, wl, rank, world, local_rank):
             line["batched_decode"] = batched
         if short_ctx is not None:
             line["decode_ctx4k"] = short_ctx
+        if model is not None:
+            line["decode_model_cfg2"] = model
         if world == 1 and not args.no_cpu_baseline:
             threads = host_threads()
             cpu_port_rate(wl, threads, 1, 1)

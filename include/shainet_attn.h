@@ -234,6 +234,79 @@ void kv_cache_append_f32(const float* staging, float* kc, float* vc, int new_tok
 void attention_kv_f32(const float* q, const float* kc, const float* vc, float* out, float* ws, int new_tokens,
                       int start_pos, int num_heads, int heads_per_kv, int head_dim, int capacity, float scale);
 
+/* ---- Q8_0 weights and the decode step around attention, resident on the device.
+ *
+ * A Q8_0 weight is the reference's QuantizedCudaMatrix
+ * (src/shainet/math/quantized_cuda_matrix.cr:8-153): int8 values q[N][K] (output-major)
+ * and one fp32 scale per 32 consecutive K of an output, scales[N][ceil(K/32)], for a
+ * weight that maps K inputs to N outputs.  q8_create quantises a host fp32 matrix
+ * [K, N] (input-major, the layout the reference's loader produces) exactly as
+ * from_simple does (:74-115); q8_create_raw uploads already quantised host arrays;
+ * q8_wrap adopts device arrays the caller owns (the q_ptr / scale_ptr of an existing
+ * QuantizedCudaMatrix) without copying.  q8_gemv_dev is gemv_into (:143-153):
+ * y[M, N] = x[M, K] . dequant(W) on device pointers.  gemm_q8_f32 is the
+ * symbol-compatible replacement for the kernel wrapper the reference loads with dlsym
+ * (src/shainet/native/cuda_kernels.cu:616-629; src/shainet/cuda.cr gemm_q8_f32):
+ * device pointers, legacy default stream, errors printed. */
+typedef struct shainet_attn_q8 shainet_attn_q8;
+int shainet_attn_q8_create(shainet_attn_ctx* ctx, shainet_attn_q8** out, const float* w_host, int K, int N);
+int shainet_attn_q8_create_raw(shainet_attn_ctx* ctx, shainet_attn_q8** out, const signed char* q_host,
+                               const float* scales_host, int K, int N);
+int shainet_attn_q8_wrap(shainet_attn_ctx* ctx, shainet_attn_q8** out, const signed char* q_dev, const float* scales_dev,
+                         int K, int N);
+int shainet_attn_q8_destroy(shainet_attn_q8* w);
+int shainet_attn_q8_export(const shainet_attn_q8* w, signed char* q_host, float* scales_host);
+int shainet_attn_q8_gemv_dev(shainet_attn_ctx* ctx, const shainet_attn_q8* w, const float* x_dev, float* y_dev, int M,
+                             void* stream);
+void gemm_q8_f32(const float* x, const signed char* q, const float* scales, float* y, int M, int N, int K);
+
+/* One decoder block with every step on the device: LlamaBlock#forward_cached
+ * (src/shainet/transformer/llama_block.cr:189-196) = norm1 (RMSNorm,
+ * src/shainet/transformer/rms_norm.cr:18-37) -> q/k/v projections (:253-255, 726-768)
+ * -> the attention of this library on `kv` -> o_proj (:298) -> residual -> norm2 ->
+ * SwiGLU FFN (src/shainet/transformer/swiglu_ff.cr:76-91) -> residual.  x and out are
+ * [new_tokens, d_model].  The block borrows kv and the weights (they must outlive it)
+ * and keeps its own stacked copy of the q/k/v weights so that one launch serves all
+ * three.  norm2/gate/up/down may all be NULL: the block then ends after the first
+ * residual (models whose FFN stays with the caller, e.g. mixture-of-experts layers).
+ * eps is the RMSNorm epsilon (LlamaBlock.new's eps, :76).  forward_host makes one
+ * host-to-device copy (x) and one device-to-host copy (the block output) per call
+ * where the reference makes sixteen; forward_dev makes none. */
+typedef struct shainet_attn_block shainet_attn_block;
+int shainet_attn_block_create(shainet_attn_ctx* ctx, shainet_attn_block** out, shainet_attn_kv* kv, int d_model,
+                              const float* norm1_host, const shainet_attn_q8* wq, const shainet_attn_q8* wk,
+                              const shainet_attn_q8* wv, const shainet_attn_q8* wo, const float* norm2_host,
+                              const shainet_attn_q8* gate, const shainet_attn_q8* up, const shainet_attn_q8* down,
+                              double eps);
+int shainet_attn_block_destroy(shainet_attn_block* block);
+int shainet_attn_block_forward_dev(shainet_attn_ctx* ctx, shainet_attn_block* block, const float* x_dev, float* out_dev,
+                                   int new_tokens, void* stream);
+int shainet_attn_block_forward_host(shainet_attn_ctx* ctx, shainet_attn_block* block, const float* x, float* out,
+                                    int new_tokens);
+
+/* The token loop: Network#run(Array(Int32)) with use_kv_cache
+ * (src/shainet/basic/network_run.cr:185-264, 294-315) = embedding gather
+ * (src/shainet/text/embedding_layer.cr:129-156) -> blocks -> final RMSNorm (:210-212)
+ * -> Q8_0 lm_head on the last row (:1465-1487) -> bias (:222-226), and
+ * Sampler.greedy (src/shainet/text/sampler.cr:38-53: first index of the largest finite
+ * logit, 0 if none).  embedding_host is [vocab, d_model] fp32; final_norm_host and
+ * lm_bias_host may be NULL.  decoder_run takes n_tokens ids (a prompt, or one token),
+ * appends them to every block's cache and returns the last row's logits [vocab]
+ * and/or its greedy token (either pointer may be NULL); it is blocking.
+ * decoder_generate runs the prompt and then steps - 1 further tokens, each step
+ * embedding the previous step's arg-max straight from device memory, and returns
+ * the `steps` greedy tokens with one copy at the end: no token, logit or activation
+ * visits the host in between. */
+typedef struct shainet_attn_decoder shainet_attn_decoder;
+int shainet_attn_decoder_create(shainet_attn_ctx* ctx, shainet_attn_decoder** out, shainet_attn_block* const* blocks,
+                                int n_layers, const float* embedding_host, int vocab, const float* final_norm_host,
+                                const shainet_attn_q8* lm_head, const float* lm_bias_host, double eps);
+int shainet_attn_decoder_destroy(shainet_attn_decoder* dec);
+int shainet_attn_decoder_run(shainet_attn_ctx* ctx, shainet_attn_decoder* dec, const int32_t* token_ids, int n_tokens,
+                             float* logits_host, int32_t* next_token_host);
+int shainet_attn_decoder_generate(shainet_attn_ctx* ctx, shainet_attn_decoder* dec, const int32_t* prompt_ids, int n_prompt,
+                                  int steps, int32_t* tokens_host);
+
 /* ---- decode without allocating.  This entry has no counterpart in the
  * reference.  It is for hosts that cannot let a library allocate device memory:
  * a server that gave the GPU's whole memory budget to its own pool at start-up

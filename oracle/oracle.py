@@ -56,6 +56,12 @@ def lib():
     L.oracle_swiglu.argtypes = [F, I, I, I, F, F, F, F]
     L.oracle_add.argtypes = [F, F, C.c_size_t, F]
     L.oracle_max_threads.restype = I
+    L.oracle_q8_quantize.argtypes = [F, I, I, P, F]
+    L.oracle_q8_gemv.argtypes = [F, P, F, F, I, I, I, I, I]
+    L.oracle_swiglu_act.argtypes = [F, F, C.c_size_t, F]
+    L.oracle_add_bias_row.argtypes = [F, F, I]
+    L.oracle_greedy.argtypes = [F, I]
+    L.oracle_greedy.restype = I
     _LIB = L
     return L
 
@@ -212,3 +218,97 @@ class OracleLlamaBlock:
 
     def clear_cache(self):
         self.attn.clear_cache()
+
+
+class OracleQ8:
+    """A Q8_0 weight as the reference holds it (QuantizedCudaMatrix,
+    src/shainet/math/quantized_cuda_matrix.cr): quantised from an fp32 matrix [K, N]."""
+
+    def __init__(self, w):
+        w = _f32(w)
+        self.K, self.N = w.shape
+        self.q = np.empty((self.N, self.K), np.int8)
+        self.scales = np.empty((self.N, (self.K + 31) // 32), np.float32)
+        lib().oracle_q8_quantize(_fp(w), self.K, self.N, self.q.ctypes.data_as(C.c_void_p), _fp(self.scales))
+
+    def dequantised(self) -> np.ndarray:
+        """[K, N] fp32: q * scale."""
+        s = np.repeat(self.scales, 32, axis=1)[:, :self.K]
+        return (self.q.astype(np.float32) * s).T.copy()
+
+    def gemv(self, x, fused=1, threads=None) -> np.ndarray:
+        """y = x . dequant(W) in the reduction order of the reference's gemm_q8_f32_kernel."""
+        x = _f32(x)
+        M = x.shape[0]
+        assert x.shape == (M, self.K)
+        y = np.empty((M, self.N), np.float32)
+        lib().oracle_q8_gemv(_fp(x), self.q.ctypes.data_as(C.c_void_p), _fp(self.scales), _fp(y), M, self.N, self.K, fused,
+                             threads or max_threads())
+        return y
+
+
+def swiglu_act(gate, up) -> np.ndarray:
+    gate, up = _f32(gate), _f32(up)
+    out = np.empty_like(gate)
+    lib().oracle_swiglu_act(_fp(gate), _fp(up), gate.size, _fp(out))
+    return out
+
+
+def greedy(logits) -> int:
+    logits = _f32(logits).reshape(-1)
+    return lib().oracle_greedy(_fp(logits), logits.size)
+
+
+class OracleQ8Block:
+    """LlamaBlock#forward_cached (llama_block.cr:189-196) with Q8_0 projections: the host
+    steps in the reference's arithmetic, the GEMVs in its kernel's order."""
+
+    def __init__(self, attn: OracleAttention, eps, norm1, wq, wk, wv, wo, norm2=None, gate=None, up=None, down=None):
+        self.attn, self.eps = attn, eps
+        self.norm1, self.norm2 = _f32(norm1), (None if norm2 is None else _f32(norm2))
+        self.wq, self.wk, self.wv, self.wo, self.gate, self.up, self.down = wq, wk, wv, wo, gate, up, down
+
+    def forward_cached(self, x, threads=None) -> np.ndarray:
+        x = _f32(x)
+        n = rmsnorm(x, self.norm1, self.eps)
+        a = self.attn.attend_cached(self.wq.gemv(n), self.wk.gemv(n), self.wv.gemv(n), threads=threads or max_threads())
+        h = add(x, self.wo.gemv(a))
+        if self.gate is None:
+            return h
+        n2 = rmsnorm(h, self.norm2, self.eps)
+        hidden = swiglu_act(self.gate.gemv(n2), self.up.gemv(n2))
+        return add(h, self.down.gemv(hidden))
+
+
+class OracleQ8Decoder:
+    """Network#run with use_kv_cache (src/shainet/basic/network_run.cr:185-264): embedding gather,
+    blocks, final norm, Q8_0 lm_head on the last row, bias, and Sampler.greedy."""
+
+    def __init__(self, embedding, blocks, final_norm, lm_head: OracleQ8, lm_bias, eps):
+        self.embedding, self.blocks = _f32(embedding), blocks
+        self.final_norm = None if final_norm is None else _f32(final_norm)
+        self.lm_head, self.eps = lm_head, eps
+        self.lm_bias = None if lm_bias is None else _f32(lm_bias)
+
+    def run(self, ids):
+        x = self.embedding[np.asarray(ids, np.int64)]
+        for b in self.blocks:
+            x = b.forward_cached(x)
+        last = x[-1:]
+        if self.final_norm is not None:
+            last = rmsnorm(last, self.final_norm, self.eps)
+        logits = self.lm_head.gemv(last)[0]
+        if self.lm_bias is not None:
+            lib().oracle_add_bias_row(_fp(logits), _fp(self.lm_bias), logits.size)
+        return logits, greedy(logits)
+
+    def generate(self, prompt, steps):
+        toks, margins = [], []
+        logits, tok = self.run(prompt)
+        for i in range(steps):
+            top = np.sort(logits)[-2:]
+            margins.append(float(top[1] - top[0]))
+            toks.append(tok)
+            if i + 1 < steps:
+                logits, tok = self.run([tok])
+        return toks, margins

@@ -460,6 +460,103 @@ void oracle_add(const float* a, const float* b, size_t n, float* out) {
     for (size_t i = 0; i < n; ++i) out[i] = (float)((double)a[i] + (double)b[i]);
 }
 
+// ---------------------------------------------------------------------------
+// Q8_0 weights (the projections of a quantised model) and the host steps around them.
+// ---------------------------------------------------------------------------
+
+// QuantizedCudaMatrix.from_simple (src/shainet/math/quantized_cuda_matrix.cr:74-115):
+// w is the host fp32 weight [K, N] (row-major, element [r, c] at r*N + c); q comes out
+// output-major [N, K], scales [N, blocks] with blocks = ceil(K / 32).  Float32#round in
+// Crystal rounds half to even, as nearbyintf does in the default rounding mode.
+void oracle_q8_quantize(const float* w, int K, int N, signed char* q, float* scales) {
+    const int BLOCK = 32;
+    const int blocks = (K + BLOCK - 1) / BLOCK;
+    for (int col = 0; col < N; ++col) {
+        for (int b = 0; b < blocks; ++b) {
+            int base = b * BLOCK;
+            int lim = std::min(base + BLOCK, K);
+            float max_abs = 0.0f;
+            for (int kk = base; kk < lim; ++kk) {
+                float v = std::fabs(w[(size_t)kk * N + col]);
+                if (v > max_abs) max_abs = v;
+            }
+            float scale = max_abs > 0.0f ? (max_abs / 127.0f) : 1.0f;
+            float inv = 1.0f / scale;
+            scales[(size_t)col * blocks + b] = scale;
+            size_t row_base = (size_t)col * K;
+            for (int kk = base; kk < lim; ++kk) {
+                float qv = nearbyintf(w[(size_t)kk * N + col] * inv);
+                if (qv > 127.0f) qv = 127.0f;
+                if (qv < -127.0f) qv = -127.0f;
+                q[row_base + kk] = (signed char)qv;
+            }
+        }
+    }
+}
+
+// gemm_q8_f32_kernel (src/shainet/native/cuda_kernels.cu:581-614) with its reduction
+// order: 256 threads, thread t accumulates k = t, t+256, ... in ascending order as
+// partial += (float)q * x * scale, then a shared-memory tree folds stride 128, 64, ... 1.
+// `fused` = 1 evaluates the accumulation as fma(q*x, scale, partial), which is what the
+// CUDA compiler's default contraction makes of that statement; 0 keeps three roundings.
+void oracle_q8_gemv(const float* x, const signed char* q, const float* scales, float* y, int M, int N, int K,
+                    int fused, int threads) {
+    const int nblocks = (K + 31) / 32;
+    const int NT = 256;
+#ifdef _OPENMP
+    int nt = threads > 0 ? threads : 1;
+#pragma omp parallel for num_threads(nt) schedule(static)
+#endif
+    for (int n = 0; n < N; ++n) {
+        const signed char* qrow = q + (size_t)n * K;
+        const float* srow = scales + (size_t)n * nblocks;
+        float sdata[NT];
+        for (int m = 0; m < M; ++m) {
+            const float* xrow = x + (size_t)m * K;
+            for (int t = 0; t < NT; ++t) sdata[t] = 0.0f;
+            for (int k0 = 0; k0 < K; k0 += NT) {
+                const int lim = std::min(NT, K - k0);
+                for (int t = 0; t < lim; ++t) {
+                    const int k = k0 + t;
+                    const float qx = (float)qrow[k] * xrow[k];
+                    sdata[t] = fused ? fmaf(qx, srow[k >> 5], sdata[t]) : sdata[t] + qx * srow[k >> 5];
+                }
+            }
+            for (int stride = NT >> 1; stride > 0; stride >>= 1)
+                for (int t = 0; t < stride; ++t) sdata[t] += sdata[t + stride];
+            y[(size_t)m * N + n] = sdata[0];
+        }
+    }
+}
+
+// The element loop of SwiGLUFF#forward (src/shainet/transformer/swiglu_ff.cr:83-88): the
+// matrix accessor widens to f64, silu in f64, the store narrows to fp32.
+void oracle_swiglu_act(const float* gate, const float* up, size_t n, float* hidden) {
+    for (size_t i = 0; i < n; ++i) {
+        double g = (double)gate[i];
+        hidden[i] = (float)((g / (1.0 + std::exp(-g))) * (double)up[i]);
+    }
+}
+
+// The host bias loop after lm_head (src/shainet/basic/network_run.cr:222-226).
+void oracle_add_bias_row(float* logits, const float* bias, int n) {
+    for (int j = 0; j < n; ++j) logits[j] = (float)((double)logits[j] + (double)bias[j]);
+}
+
+// Sampler.greedy (src/shainet/text/sampler.cr:38-53).
+int oracle_greedy(const float* logits, int n) {
+    int best_id = 0;
+    float best = -std::numeric_limits<float>::infinity();
+    for (int j = 0; j < n; ++j) {
+        float v = logits[j];
+        if (std::isfinite(v) && v > best) {
+            best = v;
+            best_id = j;
+        }
+    }
+    return best_id;
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -62,6 +62,21 @@ SIGNATURES = {
     "shainet_attn_comm_data_ptr": (C.c_int, [_P, C.POINTER(_P)]),
     "shainet_attn_forward_batched_dev": (C.c_int, [_P, C.POINTER(_P), C.c_int, _P, _P, _P, _P, C.c_float,
                                                    C.c_uint, _P]),
+    "shainet_attn_q8_create": (C.c_int, [_P, C.POINTER(_P), _F, C.c_int, C.c_int]),
+    "shainet_attn_q8_create_raw": (C.c_int, [_P, C.POINTER(_P), _P, _F, C.c_int, C.c_int]),
+    "shainet_attn_q8_wrap": (C.c_int, [_P, C.POINTER(_P), _P, _P, C.c_int, C.c_int]),
+    "shainet_attn_q8_destroy": (C.c_int, [_P]),
+    "shainet_attn_q8_export": (C.c_int, [_P, _P, _F]),
+    "shainet_attn_q8_gemv_dev": (C.c_int, [_P, _P, _P, _P, C.c_int, _P]),
+    "gemm_q8_f32": (None, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int]),
+    "shainet_attn_block_create": (C.c_int, [_P, C.POINTER(_P), _P, C.c_int, _F, _P, _P, _P, _P, _F, _P, _P, _P, C.c_double]),
+    "shainet_attn_block_destroy": (C.c_int, [_P]),
+    "shainet_attn_block_forward_dev": (C.c_int, [_P, _P, _P, _P, C.c_int, _P]),
+    "shainet_attn_block_forward_host": (C.c_int, [_P, _P, _F, _F, C.c_int]),
+    "shainet_attn_decoder_create": (C.c_int, [_P, C.POINTER(_P), C.POINTER(_P), C.c_int, _F, C.c_int, _F, _P, _F, C.c_double]),
+    "shainet_attn_decoder_destroy": (C.c_int, [_P]),
+    "shainet_attn_decoder_run": (C.c_int, [_P, _P, C.POINTER(C.c_int32), C.c_int, _F, C.POINTER(C.c_int32)]),
+    "shainet_attn_decoder_generate": (C.c_int, [_P, _P, C.POINTER(C.c_int32), C.c_int, C.c_int, C.POINTER(C.c_int32)]),
     "shainet_attn_decode_noalloc": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, _P]),
     "kv_cache_append_f32": (None, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "attention_kv_f32": (None, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

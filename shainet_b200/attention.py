@@ -281,3 +281,129 @@ def forward_batched_dev(ctx: AttnContext, caches, q_ptr: int, k_ptr: int, v_ptr:
     arr = (C.c_void_p * len(caches))(*[c.h for c in caches])
     check(ctx.L.shainet_attn_forward_batched_dev(ctx.h, arr, len(caches), q_ptr, k_ptr, v_ptr, out_ptr, scale, flags,
                                                  _stream_arg(stream)))
+
+
+class Q8Weight:
+    """The reference's ``QuantizedCudaMatrix`` (src/shainet/math/quantized_cuda_matrix.cr): a
+    weight [K, N] held on the device as Q8_0.  ``from_simple`` quantises an fp32 matrix,
+    ``from_quantized`` uploads int8 values [N, K] and scales [N, ceil(K/32)]."""
+
+    def __init__(self, ctx: AttnContext, handle, K: int, N: int):
+        self.ctx, self.h, self.K, self.N = ctx, handle, K, N
+
+    @classmethod
+    def from_simple(cls, ctx: AttnContext, w):
+        w = _f32(w)
+        h = C.c_void_p()
+        check(ctx.L.shainet_attn_q8_create(ctx.h, C.byref(h), _fp(w), w.shape[0], w.shape[1]))
+        return cls(ctx, h, w.shape[0], w.shape[1])
+
+    @classmethod
+    def from_quantized(cls, ctx: AttnContext, q, scales):
+        q = np.ascontiguousarray(q, np.int8)
+        scales = _f32(scales)
+        N, K = q.shape
+        h = C.c_void_p()
+        check(ctx.L.shainet_attn_q8_create_raw(ctx.h, C.byref(h), q.ctypes.data_as(C.c_void_p), _fp(scales), K, N))
+        return cls(ctx, h, K, N)
+
+    @classmethod
+    def wrap(cls, ctx: AttnContext, q_ptr: int, scales_ptr: int, K: int, N: int):
+        """Adopt device arrays the caller owns (int8 [N, K], fp32 [N, ceil(K/32)]) without copying."""
+        h = C.c_void_p()
+        check(ctx.L.shainet_attn_q8_wrap(ctx.h, C.byref(h), q_ptr, scales_ptr, K, N))
+        return cls(ctx, h, K, N)
+
+    def export(self):
+        q = np.empty((self.N, self.K), np.int8)
+        s = np.empty((self.N, (self.K + 31) // 32), np.float32)
+        check(self.ctx.L.shainet_attn_q8_export(self.h, q.ctypes.data_as(C.c_void_p), _fp(s)))
+        return q, s
+
+    def gemv_dev(self, x_ptr: int, y_ptr: int, rows: int, stream=None):
+        """``gemv_into``: y[rows, N] = x[rows, K] . dequant(W), device pointers."""
+        check(self.ctx.L.shainet_attn_q8_gemv_dev(self.ctx.h, self.h, x_ptr, y_ptr, rows, _stream_arg(stream)))
+
+    def close(self):
+        if getattr(self, "h", None):
+            check(self.ctx.L.shainet_attn_q8_destroy(self.h))
+            self.h = None
+
+
+class LlamaBlock:
+    """``LlamaBlock`` with every step of ``forward_cached`` on the device
+    (src/shainet/transformer/llama_block.cr:189-196): the attention state is a
+    ``LlamaAttention``, the projections and the FFN are ``Q8Weight`` objects."""
+
+    def __init__(self, ctx: AttnContext, attn: LlamaAttention, d_model: int, eps: float, norm1, wq, wk, wv, wo,
+                 norm2=None, gate=None, up=None, down=None):
+        self.ctx, self.attn, self.d_model = ctx, attn, d_model
+        self._keep = (wq, wk, wv, wo, gate, up, down)
+        n1, n1p = _opt(norm1)
+        n2, n2p = _opt(norm2)
+        hp = lambda w: None if w is None else w.h
+        h = C.c_void_p()
+        check(ctx.L.shainet_attn_block_create(ctx.h, C.byref(h), attn.cache.h, d_model, n1p, wq.h, wk.h, wv.h, wo.h, n2p,
+                                              hp(gate), hp(up), hp(down), eps))
+        self.h = h
+
+    def forward_cached(self, x) -> np.ndarray:
+        """Host rows in, host rows out: one copy each way."""
+        x = _f32(x)
+        out = np.empty_like(x)
+        check(self.ctx.L.shainet_attn_block_forward_host(self.ctx.h, self.h, _fp(x), _fp(out), x.shape[0]))
+        return out
+
+    def forward_cached_dev(self, x_ptr: int, out_ptr: int, new_tokens: int, stream=None):
+        check(self.ctx.L.shainet_attn_block_forward_dev(self.ctx.h, self.h, x_ptr, out_ptr, new_tokens, _stream_arg(stream)))
+
+    def clear_cache(self):
+        self.attn.clear_cache()
+
+    def close(self):
+        if getattr(self, "h", None):
+            check(self.ctx.L.shainet_attn_block_destroy(self.h))
+            self.h = None
+
+
+class Decoder:
+    """The token loop of ``Network#run`` with ``use_kv_cache`` (src/shainet/basic/network_run.cr:185-264,
+    294-315) plus ``Sampler.greedy``, resident on the device."""
+
+    def __init__(self, ctx: AttnContext, blocks, embedding, final_norm, lm_head: Q8Weight, lm_bias=None, eps: float = 1e-6):
+        self.ctx, self.blocks, self.lm_head = ctx, list(blocks), lm_head
+        emb = _f32(embedding)
+        self.vocab, self.d_model = emb.shape
+        fn, fnp = _opt(final_norm)
+        lb, lbp = _opt(lm_bias)
+        arr = (C.c_void_p * len(self.blocks))(*[b.h for b in self.blocks])
+        h = C.c_void_p()
+        check(ctx.L.shainet_attn_decoder_create(ctx.h, C.byref(h), arr, len(self.blocks), _fp(emb), self.vocab, fnp, lm_head.h,
+                                                lbp, eps))
+        self.h = h
+
+    def run(self, ids, want_logits: bool = True):
+        """``run(Array(Int32))``: (logits of the last row or None, greedy token)."""
+        ids = np.ascontiguousarray(ids, np.int32)
+        logits = np.empty(self.vocab, np.float32) if want_logits else None
+        tok = C.c_int32(-1)
+        check(self.ctx.L.shainet_attn_decoder_run(self.ctx.h, self.h, ids.ctypes.data_as(C.POINTER(C.c_int32)), ids.size,
+                                                  _fp(logits) if want_logits else None, C.byref(tok)))
+        return logits, tok.value
+
+    def generate(self, prompt, steps: int) -> np.ndarray:
+        """Greedy tokens of `steps` steps after the prompt; nothing visits the host in between."""
+        ids = np.ascontiguousarray(prompt, np.int32)
+        out = np.empty(steps, np.int32)
+        check(self.ctx.L.shainet_attn_decoder_generate(self.ctx.h, self.h, ids.ctypes.data_as(C.POINTER(C.c_int32)), ids.size,
+                                                       steps, out.ctypes.data_as(C.POINTER(C.c_int32))))
+        return out
+
+    def clear_cache(self):
+        for b in self.blocks:
+            b.clear_cache()
+
+    def close(self):
+        if getattr(self, "h", None):
+            check(self.ctx.L.shainet_attn_decoder_destroy(self.h))
+            self.h = None

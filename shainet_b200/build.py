@@ -37,13 +37,16 @@ def up_to_date() -> bool:
     return all(os.path.getmtime(d) <= t for d in _deps())
 
 
-def compile_library(out_path: str, obj_dir: str, srcs: list[str], verbose: bool = False) -> str:
+def compile_library(out_path: str, obj_dir: str, srcs: list[str], verbose: bool = False,
+                    include_dirs: list[str] | None = None) -> str:
     """nvcc every source for sm_100a (in parallel) and link them into one shared library."""
     os.makedirs(os.path.dirname(out_path), exist_ok=True)
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     common = [nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-diag-suppress", "177", "-Xcompiler", "-fPIC",
-              "-I", INCLUDE, "-I", CSRC]
+              "-I", INCLUDE]
+    for d in include_dirs or []:
+        common += ["-I", d]
     if verbose:
         common += ["-Xptxas", "-v"]
     procs, objs = [], []

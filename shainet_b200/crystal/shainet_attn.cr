@@ -82,6 +82,35 @@ module SHAInet
                                            stream : Void*) : Int32
     fun comm_data_ptr = shainet_attn_comm_data_ptr(ctx : Ctx, data_dev : Float32**) : Int32
 
+    # Q8_0 weights, the whole block and the token loop on the device
+    type Q8 = Void*
+    type Block = Void*
+    type Decoder = Void*
+    fun q8_create = shainet_attn_q8_create(ctx : Ctx, out_w : Q8*, w_host : Float32*, k : Int32, n : Int32) : Int32
+    fun q8_create_raw = shainet_attn_q8_create_raw(ctx : Ctx, out_w : Q8*, q_host : Int8*, scales_host : Float32*,
+                                                   k : Int32, n : Int32) : Int32
+    fun q8_wrap = shainet_attn_q8_wrap(ctx : Ctx, out_w : Q8*, q_dev : Int8*, scales_dev : Float32*, k : Int32, n : Int32) : Int32
+    fun q8_destroy = shainet_attn_q8_destroy(w : Q8) : Int32
+    fun q8_export = shainet_attn_q8_export(w : Q8, q_host : Int8*, scales_host : Float32*) : Int32
+    fun q8_gemv_dev = shainet_attn_q8_gemv_dev(ctx : Ctx, w : Q8, x_dev : Float32*, y_dev : Float32*, m : Int32,
+                                               stream : Void*) : Int32
+    fun block_create = shainet_attn_block_create(ctx : Ctx, out_block : Block*, kv : Kv, d_model : Int32, norm1 : Float32*,
+                                                 wq : Q8, wk : Q8, wv : Q8, wo : Q8, norm2 : Float32*, gate : Q8, up : Q8,
+                                                 down : Q8, eps : Float64) : Int32
+    fun block_destroy = shainet_attn_block_destroy(block : Block) : Int32
+    fun block_forward_dev = shainet_attn_block_forward_dev(ctx : Ctx, block : Block, x_dev : Float32*, out_dev : Float32*,
+                                                           new_tokens : Int32, stream : Void*) : Int32
+    fun block_forward_host = shainet_attn_block_forward_host(ctx : Ctx, block : Block, x : Float32*, out_ptr : Float32*,
+                                                             new_tokens : Int32) : Int32
+    fun decoder_create = shainet_attn_decoder_create(ctx : Ctx, out_dec : Decoder*, blocks : Block*, n_layers : Int32,
+                                                     embedding : Float32*, vocab : Int32, final_norm : Float32*, lm_head : Q8,
+                                                     lm_bias : Float32*, eps : Float64) : Int32
+    fun decoder_destroy = shainet_attn_decoder_destroy(dec : Decoder) : Int32
+    fun decoder_run = shainet_attn_decoder_run(ctx : Ctx, dec : Decoder, token_ids : Int32*, n_tokens : Int32,
+                                               logits : Float32*, next_token : Int32*) : Int32
+    fun decoder_generate = shainet_attn_decoder_generate(ctx : Ctx, dec : Decoder, prompt_ids : Int32*, n_prompt : Int32,
+                                                         steps : Int32, tokens : Int32*) : Int32
+
     # one decode token with the split partials in a fixed array inside the library (no allocation)
     fun decode_noalloc = shainet_attn_decode_noalloc(q : Float32*, k_cache : Float32*, v_cache : Float32*, out_ptr : Float32*,
                                                      start_pos : Int32, num_heads : Int32, heads_per_kv : Int32,

@@ -12,14 +12,21 @@
 #include <utility>
 #include <vector>
 
-#include "../../include/shainet_attn.h"
-#include "kernels.h"
+#include "host_state.h"
 
 using namespace shainet;
 
 namespace {
 
 thread_local std::string g_last_error;
+
+constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
+constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
+constexpr int TENSOR_MIN_T = 64;      // rows per call from which the tensor-core prefill kernel takes over
+
+}  // namespace
+
+namespace shainet {
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -37,109 +44,9 @@ int fail_cuda(cudaError_t e, const char* what) {
     return fail(code, "%s: %s", what, cudaGetErrorString(e));
 }
 
-#define CU(call)                                              \
-    do {                                                      \
-        cudaError_t e__ = (call);                             \
-        if (e__ != cudaSuccess) return fail_cuda(e__, #call); \
-    } while (0)
-
-constexpr int SEQ_RING = 8;           // in-flight descriptor uploads of batched decode
-constexpr size_t SMALL_COPY = 1 << 20;  // host entry: stage through pinned memory below this
-constexpr int SPLITK_MAX_T = 16;      // rows per call the decode kernel takes before the generic one
-constexpr int TENSOR_MIN_T = 64;      // rows per call from which the tensor-core prefill kernel takes over
-
-struct DevBuf {
-    float* p = nullptr;
-    size_t cap = 0;  // floats
-};
-
-}  // namespace
-
-struct shainet_attn_ctx {
-    int device = 0;
-    int sm_count = 148;
-    cudaStream_t stream = nullptr;
-    DevBuf q_rot, part, part_words, dev_in, dev_out;   // part_words: {value, epoch} partials of single-sequence decode
-    float* pin_in = nullptr;
-    size_t pin_in_cap = 0;
-    float* pin_out = nullptr;
-    size_t pin_out_cap = 0;
-    AttnStatus* status_host = nullptr;  // mapped pinned; kernels write through status_dev
-    AttnStatus* status_dev = nullptr;
-    SeqDesc* seq_host = nullptr;        // [SEQ_RING][seq_cap] pinned
-    SeqDesc* seq_dev = nullptr;         // [SEQ_RING][seq_cap]
-    int seq_cap = 0;
-    int seq_slot = 0;
-    cudaEvent_t seq_ev[SEQ_RING] = {};
-    int live_caches = 0;
-    unsigned* tickets = nullptr;        // split-merge tickets of the fused decode kernel, zero between launches
-    size_t tickets_cap = 0;
-    unsigned epoch = 0;                 // tag of the newest word-merged decode launch
-    bool last_fused = false;            // the newest launch on this context was a fused decode kernel
-    bool rows_rewound = false;          // a cache was truncated or reset since: the next launch may rewrite rows the
-                                        // previous one still reads, so it must not run ahead of it (F_INPUTS_READY is ignored once)
-    unsigned long long peer_wait_ns = WAIT_LIMIT_NS;   // limit of the waits for other ranks' exchange words
-    float* lse_out = nullptr;           // caller-owned device buffer for log-sum-exp values (nullable)
-    // exchange buffer shared with the other ranks of the box (IPC): comm_data_floats
-    // floats, then as many 8-byte {value, epoch} words
-    unsigned char* comm_base = nullptr;
-    size_t comm_data_floats = 0;
-    int comm_world = 0, comm_rank = 0;
-    unsigned char* comm_peer[MAX_PEERS] = {};
-    bool gather_armed = false;          // the next fused decode call delivers to the peers
-    long long gather_out_off = 0, gather_lse_off = -1;
-    unsigned gather_epoch = 0;
-    bool timing = false;
-    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;   // recorded, not yet read
-    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool;  // reusable pairs
-};
-
-struct shainet_attn_kv {
-    shainet_attn_ctx* ctx = nullptr;
-    HeadShape hs{};
-    float* k = nullptr;
-    float* v = nullptr;
-    int cap = 0;
-    int len = 0;
-    float* inv_freq = nullptr;  // device, head_dim/2
-    float* q_norm = nullptr;    // device, nullable
-    float* k_norm = nullptr;
-    float* b_q = nullptr;
-    float* b_k = nullptr;
-    float* b_v = nullptr;
-    double eps = 1e-6;
-};
+}  // namespace shainet
 
 namespace {
-
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
-    }
-    ~DeviceGuard() {
-        int cur = -1;
-        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
-    }
-};
-
-int grow(DevBuf& b, size_t floats, cudaStream_t s) {
-    if (b.cap >= floats && b.p) return SHAINET_ATTN_OK;
-    const size_t old_cap = b.cap;
-    if (b.p) {
-        CU(cudaStreamSynchronize(s));
-        CU(cudaFree(b.p));
-        b.p = nullptr;
-        b.cap = 0;
-    }
-    size_t want = std::max(floats, old_cap * 2);
-    want = (want + 63) & ~(size_t)63;
-    CU(cudaMalloc(&b.p, want * sizeof(float)));
-    b.cap = want;
-    return SHAINET_ATTN_OK;
-}
 
 int grow_pinned(float*& p, size_t& cap, size_t floats) {
     if (cap >= floats && p) return SHAINET_ATTN_OK;
@@ -151,19 +58,6 @@ int grow_pinned(float*& p, size_t& cap, size_t floats) {
     cap = want;
     return SHAINET_ATTN_OK;
 }
-
-int upload_vec(float*& dst, const float* host, size_t n) {
-    if (!host) {
-        if (dst) CU(cudaFree(dst));
-        dst = nullptr;
-        return SHAINET_ATTN_OK;
-    }
-    if (!dst) CU(cudaMalloc(&dst, n * sizeof(float)));
-    CU(cudaMemcpy(dst, host, n * sizeof(float), cudaMemcpyHostToDevice));
-    return SHAINET_ATTN_OK;
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Capacity policy of ensure_gpu_cache! (llama_block.cr:500): max(256, need, 2*old),
 // but the live rows move device-to-device instead of being re-uploaded.
@@ -489,6 +383,39 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     return SHAINET_ATTN_OK;
 }
 
+}  // namespace
+
+namespace shainet {
+
+int grow(DevBuf& b, size_t floats, cudaStream_t s) {
+    if (b.cap >= floats && b.p) return SHAINET_ATTN_OK;
+    const size_t old_cap = b.cap;
+    if (b.p) {
+        CU(cudaStreamSynchronize(s));
+        CU(cudaFree(b.p));
+        b.p = nullptr;
+        b.cap = 0;
+    }
+    size_t want = std::max(floats, old_cap * 2);
+    want = (want + 63) & ~(size_t)63;
+    CU(cudaMalloc(&b.p, want * sizeof(float)));
+    b.cap = want;
+    return SHAINET_ATTN_OK;
+}
+
+int upload_vec(float*& dst, const float* host, size_t n) {
+    if (!host) {
+        if (dst) CU(cudaFree(dst));
+        dst = nullptr;
+        return SHAINET_ATTN_OK;
+    }
+    if (!dst) CU(cudaMalloc(&dst, n * sizeof(float)));
+    CU(cudaMemcpy(dst, host, n * sizeof(float), cudaMemcpyHostToDevice));
+    return SHAINET_ATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 int forward_device(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, const float* k_new, const float* v_new,
                    float* out, int T, float scale, unsigned flags, cudaStream_t s) {
     const int cap_before = kv->cap;
@@ -505,9 +432,6 @@ int forward_device(shainet_attn_ctx* ctx, shainet_attn_kv* kv, const float* q, c
     return SHAINET_ATTN_OK;
 }
 
-}  // namespace
-
-namespace shainet {
 void set_last_error_message(const char* msg) { g_last_error = msg ? msg : ""; }
 }  // namespace shainet
 

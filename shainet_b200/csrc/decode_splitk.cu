@@ -47,6 +47,7 @@ namespace {
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int SK_MAX_STAGES = 32;
+constexpr bool LAZY_RESCALE = false;
 
 // Packed fp32 pairs: sm_100 executes fma.rn.f32x2 on a 64-bit register pair,
 // two fused multiply-adds per issued instruction.
@@ -256,12 +257,15 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
         st.m = m_new;
         ps[lane] = pack2(p, p);  // index = row_in_batch * G + head
         if (lane < G) as[lane] = pack2(alpha, alpha);
+        const bool rescale = !LAZY_RESCALE || __any_sync(FULL, alpha != 1.0f);
         __syncwarp();
+        if (rescale) {
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const f32x2 al = as[g];
-            st.o[g][0] = fmul2(st.o[g][0], al);
-            st.o[g][1] = fmul2(st.o[g][1], al);
+            for (int g = 0; g < G; ++g) {
+                const f32x2 al = as[g];
+                st.o[g][0] = fmul2(st.o[g][0], al);
+                st.o[g][1] = fmul2(st.o[g][1], al);
+            }
         }
 #pragma unroll
         for (int rr = 0; rr < C::BR; rr += C::RPI) {

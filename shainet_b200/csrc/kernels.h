@@ -159,6 +159,35 @@ cudaError_t launch_gather_wait(const unsigned long long* words, float* data, lon
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
                                unsigned long long seed, cudaStream_t s);
 
+// y[M, N] = x[M, K] . dequant(q[N, K], scales[N, ceil(K/32)]) with optional fused pieces:
+// gamma != null: x is RMS-normalised first (f64 sum and scaling, weight gamma[K], eps);
+// q2 != null: SwiGLU, y[M, N] = silu(x . W) * (x . W2) with silu in f64 (q2/scales2 shaped like q/scales);
+// bias != null: + bias[N]; residual != null: residual[M, N] + result; argmax != null: every
+// row's word receives max over its finite outputs of (order-preserving key << 32 | ~index)
+// by atomicMax (the words must be zero before the launch).
+struct Q8GemvArgs {
+    const float* x;
+    const signed char* q;
+    const float* scales;
+    const signed char* q2;
+    const float* scales2;
+    float* y;
+    const float* residual;
+    const float* bias;
+    const float* gamma;
+    double eps;
+    unsigned long long* argmax;
+    int M, N, K;
+};
+bool q8_fast_path(int K);
+cudaError_t launch_q8_gemv(const Q8GemvArgs& a, int sm_count, cudaStream_t s);
+// x[t] = table[ids[t]] for `rows` tokens; also zeroes n_words arg-max words.
+cudaError_t launch_embed_rows(const int* ids_dev, const float* table, float* x, int rows, int d_model, int vocab,
+                              unsigned long long* argmax_words, int n_words, cudaStream_t s);
+// tokens[m] = index held by arg-max word m; the last one also goes to *next_id and history[history_pos] when given.
+cudaError_t launch_argmax_decode(const unsigned long long* words, int* tokens, int n, int* next_id, int* history,
+                                 int history_pos, cudaStream_t s);
+
 // Sets the calling thread's message for shainet_attn_last_error().
 void set_last_error_message(const char* msg);
 

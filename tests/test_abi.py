@@ -19,7 +19,7 @@ def lib():
 def _declared_symbols():
     text = open(os.path.join(ROOT, "include", "shainet_attn.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"\b(shainet_attn_\w+|kv_cache_append_f32|attention_kv_f32)\s*\(", text)
+    names = re.findall(r"\b(shainet_attn_\w+|kv_cache_append_f32|attention_kv_f32|gemm_q8_f32)\s*\(", text)
     return sorted(set(names))
 
 

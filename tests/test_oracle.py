@@ -172,3 +172,48 @@ def test_bad_head_split_rejected():
     # llama_block.cr:80
     with pytest.raises(ValueError):
         O.OracleAttention(6, 4, 8)
+
+
+# ---- Q8_0 weights and the host steps around the projections ----
+
+def test_q8_quantiser_known_answers():
+    """quantized_cuda_matrix.cr:84-110 on cases worked by hand: scale = max|w|/127 per block of 32
+    inputs of one output, the extreme maps to +-127, an all-zero block gets scale 1, a ragged last
+    block (K = 40) is its own block, halves round to even."""
+    K, N = 40, 2
+    w = np.zeros((K, N), np.float32)
+    w[:32, 0] = np.linspace(-1.27, 1.27, 32, dtype=np.float32)      # block 0 of output 0: max 1.27 -> scale 0.01
+    w[32:, 0] = 0.0                                                 # ragged block 1 of output 0: all zero
+    w[0, 1], w[1, 1], w[2, 1] = 127.0, 0.5, 1.5                     # output 1, scale 1: ties 0.5 -> 0, 1.5 -> 2
+    w[39, 1] = -3.0                                                 # ragged block of output 1: scale 3/127
+    W = O.OracleQ8(w)
+    assert W.q.shape == (2, 40) and W.scales.shape == (2, 2)
+    assert W.scales[0, 0] == np.float32(np.float32(1.27) / np.float32(127.0)) and W.scales[0, 1] == 1.0
+    assert W.q[0, 0] == -127 and W.q[0, 31] == 127 and not W.q[0, 32:].any()
+    assert W.scales[1, 0] == 1.0 and list(W.q[1, :3]) == [127, 0, 2]
+    assert W.scales[1, 1] == np.float32(np.float32(3.0) / np.float32(127.0)) and W.q[1, 39] == -127
+    assert np.abs(W.dequantised() - w).max() <= 0.5 * W.scales.max() + 1e-7
+
+
+def test_q8_gemv_follows_the_dequantised_product():
+    rng = np.random.default_rng(8)
+    K, N, M = 2048, 96, 3
+    W = O.OracleQ8((0.02 * rng.standard_normal((K, N))).astype(np.float32))
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    truth = x.astype(np.float64) @ W.dequantised().astype(np.float64)
+    for fused in (0, 1):
+        y = W.gemv(x, fused=fused, threads=2)
+        assert np.abs(y - truth).max() <= 2e-6 * np.abs(truth).max()
+    assert np.abs(W.gemv(x, fused=0) - W.gemv(x, fused=1)).max() <= 1e-6 * np.abs(truth).max()
+
+
+def test_swiglu_activation_bias_and_greedy():
+    rng = np.random.default_rng(9)
+    g = rng.standard_normal(500).astype(np.float32) * 4
+    u = rng.standard_normal(500).astype(np.float32)
+    ref = ((g.astype(np.float64) / (1.0 + np.exp(-g.astype(np.float64)))) * u.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(O.swiglu_act(g, u), ref)
+    # Sampler.greedy (sampler.cr:38-53): first index of the largest finite value; 0 if there is none
+    assert O.greedy(np.array([1.0, 5.0, 5.0, np.inf, np.nan, -2.0], np.float32)) == 1
+    assert O.greedy(np.array([np.nan, np.inf, -np.inf], np.float32)) == 0
+    assert O.greedy(np.array([-3.0, -1.0, -2.0], np.float32)) == 1
