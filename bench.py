@@ -238,46 +238,58 @@ def prefill_block(S, ctx, dev, stream_obj):
 
 
 BATCHED_WL = dict(name="cfg4: Qwen3-8B attention, 64 sequences in lock step, context lengths log-uniform in [1k, 32k], fp32 KV cache, decode",
-                  H=32, KV=8, hd=128, theta=1e6, batch=64, lo=1024, hi=32768, layers_total=36, layers_timed=2, steps=16)
+                  H=32, KV=8, hd=128, theta=1e6, batch=64, lo=1024, hi=32768, layers_total=36, steps=16)
 
 
-def batched_block(S, ctx, dev, stream_obj):
-    """Batched ragged decode GB/s on the cfg4 shape: one launch per layer serves all 64
-    sequences (norm/RoPE/append and attention fused, two-level ticket merge).  Two of the
-    36 layers are resident (4.9 GB each); the per-layer time scales to a step."""
+def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None):
+    """Batched ragged decode on the cfg4 shape: one launch per layer serves all 64 sequences (norm/RoPE/
+    append and attention fused, two-level ticket merge).  Over several ranks the kv heads (and their
+    query heads) are divided, every rank holds its heads of all 64 sequences, and the head outputs
+    [64, q_dim / ranks] of a layer are all-gathered (NCCL, 1 MB per layer: a real exchange step, not
+    latency-class) before o_proj would read them.  2 x ranks of the 36 layers are resident per rank
+    (4.9 GB per layer over all ranks); the per-layer time scales to a step."""
     import torch
     w = BATCHED_WL
     H, KV, hd, B = w["H"], w["KV"], w["hd"], w["batch"]
+    if KV % world:
+        return None
+    KVl, Hl = KV // world, H // world
+    layers_timed = 2 * world
     rng = np.random.default_rng(4001)
     lens = np.exp(rng.uniform(np.log(w["lo"]), np.log(w["hi"]), B)).astype(np.int64)
     steps, warm = w["steps"], 3
     qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
     kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
     layers = []
-    for l in range(w["layers_timed"]):
+    for l in range(layers_timed):
         caches = []
         for b in range(B):
-            a = S.LlamaAttention(ctx, H, KV, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn,
+            a = S.LlamaAttention(ctx, Hl, KVl, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn,
                                  initial_capacity=int(lens[b]) + steps + warm + 8)
-            a.cache.fill_normal(int(lens[b]), 4002 + 1000 * l + b)
+            a.cache.fill_normal(int(lens[b]), 4002 + 100000 * rank + 1000 * l + b)
             caches.append(a)
         layers.append(caches)
     g = torch.Generator(device=dev)
-    g.manual_seed(4003)
-    q = torch.randn(B, H * hd, device=dev, generator=g)
-    k = torch.randn(B, KV * hd, device=dev, generator=g)
-    v = torch.randn(B, KV * hd, device=dev, generator=g)
-    out = torch.empty_like(q)
+    g.manual_seed(4003 + rank)
+    q = torch.randn(B, Hl * hd, device=dev, generator=g)
+    k = torch.randn(B, KVl * hd, device=dev, generator=g)
+    v = torch.randn(B, KVl * hd, device=dev, generator=g)
+    out = torch.empty(layers_timed, B, Hl * hd, device=dev)
+    gathered = torch.empty(layers_timed, world, B, Hl * hd, device=dev) if world > 1 else None
     scale = layers[0][0].scale
     handles = [[a.cache for a in caches] for caches in layers]
 
     def step():
-        for hs in handles:
-            S.forward_batched_dev(ctx, hs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), scale,
+        for l, hs in enumerate(handles):
+            S.forward_batched_dev(ctx, hs, q.data_ptr(), k.data_ptr(), v.data_ptr(), out[l].data_ptr(), scale,
                                   stream_obj.cuda_stream)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[l].view(-1), out[l].view(-1))
     for _ in range(warm):
         step()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -285,18 +297,79 @@ def batched_block(S, ctx, dev, stream_obj):
     e1.record()
     torch.cuda.synchronize()
     ctx.sync()
-    ms_layer = e0.elapsed_time(e1) / (steps * len(layers))
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_layer = ms / (steps * len(layers))
     mean_len = float(lens.sum()) + B * (warm + (steps + 1) / 2.0)
-    bytes_layer = 2.0 * KV * mean_len * hd * 4 + B * (2 * KV + 2 * H) * hd * 4
+    bytes_layer_rank = 2.0 * KVl * mean_len * hd * 4 + B * (2 * KVl + 2 * Hl) * hd * 4
     for caches in layers:
         for a in caches:
             a.close()
+    check = batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist)
     peak, kind = measured_peak()
-    gbs = bytes_layer / (ms_layer / 1e3) / 1e9
+    gbs = bytes_layer_rank / (ms_layer / 1e3) / 1e9
     return {"workload": w["name"], "sum_of_context_lengths": int(lens.sum()), "ms_per_layer": ms_layer,
             "tokens_per_s_36_layers": B / (ms_layer * w["layers_total"] / 1e3), "layers_timed": len(layers), "steps": steps,
+            "sharding": (f"{world} rank(s) x {KVl} kv head(s) of every sequence"
+                         + ("; head outputs all-gathered per layer (NCCL)" if world > 1 else "; no exchange")),
+            "parity_check": check,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel (batched)", "achieved": gbs, "peak": peak,
-                         "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "bytes_per_launch": bytes_layer}}
+                         "peak_kind": kind, "unit": "GB/s per GPU", "frac": gbs / peak, "bytes_per_launch": bytes_layer_rank,
+                         "note": "per GPU; the launch time includes the layer's all-gather when ranks > 1"}}
+
+
+def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist):
+    """One checked lock-step step of the batched (and, over several ranks, kv-head-sharded and gathered)
+    path: 5 short sequences with seeded caches against one CPU oracle per sequence, on rank 0."""
+    import torch
+    H, KV, hd = w["H"], w["KV"], w["hd"]
+    KVl, Hl = KV // world, H // world
+    rng = np.random.default_rng(4400)
+    lens = [1, 40, 257, 600, 1031]
+    B = len(lens)
+    qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    full = [(rng.standard_normal((KV, L, hd), dtype=np.float32), rng.standard_normal((KV, L, hd), dtype=np.float32)) for L in lens]
+    q = rng.standard_normal((B, H * hd)).astype(np.float32)
+    k = rng.standard_normal((B, KV * hd)).astype(np.float32)
+    v = rng.standard_normal((B, KV * hd)).astype(np.float32)
+    kvs = slice(rank * KVl, (rank + 1) * KVl)
+    caches = []
+    for kc, vc in full:
+        a = S.LlamaAttention(ctx, Hl, KVl, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        a.cache.import_(kc[kvs], vc[kvs])
+        a.cache.reserve(kc.shape[1] + 2)
+        caches.append(a)
+    ql = q.reshape(B, H, hd)[:, rank * Hl:(rank + 1) * Hl].reshape(B, -1).copy()
+    kl = k.reshape(B, KV, hd)[:, kvs].reshape(B, -1).copy()
+    vl = v.reshape(B, KV, hd)[:, kvs].reshape(B, -1).copy()
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
+    out = torch.zeros(B, Hl * hd, device=dev)
+    S.forward_batched_dev(ctx, [a.cache for a in caches], tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(),
+                          caches[0].scale, stream_obj.cuda_stream)
+    if world > 1:
+        gathered = torch.zeros(world, B, Hl * hd, device=dev)
+        dist.all_gather_into_tensor(gathered.view(-1), out.view(-1))
+        got = gathered.permute(1, 0, 2).reshape(B, H * hd).cpu().numpy()
+    else:
+        got = out.cpu().numpy()
+    torch.cuda.synchronize()
+    ctx.sync()
+    for a in caches:
+        a.close()
+    if rank != 0:
+        return None
+    from oracle import oracle as O
+    worst = 0.0
+    for b, (kc, vc) in enumerate(full):
+        o = O.OracleAttention(H, KV, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        o.import_cache(kc, vc)
+        ref = o.attend_cached(q[b:b + 1], k[b:b + 1], v[b:b + 1], threads=host_threads())
+        worst = max(worst, float(np.abs(got[b:b + 1].astype(np.float64) - ref).max() / np.abs(ref).max()))
+    return {"max_rel_err": worst, "tol": 1e-5, "ok": bool(worst <= 1e-5), "sequences": B, "ranks": world}
 
 
 def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
@@ -492,6 +565,30 @@ def parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, comm_slot
     if world > 1:
         dist.barrier()
     return res
+
+
+def run_one_block(args):
+    """--only NAME: one of the secondary blocks alone, printed as its own JSON object (profiling and
+    quick measurements; the driver's line is the default run)."""
+    import torch
+    import shainet_b200 as S
+    from shainet_b200 import build
+    build.build()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    ctx = S.AttnContext(0)
+    tstream = torch.cuda.Stream(device=dev)
+    torch.cuda.set_stream(tstream)
+    if args.only == "model":
+        res = model_decode_block(S, ctx, dev, steps=args.steps if args.steps != 256 else 96)
+    elif args.only == "ctx4k":
+        res = short_context_block(S, ctx, dev, tstream)
+    elif args.only == "batched":
+        res = batched_block(S, ctx, dev, tstream)
+    else:
+        res = prefill_block(S, ctx, dev, tstream)
+    ctx.close()
+    print(json.dumps({args.only: res}), flush=True)
 
 
 def run_ours(args, wl, rank, world, local_rank):
@@ -743,7 +840,8 @@ def run_ours(args, wl, rank, world, local_rank):
     prefill = batched = short_ctx = None
     if world == 1 and not args.no_prefill:
         prefill = prefill_block(S, ctx, dev, tstream)
-        batched = batched_block(S, ctx, dev, tstream)
+    if not args.no_prefill:
+        batched = batched_block(S, ctx, dev, tstream, rank, world, dist)
     model = None
     if world == 1 and not args.no_prefill and args.workload != "cfg2":
         short_ctx = short_context_block(S, ctx, dev, tstream)
@@ -820,6 +918,8 @@ def run_ours(args, wl, rank, world, local_rank):
         dist.destroy_process_group()
     if rank == 0 and not parity["ok"]:
         sys.exit(f"parity check failed: max relative error {parity['max_rel_err']:.3e} > {PARITY_TOL}")
+    if rank == 0 and batched is not None and not batched["parity_check"]["ok"]:
+        sys.exit(f"batched parity check failed: max relative error {batched['parity_check']['max_rel_err']:.3e}")
 
 
 def main():
@@ -835,6 +935,8 @@ def main():
                     help="override 'query_heads,kv_heads' (debugging: e.g. 8,1 on 2 ranks runs the sequence-split path)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="several ranks: gather head outputs with torch.distributed instead of the kernel's peer stores")
+    ap.add_argument("--only", default=None, choices=["model", "ctx4k", "batched", "prefill"],
+                    help="run one secondary block alone on one GPU and print its JSON object")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (cfg3 shape) block of the JSON line")
     args = ap.parse_args()
@@ -851,7 +953,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.only:
+        run_one_block(args)
+    elif args.impl == "reference":
         run_reference(args, wl, rank, world)
     else:
         run_ours(args, wl, rank, world, local_rank)

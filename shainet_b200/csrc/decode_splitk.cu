@@ -902,7 +902,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
                 }
 #pragma unroll
                 for (int c = 0; c < 2 * PL; ++c) {
-                    x[n][c] = src[lane + 32 * c];
+                    x[n][c] = __ldcg(src + lane + 32 * c);   // written by the grid ahead while this one was resident: L2 only
                     if (bias) x[n][c] = __fadd_rn(x[n][c], bias[lane + 32 * c]);
                 }
             }

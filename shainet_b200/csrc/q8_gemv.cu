@@ -73,6 +73,12 @@ __device__ __forceinline__ unsigned float_key(float v) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// The activations (x, the residual, token ids, arg-max words) are written by the kernel
+// ahead in the stream while this kernel may already be resident, so they are read with
+// L2-only loads (__ldcg) after the wait, never through the non-coherent path, which may
+// keep a line from before the write.  Weights, scales, norm weights and biases are
+// constants and do take that path.
+//
 // Activation rows into shared memory, optionally RMS-normalised, in the permuted order
 // the main loop reads: element k of a row (chunk = k / 512, r = k % 512) goes to
 // chunk*512 + ((r % 16) / 4)*128 + (r / 16)*4 + r % 4, so lane l's j-th float4 of a
@@ -88,7 +94,7 @@ __device__ __forceinline__ void stage_rows(const Q8GemvArgs& a, int m0, int rows
             // rms_norm.cr:29-31: sq_sum over f64(x)^2, rms = sqrt(sq_sum / cols + eps)
             double sq = 0.0;
             for (int i = threadIdx.x; i < K / 4; i += Q8_THREADS) {
-                const float4 v = live ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 v = live ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
                 sq += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
             }
             sq = warp_sum(sq);
@@ -105,7 +111,7 @@ __device__ __forceinline__ void stage_rows(const Q8GemvArgs& a, int m0, int rows
             // destination float4 d = chunk*128 + j*32 + l  <-  source float4 chunk*128 + l*4 + j
             const int chunk = d >> 7, j = (d >> 5) & 3, l = d & 31;
             const int s = (chunk << 7) + (l << 2) + j;
-            float4 v = live ? __ldg(src + s) : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 v = live ? __ldcg(src + s) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (a.gamma != nullptr) {
                 const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + s);
                 // rms_norm.cr:32: f32((f64 x / rms) * f64 g); the division is done as a product
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_kernel(Q8GemvArgs a) {
                         if (n >= a.N) break;
                         float v = acc[m][c];
                         if (a.bias != nullptr) v = __fadd_rn(v, a.bias[n]);
-                        if (a.residual != nullptr) v = __fadd_rn(a.residual[row + n], v);
+                        if (a.residual != nullptr) v = __fadd_rn(__ldcg(a.residual + row + n), v);
                         a.y[row + n] = v;
                         if (a.argmax != nullptr && isfinite(v)) {
                             const unsigned long long cand = ((unsigned long long)float_key(v) << 32) | (0xffffffffu - (unsigned)n);
@@ -283,7 +289,10 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_generic_kernel(Q8GemvArgs 
     double inv_rms = 1.0;
     if (a.gamma != nullptr) {
         double sq = 0.0;
-        for (int k = threadIdx.x; k < a.K; k += Q8_THREADS) sq += (double)xrow[k] * (double)xrow[k];
+        for (int k = threadIdx.x; k < a.K; k += Q8_THREADS) {
+            const double v = (double)__ldcg(xrow + k);
+            sq += v * v;
+        }
         sq = warp_sum(sq);
         if (lane == 0) red[warp] = sq;
         __syncthreads();
@@ -291,8 +300,10 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_generic_kernel(Q8GemvArgs 
         for (int w = 0; w < Q8_WARPS; ++w) tot += red[w];
         inv_rms = 1.0 / sqrt(tot / (double)a.K + a.eps);
     }
-    for (int k = threadIdx.x; k < a.K; k += Q8_THREADS)
-        q8_xs[k] = a.gamma != nullptr ? (float)(((double)xrow[k] * inv_rms) * (double)a.gamma[k]) : xrow[k];
+    for (int k = threadIdx.x; k < a.K; k += Q8_THREADS) {
+        const float xv = __ldcg(xrow + k);
+        q8_xs[k] = a.gamma != nullptr ? (float)(((double)xv * inv_rms) * (double)a.gamma[k]) : xv;
+    }
     __syncthreads();
     const int kb = (a.K + 31) / 32;
     unsigned long long best = 0ull;
@@ -315,7 +326,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_generic_kernel(Q8GemvArgs 
             } else {
                 float v = acc[0];
                 if (a.bias != nullptr) v = __fadd_rn(v, a.bias[n]);
-                if (a.residual != nullptr) v = __fadd_rn(a.residual[row + n], v);
+                if (a.residual != nullptr) v = __fadd_rn(__ldcg(a.residual + row + n), v);
                 a.y[row + n] = v;
                 if (a.argmax != nullptr && isfinite(v)) {
                     const unsigned long long cand = ((unsigned long long)float_key(v) << 32) | (0xffffffffu - (unsigned)n);
@@ -333,13 +344,13 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_generic_kernel(Q8GemvArgs 
 
 // x[t] = table[ids[t]] (EmbeddingLayer#embed_cpu, text/embedding_layer.cr:129-156) and the
 // reset of the arg-max words the step's lm_head launch will fill.
-__global__ void embed_rows_kernel(const int* __restrict__ ids, const float* __restrict__ table, float* __restrict__ x,
+__global__ void embed_rows_kernel(const int* ids, const float* __restrict__ table, float* x,
                                   int d_model, int vocab, unsigned long long* argmax_words, int n_words) {
     pdl_wait();
     pdl_launch_dependents();
     const int t = blockIdx.x;
     if (t == 0 && threadIdx.x < n_words) argmax_words[threadIdx.x] = 0ull;
-    int id = ids[t];
+    int id = __ldcg(ids + t);
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const float4* src = reinterpret_cast<const float4*>(table + (size_t)id * d_model);
     float4* dst = reinterpret_cast<float4*>(x + (size_t)t * d_model);
@@ -348,13 +359,13 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const float* __re
 
 // token[m] = index packed in the arg-max word of row m (0 when no finite logit was seen,
 // as Sampler.greedy returns); also stored where the next step's embedding reads its id.
-__global__ void argmax_decode_kernel(const unsigned long long* __restrict__ words, int* __restrict__ tokens, int n,
-                                     int* __restrict__ next_id, int* __restrict__ history, int history_pos) {
+__global__ void argmax_decode_kernel(const unsigned long long* words, int* tokens, int n, int* next_id, int* history,
+                                     int history_pos) {
     pdl_wait();
     pdl_launch_dependents();
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     if (m >= n) return;
-    const unsigned long long w = words[m];
+    const unsigned long long w = __ldcg(words + m);
     const int tok = w == 0ull ? 0 : (int)(0xffffffffu - (unsigned)(w & 0xffffffffull));
     tokens[m] = tok;
     if (m == n - 1) {

@@ -192,8 +192,9 @@ def test_decoder_run_and_generate_against_the_oracle(ctx):
     assert rel_err(got_logits, ref_logits) <= LOGIT_TOL, rel_err(got_logits, ref_logits)
     assert got_tok == int(np.argmax(got_logits))
     for _ in range(3):
-        ref_logits, ref_tok = odec.run([ref_tok])
-        got_logits, got_tok2 = gdec.run([ref_tok])
+        fed = ref_tok                     # both sides are fed the oracle's token
+        ref_logits, ref_tok = odec.run([fed])
+        got_logits, got_tok2 = gdec.run([fed])
         assert rel_err(got_logits, ref_logits) <= LOGIT_TOL
         assert got_tok2 == int(np.argmax(got_logits))
     # generate from a fresh state on both sides
