@@ -86,5 +86,42 @@ module SHAInet
       @cache_len += new_tokens
       gpu_matmul(output, @w_o)
     end
+
+    # ---- second level: the whole forward_cached on the device (llama_block.cr:189-196) ----
+    # Available once every projection and the FFN are Q8_0 on the device (to_gpu!(quantize: true),
+    # llama_block.cr:132-176) and the FFN is the dense SwiGLU; otherwise the definition above runs.
+    @attn_block : LibShainetAttn::Block = Pointer(Void).null.as(LibShainetAttn::Block)
+
+    private def q8_handle(w) : LibShainetAttn::Q8
+      qm = w.as(QuantizedCudaMatrix)
+      h = Pointer(Void).null.as(LibShainetAttn::Q8)
+      # adopts the arrays the QuantizedCudaMatrix owns: q [cols, rows] int8, scales [cols, blocks]
+      AttnB200.check LibShainetAttn.q8_wrap(AttnB200.ctx, pointerof(h), qm.q_ptr, qm.scale_ptr, qm.rows, qm.cols)
+      h
+    end
+
+    private def attn_block? : Bool
+      return false unless gpu_attention?
+      return true unless @attn_block.null?
+      ws = {@w_q, @w_k, @w_v, @w_o}
+      return false unless ws.all?(QuantizedCudaMatrix)
+      f = @ffn
+      return false unless f.is_a?(SwiGLUFF) && {f.gate_proj, f.up_proj, f.down_proj}.all?(QuantizedCudaMatrix)
+      blk = Pointer(Void).null.as(LibShainetAttn::Block)
+      AttnB200.check LibShainetAttn.block_create(AttnB200.ctx, pointerof(blk), attn_kv, @d_model,
+        @norm1.gamma.as(SimpleMatrix).data.to_unsafe, q8_handle(@w_q), q8_handle(@w_k), q8_handle(@w_v), q8_handle(@w_o),
+        @norm2.gamma.as(SimpleMatrix).data.to_unsafe, q8_handle(f.gate_proj), q8_handle(f.up_proj), q8_handle(f.down_proj),
+        @qk_norm_eps)   # LlamaBlock.new hands the same eps to norm1, norm2 and the per-head norms (llama_block.cr:92-94)
+      @attn_block = blk
+      true
+    end
+
+    def forward_cached(x : SimpleMatrix) : SimpleMatrix
+      return previous_def unless attn_block?
+      out = SimpleMatrix.new(x.rows, x.cols)
+      AttnB200.check LibShainetAttn.block_forward_host(AttnB200.ctx, @attn_block, x.data.to_unsafe, out.data.to_unsafe, x.rows)
+      @cache_len += x.rows
+      out
+    end
   end
 end

@@ -225,3 +225,84 @@ def test_two_ranks_deliver_to_each_other(tmp_path, mode):
         outs.append(o)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and "RANK_OK" in o, f"rank {r}:\n{o[-3000:]}"
+
+
+BATCHED_WORKER = r"""
+import os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.path.join(sys.argv[1], "tests")); sys.path.insert(0, sys.argv[1])
+import shainet_b200 as S
+from helpers import Q8B, qkv, rel_err, DECODE_TOL
+from oracle import oracle as O
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo")
+H, KV, hd = Q8B["H"], Q8B["KV"], Q8B["hd"]
+KVl, Hl = KV // world, H // world
+rng = np.random.default_rng(6400)            # same stream on every rank: identical full inputs
+qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+kn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+lens = [1, 33, 700, 1500, 2900, 64]
+ctx = S.AttnContext(rank)
+oracles, caches = [], []
+kvs = slice(rank * KVl, (rank + 1) * KVl)
+for L in lens:
+    kc = rng.standard_normal((KV, L, hd), dtype=np.float32)
+    vc = rng.standard_normal((KV, L, hd), dtype=np.float32)
+    o = O.OracleAttention(H, KV, hd, Q8B["theta"], 1e-6, q_norm=qn, k_norm=kn)
+    o.import_cache(kc, vc)
+    g = S.LlamaAttention(ctx, Hl, KVl, hd, Q8B["theta"], 1e-6, q_norm=qn, k_norm=kn)
+    g.cache.import_(kc[kvs], vc[kvs])
+    g.cache.reserve(L + 4)
+    oracles.append(o); caches.append(g)
+dev = torch.device("cuda", rank)
+stream = torch.cuda.current_stream().cuda_stream
+B = len(lens)
+worst = 0.0
+for step in range(3):
+    q, k, v = qkv(rng, Q8B, B)
+    ql = q.reshape(B, H, hd)[:, rank * Hl:(rank + 1) * Hl].reshape(B, -1).copy()
+    kl = k.reshape(B, KV, hd)[:, kvs].reshape(B, -1).copy()
+    vl = v.reshape(B, KV, hd)[:, kvs].reshape(B, -1).copy()
+    tq, tk, tv = (torch.from_numpy(x).to(dev) for x in (ql, kl, vl))
+    out = torch.empty(B, Hl * hd, device=dev)
+    S.forward_batched_dev(ctx, [g.cache for g in caches], tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), out.data_ptr(),
+                          caches[0].scale, stream)
+    torch.cuda.synchronize(); ctx.sync()
+    mine = out.cpu()
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)              # head outputs of all ranks, before o_proj
+    full = torch.stack(parts, 1).reshape(B, H * hd).numpy()
+    for b, o in enumerate(oracles):
+        ref = o.attend_cached(q[b:b + 1], k[b:b + 1], v[b:b + 1], threads=4)
+        worst = max(worst, rel_err(full[b:b + 1], ref))
+assert worst <= DECODE_TOL, worst
+for b, g in enumerate(caches):
+    assert g.cache_len == lens[b] + 3
+    g.close()
+dist.barrier()
+ctx.close()
+print("RANK_OK", rank, worst)
+"""
+
+
+def test_two_ranks_share_a_ragged_batch_by_kv_head(tmp_path):
+    """Batched ragged decode with the kv heads of every sequence divided over two processes (one GPU
+    each), head outputs gathered before o_proj: against one unsharded oracle per sequence."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker_batched.py"
+    script.write_text(BATCHED_WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29543", WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+        outs.append(o)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "RANK_OK" in o, f"rank {r}:\n{o[-3000:]}"
