@@ -341,7 +341,8 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     }
     // A fused kernel may start while the previous fused kernel still runs; that
     // one can be appending the newest row of this very cache.
-    f.unsafe_tail = ctx->last_fused ? 1 : 0;
+    f.unsafe_tail = (ctx->last_fused || ctx->after_chain_kernel) ? 1 : 0;
+    ctx->after_chain_kernel = false;
     f.inputs_ready = ((flags & SHAINET_ATTN_F_INPUTS_READY) && !ctx->rows_rewound) ? 1 : 0;
     ctx->rows_rewound = false;
     f.pos_delta = pos_delta;

@@ -913,7 +913,9 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         // The rows of a warp go through each stage together (no per-row branches around
         // the shuffles), so their shuffle and double-precision latencies overlap.
         float inv[MAXIT];
-        {
+#pragma unroll
+        for (int n = 0; n < MAXIT; ++n) inv[n] = 1.0f;
+        if (a.q_norm != nullptr || a.k_norm != nullptr) {   // models without per-head norms skip the sums and the f64 root
             float ss[MAXIT];
 #pragma unroll
             for (int n = 0; n < MAXIT; ++n) {

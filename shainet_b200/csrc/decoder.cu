@@ -134,6 +134,7 @@ int gemv(shainet_attn_ctx* ctx, const float* x, const signed char* q, const floa
     if ((size_t)K * sizeof(float) > 200 * 1024) return fail(SHAINET_ATTN_E_UNSUPPORTED, "input width %d exceeds what one CTA stages in shared memory", K);
     CU(launch_q8_gemv(a, ctx->sm_count, s));
     ctx->last_fused = false;
+    ctx->after_chain_kernel = true;
     return SHAINET_ATTN_OK;
 }
 

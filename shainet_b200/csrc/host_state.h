@@ -45,6 +45,9 @@ struct shainet_attn_ctx {
     size_t tickets_cap = 0;
     unsigned epoch = 0;                 // tag of the newest word-merged decode launch
     bool last_fused = false;            // the newest launch on this context was a fused decode kernel
+    bool after_chain_kernel = false;    // the newest launch was a kernel of the decoder chain (programmatic launch): a fused
+                                        // decode kernel behind it may become resident while the chain's previous attention
+                                        // kernel still appends its row
     bool rows_rewound = false;          // a cache was truncated or reset since: the next launch may rewrite rows the
                                         // previous one still reads, so it must not run ahead of it (F_INPUTS_READY is ignored once)
     unsigned long long peer_wait_ns = shainet::WAIT_LIMIT_NS;   // limit of the waits for other ranks' exchange words

@@ -40,6 +40,7 @@ constexpr int Q8_WARPS = Q8_THREADS / 32;
 constexpr int Q8_CHUNK = 512;    // K covered by one 128-bit load per lane
 constexpr int Q8_SEG = 2048;     // K per unit of work: four chunks
 constexpr unsigned FULL = 0xffffffffu;
+constexpr int Q8_CTAS_PER_SM = 2;         // grid cap per SM (one per SM measured 15 % slower on the 16-layer decode chain)
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
     uint4 v;
@@ -83,45 +84,84 @@ __device__ __forceinline__ unsigned float_key(float v) {
 // the main loop reads: element k of a row (chunk = k / 512, r = k % 512) goes to
 // chunk*512 + ((r % 16) / 4)*128 + (r / 16)*4 + r % 4, so lane l's j-th float4 of a
 // chunk is at chunk*512 + j*128 + l*4 and a warp's 128-bit loads touch 512 consecutive bytes.
+// Each thread owns up to Q8_XREG float4 of a row (destination order); the norm weights for
+// them are constants and are fetched before the wait for the previous kernel.
+constexpr int Q8_XREG = 4;   // covers K <= 4096 from registers; wider rows re-read x from L2
+
 template <int MB>
-__device__ __forceinline__ void stage_rows(const Q8GemvArgs& a, int m0, int rows, float* xs, double* red) {
+__device__ __forceinline__ void stage_rows(const Q8GemvArgs& a, int m0, int rows, float* xs, double* red,
+                                           const float4 (&gam)[Q8_XREG]) {
     const int K = a.K;
+    const int n4 = K >> 2;
+    const bool in_regs = n4 <= Q8_XREG * Q8_THREADS;
     for (int m = 0; m < MB; ++m) {
         const bool live = m < rows;
         const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)(m0 + (live ? m : 0)) * K);
-        double inv_rms = 1.0;
-        if (a.gamma != nullptr) {
-            // rms_norm.cr:29-31: sq_sum over f64(x)^2, rms = sqrt(sq_sum / cols + eps)
-            double sq = 0.0;
-            for (int i = threadIdx.x; i < K / 4; i += Q8_THREADS) {
-                const float4 v = live ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4* dst = reinterpret_cast<float4*>(xs + (size_t)m * K);
+        // destination float4 d = chunk*128 + j*32 + l  <-  source float4 chunk*128 + l*4 + j
+        auto source_of = [](int d) { return ((d >> 7) << 7) + ((d & 31) << 2) + ((d >> 5) & 3); };
+        float4 xr[Q8_XREG];
+        double sq = 0.0;
+#pragma unroll
+        for (int it = 0; it < Q8_XREG; ++it) {
+            const int d = threadIdx.x + it * Q8_THREADS;
+            xr[it] = (live && d < n4) ? __ldcg(src + source_of(d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (a.gamma == nullptr) {
+            if (in_regs) {
+#pragma unroll
+                for (int it = 0; it < Q8_XREG; ++it) {
+                    const int d = threadIdx.x + it * Q8_THREADS;
+                    if (d < n4) dst[d] = xr[it];
+                }
+            } else {
+                for (int d = threadIdx.x; d < n4; d += Q8_THREADS)
+                    dst[d] = live ? __ldcg(src + source_of(d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            continue;
+        }
+        // rms_norm.cr:29-31: sq_sum over f64(x)^2, rms = sqrt(sq_sum / cols + eps)
+        if (in_regs) {
+#pragma unroll
+            for (int it = 0; it < Q8_XREG; ++it) {
+                const float4 v = xr[it];
                 sq += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
             }
-            sq = warp_sum(sq);
-            __syncthreads();   // red[] free again
-            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
-            __syncthreads();
-            double tot = 0.0;
-#pragma unroll
-            for (int w = 0; w < Q8_WARPS; ++w) tot += red[w];
-            inv_rms = 1.0 / sqrt(tot / (double)K + a.eps);
-        }
-        float4* dst = reinterpret_cast<float4*>(xs + (size_t)m * K);
-        for (int d = threadIdx.x; d < K / 4; d += Q8_THREADS) {
-            // destination float4 d = chunk*128 + j*32 + l  <-  source float4 chunk*128 + l*4 + j
-            const int chunk = d >> 7, j = (d >> 5) & 3, l = d & 31;
-            const int s = (chunk << 7) + (l << 2) + j;
-            float4 v = live ? __ldcg(src + s) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (a.gamma != nullptr) {
-                const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + s);
-                // rms_norm.cr:32: f32((f64 x / rms) * f64 g); the division is done as a product
-                // with 1/rms, which can differ from it in the last f64 bit only
-                v.x = (float)(((double)v.x * inv_rms) * (double)g.x);
-                v.y = (float)(((double)v.y * inv_rms) * (double)g.y);
-                v.z = (float)(((double)v.z * inv_rms) * (double)g.z);
-                v.w = (float)(((double)v.w * inv_rms) * (double)g.w);
+        } else {
+            for (int d = threadIdx.x; d < n4; d += Q8_THREADS) {
+                const float4 v = live ? __ldcg(src + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+                sq += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
             }
-            dst[d] = v;
+        }
+        sq = warp_sum(sq);
+        if (m > 0) __syncthreads();   // red[] of the previous row has been read
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        double tot = 0.0;
+#pragma unroll
+        for (int w = 0; w < Q8_WARPS; ++w) tot += red[w];
+        // 1 / rms; rsqrt is within an ulp of the f64 quotient, far below the fp32 rounding that follows
+        const double inv_rms = rsqrt(tot / (double)K + a.eps);
+        // rms_norm.cr:32: f32((f64 x / rms) * f64 g), the division as a product with 1/rms
+        auto normed = [&](float4 v, float4 g) {
+            v.x = (float)(((double)v.x * inv_rms) * (double)g.x);
+            v.y = (float)(((double)v.y * inv_rms) * (double)g.y);
+            v.z = (float)(((double)v.z * inv_rms) * (double)g.z);
+            v.w = (float)(((double)v.w * inv_rms) * (double)g.w);
+            return v;
+        };
+        if (in_regs) {
+#pragma unroll
+            for (int it = 0; it < Q8_XREG; ++it) {
+                const int d = threadIdx.x + it * Q8_THREADS;
+                if (d < n4) dst[d] = normed(xr[it], gam[it]);
+            }
+        } else {
+            for (int d = threadIdx.x; d < n4; d += Q8_THREADS) {
+                const int s = source_of(d);
+                const float4 v = live ? __ldcg(src + s) : make_float4(0.f, 0.f, 0.f, 0.f);
+                dst[d] = normed(v, __ldg(reinterpret_cast<const float4*>(a.gamma) + s));
+            }
         }
     }
     __syncthreads();
@@ -188,7 +228,7 @@ __device__ __forceinline__ void consume_unit(const Unit& u, const float* xs, int
 
 // y[m0 .. m0+MB) x all N columns; gridDim.y walks the row tiles.
 template <int MB, bool SWIGLU>
-__global__ void __launch_bounds__(Q8_THREADS) q8_gemv_kernel(Q8GemvArgs a) {
+__global__ void __launch_bounds__(Q8_THREADS, MB == 1 ? 2 : 1) q8_gemv_kernel(Q8GemvArgs a) {
     extern __shared__ __align__(16) float q8_xs[];   // [MB][K] permuted activations
     __shared__ double red[Q8_WARPS];
     __shared__ unsigned long long best_sh[4];        // MB <= 4
@@ -202,13 +242,21 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_gemv_kernel(Q8GemvArgs a) {
     // weights first: they do not depend on the kernel ahead in the stream
     Unit cur;
     if (gw < pairs) load_unit<SWIGLU>(a, gw, 0, lane, cur);
+    float4 gam[Q8_XREG];   // norm weights of this thread's slots of a row: constants too
+#pragma unroll
+    for (int it = 0; it < Q8_XREG; ++it) {
+        const int d = threadIdx.x + it * Q8_THREADS;
+        gam[it] = (a.gamma != nullptr && d < (a.K >> 2) && (a.K >> 2) <= Q8_XREG * Q8_THREADS)
+                      ? __ldg(reinterpret_cast<const float4*>(a.gamma) + ((d >> 7) << 7) + ((d & 31) << 2) + ((d >> 5) & 3))
+                      : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
     // Dependents are released only after this kernel's own wait has returned: at most one
     // kernel then runs ahead of its predecessor, so a kernel's early phase can never overlap
     // anything older than the kernel directly ahead of it in the stream.
     pdl_wait();
     pdl_launch_dependents();
     if (threadIdx.x < 4) best_sh[threadIdx.x] = 0ull;
-    stage_rows<MB>(a, m0, rows, q8_xs, red);
+    stage_rows<MB>(a, m0, rows, q8_xs, red, gam);
 
     unsigned long long best[MB];
 #pragma unroll
@@ -400,7 +448,7 @@ cudaError_t launch_fast(const Q8GemvArgs& a, int sm_count, cudaStream_t s) {
     const int pairs = SWIGLU ? a.N : (a.N + 1) / 2;
     const int row_tiles = (a.M + MB - 1) / MB;
     int gx = (pairs + Q8_WARPS - 1) / Q8_WARPS;
-    const int cap = sm_count * 2;              // two resident CTAs per SM at this register budget
+    const int cap = sm_count * Q8_CTAS_PER_SM;
     if (gx > cap) gx = cap;
     return launch_pdl(kern, dim3(gx, row_tiles), dim3(Q8_THREADS), smem, s, a);
 }
