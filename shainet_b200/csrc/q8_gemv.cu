@@ -29,9 +29,12 @@
 // weights BEFORE waiting for the previous kernel in the stream (weights never depend on
 // it), waits, lets its own dependents start, and reads the activations.
 #include <math.h>
+#include <atomic>
 #include "kernels.h"
 
 namespace shainet {
+
+bool q8_fast_path(int K);
 
 namespace {
 
@@ -321,6 +324,291 @@ __global__ void __launch_bounds__(Q8_THREADS, MB == 1 ? 2 : 1) q8_gemv_kernel(Q8
     }
 }
 
+// ---------------------------------------------------------------------------
+// Single-row GEMV with the weights streamed through shared memory by the TMA engine.
+//
+// A stage is four output columns x 2048 inputs: four 2 KB bulk copies of int8 weights and
+// four 256-byte copies of their scales land on one mbarrier.  A producer thread keeps a ring
+// of such stages full; each of eight consumer warps owns the stages whose slot number equals
+// its index modulo eight (an mbarrier parity wait is only valid for a waiter that has seen
+// the previous phase, which a fixed slot -> warp map guarantees).  The ring is filled before
+// the wait for the previous kernel, so a kernel that becomes resident while its predecessor
+// still runs already holds its first 72 KB of weights per SM when the activations arrive.
+// A CTA owns a contiguous range of column quads; its warps leave one partial sum per
+// (quad, 2048-input segment, column) in shared memory and the CTA folds the segments in
+// order at the end, so results do not depend on timing.
+// ---------------------------------------------------------------------------
+constexpr int RG_NW = 8;
+constexpr int RG_THREADS = (RG_NW + 1) * 32;
+constexpr int RG_COLS = 4;
+constexpr int RG_WBYTES = RG_COLS * Q8_SEG;              // 8192
+constexpr int RG_SBYTES = RG_COLS * (Q8_SEG / 32) * 4;   // 1024
+constexpr int RG_STAGE = RG_WBYTES + RG_SBYTES;          // 9216
+constexpr int RG_CTAS_PER_SM = 2;   // sixteen consumer warps per SM; one CTA per SM measured 40 % slower on the decode chain
+
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 fadd2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 ffma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+template <int NS, bool SWIGLU>
+__global__ void __launch_bounds__(RG_THREADS, 2) q8_gemv_ring_kernel(Q8GemvArgs a, int quads_per_cta) {
+    extern __shared__ __align__(128) unsigned char rg_raw[];
+    unsigned char* ring = rg_raw;                                             // [NS][RG_STAGE]
+    float* xs = reinterpret_cast<float*>(rg_raw + (size_t)NS * RG_STAGE);     // [K] permuted activations
+    const int nseg = a.K / Q8_SEG;
+    const int vmul = SWIGLU ? 2 : 1;
+    float* part = xs + a.K;                                                   // [local stages][RG_COLS]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + (size_t)quads_per_cta * vmul * nseg * RG_COLS);
+    uint64_t* empty_bar = full_bar + NS;
+    double* red = reinterpret_cast<double*>(empty_bar + NS);                  // [RG_NW]
+    unsigned long long* best_sh = reinterpret_cast<unsigned long long*>(red + RG_NW);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int quads = a.N / RG_COLS;
+    const int q0 = blockIdx.x * quads_per_cta;
+    const int q1 = min(quads, q0 + quads_per_cta);
+    const int n_local = q1 > q0 ? (q1 - q0) * vmul * nseg : 0;   // stages of this CTA; stage i = ((quad - q0) * vmul + matrix) * nseg + seg
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        *best_sh = 0ull;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int i) {
+        const int slot = i % NS;
+        const int seg = i % nseg, v = i / nseg;
+        const int quad = q0 + v / vmul;
+        const bool second = SWIGLU && (v & 1);
+        const signed char* qb = (second ? a.q2 : a.q) + (size_t)quad * RG_COLS * a.K + (size_t)seg * Q8_SEG;
+        const float* sb = (second ? a.scales2 : a.scales) + (size_t)quad * RG_COLS * (a.K >> 5) + seg * (Q8_SEG / 32);
+        unsigned char* st = ring + (size_t)slot * RG_STAGE;
+        mbar_arrive_expect_tx(&full_bar[slot], RG_STAGE);
+#pragma unroll
+        for (int c = 0; c < RG_COLS; ++c) {
+            bulk_g2s(st + c * Q8_SEG, qb + (size_t)c * a.K, Q8_SEG, &full_bar[slot]);
+            bulk_g2s(st + RG_WBYTES + c * (Q8_SEG / 8), sb + (size_t)c * (a.K >> 5), Q8_SEG / 8, &full_bar[slot]);
+        }
+    };
+
+    if (warp == RG_NW) {
+        // ---------------- producer: weights are constants, nothing to wait for but free slots ----------------
+        if (lane == 0) {
+            for (int i = 0; i < n_local; ++i) {
+                if (i >= NS && !mbar_wait(&empty_bar[i % NS], ((i / NS) - 1) & 1, nullptr, 0)) break;
+                issue(i);
+            }
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int n4 = a.K >> 2;
+        auto source_of = [](int d) { return ((d >> 7) << 7) + ((d & 31) << 2) + ((d >> 5) & 3); };
+        float4 gam[Q8_XREG];
+        const bool in_regs = n4 <= Q8_XREG * RG_NW * 32;
+#pragma unroll
+        for (int it = 0; it < Q8_XREG; ++it) {
+            const int d = threadIdx.x + it * RG_NW * 32;
+            gam[it] = (a.gamma != nullptr && in_regs && d < n4) ? __ldg(reinterpret_cast<const float4*>(a.gamma) + source_of(d))
+                                                                : make_float4(1.f, 1.f, 1.f, 1.f);
+        }
+        pdl_wait();
+        pdl_launch_dependents();
+        // activations into shared memory (permuted), RMS-normalised if asked (rms_norm.cr:18-37)
+        const float4* src = reinterpret_cast<const float4*>(a.x);
+        float4* dst = reinterpret_cast<float4*>(xs);
+        float4 xr[Q8_XREG];
+#pragma unroll
+        for (int it = 0; it < Q8_XREG; ++it) {
+            const int d = threadIdx.x + it * RG_NW * 32;
+            xr[it] = (in_regs && d < n4) ? __ldcg(src + source_of(d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        double inv_rms = 1.0;
+        if (a.gamma != nullptr) {
+            double sq = 0.0;
+            if (in_regs) {
+#pragma unroll
+                for (int it = 0; it < Q8_XREG; ++it) {
+                    const float4 v = xr[it];
+                    sq += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
+                }
+            } else {
+                for (int d = threadIdx.x; d < n4; d += RG_NW * 32) {
+                    const float4 v = __ldcg(src + d);
+                    sq += (double)v.x * (double)v.x + (double)v.y * (double)v.y + (double)v.z * (double)v.z + (double)v.w * (double)v.w;
+                }
+            }
+            sq = warp_sum(sq);
+            if (lane == 0) red[warp] = sq;
+            asm volatile("bar.sync 1, %0;" ::"n"(RG_NW * 32) : "memory");
+            double tot = 0.0;
+#pragma unroll
+            for (int w = 0; w < RG_NW; ++w) tot += red[w];
+            inv_rms = rsqrt(tot / (double)a.K + a.eps);
+        }
+        auto normed = [&](float4 v, float4 g) {
+            v.x = (float)(((double)v.x * inv_rms) * (double)g.x);
+            v.y = (float)(((double)v.y * inv_rms) * (double)g.y);
+            v.z = (float)(((double)v.z * inv_rms) * (double)g.z);
+            v.w = (float)(((double)v.w * inv_rms) * (double)g.w);
+            return v;
+        };
+        if (in_regs) {
+#pragma unroll
+            for (int it = 0; it < Q8_XREG; ++it) {
+                const int d = threadIdx.x + it * RG_NW * 32;
+                if (d < n4) dst[d] = a.gamma != nullptr ? normed(xr[it], gam[it]) : xr[it];
+            }
+        } else {
+            for (int d = threadIdx.x; d < n4; d += RG_NW * 32) {
+                const int sidx = source_of(d);
+                const float4 v = __ldcg(src + sidx);
+                dst[d] = a.gamma != nullptr ? normed(v, __ldg(reinterpret_cast<const float4*>(a.gamma) + sidx)) : v;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(RG_NW * 32) : "memory");
+
+        const f32x2 neg_magic = pk2(-8388736.0f, -8388736.0f);   // -(2^23 + 128)
+        for (int i = warp; i < n_local; i += RG_NW) {
+            const int slot = i % NS;
+            if (!mbar_wait(&full_bar[slot], (i / NS) & 1, nullptr, 0)) break;
+            const unsigned char* st = ring + (size_t)slot * RG_STAGE;
+            const float* sc = reinterpret_cast<const float*>(st + RG_WBYTES);
+            const int seg = i % nseg;
+            float acc[RG_COLS];
+#pragma unroll
+            for (int c = 0; c < RG_COLS; ++c) acc[c] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                ulonglong2 xv[4];   // 16 activations of this lane as packed pairs
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj)
+                    xv[jj] = *reinterpret_cast<const ulonglong2*>(xs + (seg * 4 + j) * Q8_CHUNK + jj * 128 + lane * 4);
+#pragma unroll
+                for (int c = 0; c < RG_COLS; ++c) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(st + c * Q8_SEG + j * Q8_CHUNK + lane * 16);
+                    const float scale = sc[c * (Q8_SEG / 32) + j * (Q8_CHUNK / 32) + (lane >> 1)];
+                    const unsigned words[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+                    f32x2 p2 = 0ull;
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const unsigned u = words[jj];
+                        const f32x2 lo = fadd2(pk2(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)),
+                                                   __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651))), neg_magic);
+                        const f32x2 hi = fadd2(pk2(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)),
+                                                   __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653))), neg_magic);
+                        p2 = ffma2(lo, xv[jj].x, p2);
+                        p2 = ffma2(hi, xv[jj].y, p2);
+                    }
+                    float plo, phi;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(plo), "=f"(phi) : "l"(p2));
+                    acc[c] = fmaf(plo + phi, scale, acc[c]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[slot]);   // the stage's bytes are in registers / consumed
+#pragma unroll
+            for (int c = 0; c < RG_COLS; ++c)
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) acc[c] += __shfl_xor_sync(FULL, acc[c], off);
+            if (lane == 0) *reinterpret_cast<float4*>(part + (size_t)i * RG_COLS) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+    }
+    __syncthreads();
+    // fold the segments of every column in order and finish the row
+    const int cols_local = (q1 > q0 ? q1 - q0 : 0) * RG_COLS;
+    unsigned long long best = 0ull;
+    for (int e = threadIdx.x; e < cols_local; e += RG_THREADS) {
+        const int ql = e / RG_COLS, c = e - ql * RG_COLS;
+        const int n = (q0 + ql) * RG_COLS + c;
+        float v0 = 0.0f, v1 = 0.0f;
+        for (int sg = 0; sg < nseg; ++sg) {
+            v0 += part[((size_t)(ql * vmul) * nseg + sg) * RG_COLS + c];
+            if (SWIGLU) v1 += part[((size_t)(ql * vmul + 1) * nseg + sg) * RG_COLS + c];
+        }
+        if (SWIGLU) {
+            const double g = (double)v0, up = (double)v1;
+            a.y[n] = (float)((g / (1.0 + exp(-g))) * up);
+        } else {
+            float v = v0;
+            if (a.bias != nullptr) v = __fadd_rn(v, a.bias[n]);
+            if (a.residual != nullptr) v = __fadd_rn(__ldcg(a.residual + n), v);
+            a.y[n] = v;
+            if (a.argmax != nullptr && isfinite(v)) {
+                const unsigned long long cand = ((unsigned long long)float_key(v) << 32) | (0xffffffffu - (unsigned)n);
+                best = cand > best ? cand : best;
+            }
+        }
+    }
+    if (a.argmax != nullptr) {
+        if (best != 0ull) atomicMax(best_sh, best);
+        __syncthreads();
+        if (threadIdx.x == 0 && *best_sh != 0ull) atomicMax(a.argmax, *best_sh);
+    }
+}
+
+template <int NS, bool SWIGLU>
+cudaError_t launch_ring(const Q8GemvArgs& a, int sm_count, cudaStream_t s) {
+    const int quads = a.N / RG_COLS;
+    int ctas = quads < sm_count * RG_CTAS_PER_SM ? quads : sm_count * RG_CTAS_PER_SM;
+    const int qpc = (quads + ctas - 1) / ctas;
+    ctas = (quads + qpc - 1) / qpc;
+    const int nseg = a.K / Q8_SEG, vmul = SWIGLU ? 2 : 1;
+    const size_t smem = (size_t)NS * RG_STAGE + (size_t)a.K * 4 + (size_t)qpc * vmul * nseg * RG_COLS * 4 + 2 * NS * 8 + RG_NW * 8 + 16;
+    auto kern = q8_gemv_ring_kernel<NS, SWIGLU>;
+    static std::atomic<unsigned long long> configured{0};   // bit per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 64 || !(configured.load(std::memory_order_acquire) >> dev & 1ull)) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        if (dev < 64) configured.fetch_or(1ull << dev, std::memory_order_release);
+    }
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(RG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a, qpc);
+}
+
+constexpr int RG_NS = 8;   // ring stages (a multiple of the consumer warps): 72 KB
+
+bool ring_ok(const Q8GemvArgs& a, int sm_count) {
+    if (a.M != 1 || !q8_fast_path(a.K) || a.N % RG_COLS != 0) return false;
+    // Long streams (the lm_head, 295 MB at a 128 K vocabulary) run faster through the register
+    // kernel (4.6 against 3.8 TB/s measured); the ring pays off where a kernel is short and its
+    // first 72 KB per CTA are already on chip when the activations arrive.
+    if ((size_t)a.N * a.K * (a.q2 ? 2 : 1) > ((size_t)64 << 20)) return false;
+    const int quads = a.N / RG_COLS;
+    const int ctas = quads < sm_count * RG_CTAS_PER_SM ? quads : sm_count * RG_CTAS_PER_SM;
+    const int qpc = (quads + ctas - 1) / ctas;
+    const size_t smem = (size_t)RG_NS * RG_STAGE + (size_t)a.K * 4 + (size_t)qpc * (a.q2 ? 2 : 1) * (a.K / Q8_SEG) * RG_COLS * 4 + 512;
+    return smem <= 200 * 1024;
+}
+
 // Any K (ragged last block included), any N: one warp per output element.  Small shapes
 // of tests and models whose K is not a multiple of 2048; not a tuned path.
 template <bool SWIGLU>
@@ -463,6 +751,7 @@ cudaError_t launch_q8_gemv(const Q8GemvArgs& a, int sm_count, cudaStream_t s) {
     const bool swiglu = a.q2 != nullptr;
     if (q8_fast_path(a.K) && (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 && (!swiglu || (reinterpret_cast<uintptr_t>(a.q2) & 15u) == 0) &&
         (reinterpret_cast<uintptr_t>(a.x) & 15u) == 0 && (a.gamma == nullptr || (reinterpret_cast<uintptr_t>(a.gamma) & 15u) == 0)) {
+        if (ring_ok(a, sm_count)) return swiglu ? launch_ring<RG_NS, true>(a, sm_count, s) : launch_ring<RG_NS, false>(a, sm_count, s);
         // Rows are taken four at a time while that fits shared memory; a row tile re-reads the weights.
         const bool four = a.M >= 3 && (size_t)4 * a.K * sizeof(float) <= 160 * 1024;
         const bool two = !four && a.M >= 2 && (size_t)2 * a.K * sizeof(float) <= 160 * 1024;
