@@ -241,7 +241,7 @@ BATCHED_WL = dict(name="cfg4: Qwen3-8B attention, 64 sequences in lock step, con
                   H=32, KV=8, hd=128, theta=1e6, batch=64, lo=1024, hi=32768, layers_total=36, steps=16)
 
 
-def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None):
+def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None, layers_resident=None):
     """Batched ragged decode on the cfg4 shape: one launch per layer serves all 64 sequences (norm/RoPE/
     append and attention fused, two-level ticket merge).  Over several ranks the kv heads (and their
     query heads) are divided, every rank holds its heads of all 64 sequences, and the head outputs
@@ -250,11 +250,11 @@ def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None):
     (4.9 GB per layer over all ranks); the per-layer time scales to a step."""
     import torch
     w = BATCHED_WL
-    H, KV, hd, B = w["H"], w["KV"], w["hd"], w["batch"]
+    H, KV, hd, B = w["H"], w["KV"], w["hd"], seqs or w["batch"]
     if KV % world:
         return None
     KVl, Hl = KV // world, H // world
-    layers_timed = 2 * world
+    layers_timed = layers_resident or 2 * world
     rng = np.random.default_rng(4001)
     lens = np.exp(rng.uniform(np.log(w["lo"]), np.log(w["hi"]), B)).astype(np.int64)
     steps, warm = w["steps"], 3
@@ -425,6 +425,61 @@ def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
                          "avg_launch_us": us, "launches_timed": steps * layers}}
 
 
+def gemv_block(S, ctx, dev, stream_obj):
+    """Q8_0 GEMV (one activation row) at the projection shapes of the LLaMA-3.2-1B block: bytes = one per weight
+    plus four per 32-weight scale, over the time of a launch in a chain of launches on one stream (each launch
+    waits for the one before it, as in decode).  Every shape cycles over enough distinct weights to exceed L2."""
+    import torch
+    g = torch.Generator(device=dev)
+    g.manual_seed(2401)
+    peak, kind = measured_peak()
+    out = []
+    for name, K, N in (("q_proj / o_proj", 2048, 2048), ("k_proj / v_proj", 2048, 512), ("q|k|v stacked", 2048, 3072),
+                       ("gate_proj / up_proj", 2048, 8192), ("down_proj", 8192, 2048)):
+        per = K * N + 4 * N * (K // 32)
+        count = max(4, int(400e6 // per))
+        keep, ws = [], []
+        for _ in range(count):
+            q = torch.randint(-127, 128, (N, K), device=dev, dtype=torch.int8, generator=g)
+            sc = (0.02 / 127.0) * (0.5 + torch.rand(N, K // 32, device=dev, generator=g))
+            keep.extend([q, sc])
+            ws.append(S.Q8Weight.wrap(ctx, q.data_ptr(), sc.data_ptr(), K, N))
+        x = torch.randn(1, K, device=dev, generator=g)
+        y = torch.empty(1, N, device=dev)
+        calls = []
+        gemv = ctx.L.shainet_attn_q8_gemv_dev
+        vp = C.c_void_p
+        for i in range(count):
+            calls.append((ctx.h, ws[i].h, vp(x.data_ptr()), vp(y.data_ptr()), 1, vp(stream_obj.cuda_stream)))
+        reps = 6
+
+        def run(n):
+            for _ in range(n):
+                for a in calls:
+                    rc = gemv(*a)
+                    if rc:
+                        S.check(rc)
+        run(1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run(reps)
+        e1.record()
+        torch.cuda.synchronize()
+        ctx.sync()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * count)
+        single = K * N + 4 * N * (K // 32)
+        gbs = single / (us * 1e-6) / 1e9
+        out.append({"shape": name, "K": K, "N": N,
+                    "bytes_per_launch": single, "us_per_launch": us, "gbs": gbs, "frac": gbs / peak, "weights_cycled": count})
+        for w in ws:
+            w.close()
+        del keep
+    return {"kernel": "q8_gemv_ring_kernel (one row)", "peak": peak, "peak_kind": kind, "unit": "GB/s", "shapes": out,
+            "note": "launches are chained on one stream, each waiting for its predecessor; us_per_launch therefore "
+                    "includes the dependent-launch latency that dominates at these sizes (1.3 to 19 MB per launch)"}
+
+
 def model_decode_block(S, ctx, dev, steps=96, warm=8):
     """BASELINE config 2 as a whole model on the device: 16 LLaMA-3.2-1B-shaped blocks (hidden 2048, 32/8
     heads, head_dim 64, FFN 8192), vocabulary 128256, every projection / FFN / lm_head weight Q8_0, fp32
@@ -579,12 +634,14 @@ def run_one_block(args):
     ctx = S.AttnContext(0)
     tstream = torch.cuda.Stream(device=dev)
     torch.cuda.set_stream(tstream)
-    if args.only == "model":
+    if args.only == "gemv":
+        res = gemv_block(S, ctx, dev, tstream)
+    elif args.only == "model":
         res = model_decode_block(S, ctx, dev, steps=args.steps if args.steps != 256 else 96)
     elif args.only == "ctx4k":
         res = short_context_block(S, ctx, dev, tstream)
     elif args.only == "batched":
-        res = batched_block(S, ctx, dev, tstream)
+        res = batched_block(S, ctx, dev, tstream, seqs=args.batched_seqs, layers_resident=args.batched_layers)
     else:
         res = prefill_block(S, ctx, dev, tstream)
     ctx.close()
@@ -842,10 +899,11 @@ def run_ours(args, wl, rank, world, local_rank):
         prefill = prefill_block(S, ctx, dev, tstream)
     if not args.no_prefill:
         batched = batched_block(S, ctx, dev, tstream, rank, world, dist)
-    model = None
+    model = gemv = None
     if world == 1 and not args.no_prefill and args.workload != "cfg2":
         short_ctx = short_context_block(S, ctx, dev, tstream)
         model = model_decode_block(S, ctx, dev)
+        gemv = gemv_block(S, ctx, dev, tstream)
     parity = parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, layers * world * pay, epoch[0] + 1)
 
     if rank == 0:
@@ -899,6 +957,8 @@ def run_ours(args, wl, rank, world, local_rank):
             line["decode_ctx4k"] = short_ctx
         if model is not None:
             line["decode_model_cfg2"] = model
+        if gemv is not None:
+            line["q8_gemv"] = gemv
         if world == 1 and not args.no_cpu_baseline:
             threads = host_threads()
             cpu_port_rate(wl, threads, 1, 1)
@@ -935,8 +995,10 @@ def main():
                     help="override 'query_heads,kv_heads' (debugging: e.g. 8,1 on 2 ranks runs the sequence-split path)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="several ranks: gather head outputs with torch.distributed instead of the kernel's peer stores")
-    ap.add_argument("--only", default=None, choices=["model", "ctx4k", "batched", "prefill"],
+    ap.add_argument("--only", default=None, choices=["model", "gemv", "ctx4k", "batched", "prefill"],
                     help="run one secondary block alone on one GPU and print its JSON object")
+    ap.add_argument("--batched-seqs", type=int, default=None, help="--only batched: sequences in the batch (profiling: a small resident case)")
+    ap.add_argument("--batched-layers", type=int, default=None, help="--only batched: resident layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (cfg3 shape) block of the JSON line")
     args = ap.parse_args()
