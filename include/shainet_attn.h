@@ -10,6 +10,12 @@
  *
  * Threading: a context and the caches created from it are used by one host
  * thread at a time (the contract of the reference's mutex-serialised Network).
+ * Streams: the *_dev entries enqueue on the stream they are given and return at
+ * once.  Calls that read or replace what those kernels use - kv_export, kv_import,
+ * kv_set_rope*, kv_set_qk_norm, kv_set_bias, kv_fill_normal, ctx_sync - synchronise
+ * only the context's own stream: a caller that launched on a stream of its own
+ * synchronises that stream first (ctx_sync also reports a kernel-side wait failure
+ * only once the stream that ran the kernel has been synchronised).
  * There is no CPU fallback: without a CUDA device every call fails.
  */
 #ifndef SHAINET_ATTN_H
@@ -43,7 +49,8 @@ extern "C" {
  * kernel then starts its RoPE/norm prologue and its streaming while that
  * kernel is still draining, and only waits for it before touching the scratch
  * the two share.  Without the flag nothing is assumed. */
-#define SHAINET_ATTN_F_INPUTS_READY 16u
+#define SHAINET_ATTN_F_INPUTS_READY 16u   /* ignored for the first launch after kv_truncate / kv_reset: the rows it
+                                             rewrites may still be read by the launch ahead of it */
 /* Merge the split partials of the fused decode kernel with "last finisher"
  * tickets even where the flag-polling merge would be chosen (testing). */
 #define SHAINET_ATTN_F_TICKET_MERGE 32u

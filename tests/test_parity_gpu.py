@@ -443,3 +443,43 @@ def test_rope_known_answers_in_the_appended_rows(ctx):
         ref = O.rope_apply(x, 0, theta)
         assert np.abs(kc[0] - ref).max() <= 1e-5 * max(1.0, np.abs(ref).max())
         g.close()
+
+
+def test_truncate_then_inputs_ready_does_not_race_with_the_previous_launch(ctx):
+    """Roll-back of speculative rows (kv_truncate) followed at once by a launch that declares its inputs
+    ready: the new launch rewrites a row the still-running previous launch reads, so the library drops the
+    declaration for that one launch.  Queued back to back on one stream, checked against the oracle."""
+    import torch
+    import shainet_b200 as S
+    rng = np.random.default_rng(909)
+    o, g = make_pair(ctx, Q30, rng)
+    q, k, v = qkv(rng, Q30, 4500)
+    o.attend_cached(q, k, v, threads=8)
+    kc, vc = o.export_cache()
+    g.cache.import_(kc, vc)
+    g.cache.reserve(4700)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    ins = [qkv(rng, Q30, 1) for _ in range(12)]
+    dins = [tuple(torch.from_numpy(x).to(dev) for x in trip) for trip in ins]
+    outs = [torch.empty(1, Q30["H"] * Q30["hd"], device=dev) for _ in ins]
+    torch.cuda.synchronize()
+    plan = [0, 1, 2, 3, "back2", 4, 5, "back1", 6, 7, 8, "back3", 9, 10, 11]
+    for step in plan:
+        if isinstance(step, str):
+            g.cache.truncate(g.cache_len - int(step[-1]))
+            continue
+        tq, tk, tv = dins[step]
+        g.forward_cached_dev(tq.data_ptr(), tk.data_ptr(), tv.data_ptr(), outs[step].data_ptr(), 1, stream, S.F_INPUTS_READY)
+    torch.cuda.synchronize()
+    ctx.sync()
+    for step in plan:
+        if isinstance(step, str):
+            kc, vc = o.export_cache()
+            n = o.cache_len - int(step[-1])
+            o.import_cache(kc[:, :n], vc[:, :n])
+            continue
+        ref = o.attend_cached(*ins[step])
+        assert rel_err(outs[step].cpu().numpy(), ref) <= DECODE_TOL, step
+    assert g.cache_len == o.cache_len
+    g.close()
