@@ -254,7 +254,7 @@ def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None
     if KV % world:
         return None
     KVl, Hl = KV // world, H // world
-    layers_timed = layers_resident or 2 * world
+    layers_timed = layers_resident or min(2 * world, 8)
     rng = np.random.default_rng(4001)
     lens = np.exp(rng.uniform(np.log(w["lo"]), np.log(w["hi"]), B)).astype(np.int64)
     steps, warm = w["steps"], 3

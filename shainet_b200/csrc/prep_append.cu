@@ -52,9 +52,10 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
         cs[i] = c_;
         sn[i] = s_;
     }
-    for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
-        const float* src;
-        const float* bias;
+    // Stage the token's rows in shared memory.  A warp takes its slots six at a time and issues all of
+    // their 128-bit loads before it uses the first, so that a token costs two round trips to memory
+    // instead of one per head.
+    auto slot_src = [&](int slot, const float*& src, const float*& bias) {
         if (slot < H) {
             src = a.q + ((size_t)r * H + slot) * hd;
             bias = a.b_q ? a.b_q + (size_t)slot * hd : nullptr;
@@ -65,11 +66,66 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
             src = a.v_new + ((size_t)r * KV + (slot - H - KV)) * hd;
             bias = a.b_v ? a.b_v + (size_t)(slot - H - KV) * hd : nullptr;
         }
-        float* row = buf + (size_t)slot * stride;
-        for (int d = lane; d < hd; d += 32) {
-            float x = src[d];
-            if (bias) x = __fadd_rn(x, bias[d]);
-            row[d] = x;
+    };
+    constexpr int GROUP = 6;
+    const int hd4 = hd >> 2;
+    const bool vec = (hd & 3) == 0 && hd4 <= 64 && (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(a.k_new) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.v_new) & 15u) == 0;
+    if (vec) {
+        for (int s0 = warp; s0 < per_row; s0 += PREP_WARPS * GROUP) {
+            float4 x[GROUP][2];
+#pragma unroll
+            for (int g = 0; g < GROUP; ++g) {
+                const int slot = s0 + g * PREP_WARPS;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int d4 = lane + 32 * h;
+                    x[g][h] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (slot < per_row && d4 < hd4) {
+                        const float* src;
+                        const float* bias;
+                        slot_src(slot, src, bias);
+                        x[g][h] = __ldg(reinterpret_cast<const float4*>(src) + d4);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < GROUP; ++g) {
+                const int slot = s0 + g * PREP_WARPS;
+                if (slot >= per_row) break;
+                const float* src;
+                const float* bias;
+                slot_src(slot, src, bias);
+                float* row = buf + (size_t)slot * stride;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int d = (lane + 32 * h) * 4;
+                    if (d >= hd) break;
+                    float4 v = x[g][h];
+                    if (bias) {
+                        v.x = __fadd_rn(v.x, bias[d]);
+                        v.y = __fadd_rn(v.y, bias[d + 1]);
+                        v.z = __fadd_rn(v.z, bias[d + 2]);
+                        v.w = __fadd_rn(v.w, bias[d + 3]);
+                    }
+                    row[d] = v.x;
+                    row[d + 1] = v.y;
+                    row[d + 2] = v.z;
+                    row[d + 3] = v.w;
+                }
+            }
+        }
+    } else {
+        for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+            const float* src;
+            const float* bias;
+            slot_src(slot, src, bias);
+            float* row = buf + (size_t)slot * stride;
+            for (int d = lane; d < hd; d += 32) {
+                float x = src[d];
+                if (bias) x = __fadd_rn(x, bias[d]);
+                row[d] = x;
+            }
         }
     }
     __syncthreads();
