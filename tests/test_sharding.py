@@ -117,3 +117,56 @@ def test_two_gloo_ranks_reproduce_the_unsharded_oracle(tmp_path):
                        capture_output=True, text=True, env=env, timeout=240)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("ok") == 2
+
+
+BATCHED_WORKER = textwrap.dedent("""
+    import os, sys
+    sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "tests"))
+    import numpy as np, torch, torch.distributed as dist
+    from oracle import oracle as O
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    H, KV, hd = 8, 4, 16
+    Hl, KVl = H // world, KV // world
+    rng = np.random.default_rng(123)        # same stream on every rank
+    lens = [1, 9, 40, 17]
+    B = len(lens)
+    full, mine = [], []
+    kvs = slice(rank * KVl, (rank + 1) * KVl)
+    for L in lens:
+        kc = rng.standard_normal((KV, L, hd)).astype(np.float32)
+        vc = rng.standard_normal((KV, L, hd)).astype(np.float32)
+        f = O.OracleAttention(H, KV, hd, 10000.0); f.import_cache(kc, vc); full.append(f)
+        m = O.OracleAttention(Hl, KVl, hd, 10000.0); m.import_cache(kc[kvs], vc[kvs]); mine.append(m)
+    for step in range(3):
+        q = rng.standard_normal((B, H * hd)).astype(np.float32)
+        k = rng.standard_normal((B, KV * hd)).astype(np.float32)
+        v = rng.standard_normal((B, KV * hd)).astype(np.float32)
+        # this rank's columns of the lock-step rows: its query heads and its kv heads
+        ql = q.reshape(B, H, hd)[:, rank * Hl:(rank + 1) * Hl].reshape(B, -1)
+        kl = k.reshape(B, KV, hd)[:, kvs].reshape(B, -1)
+        vl = v.reshape(B, KV, hd)[:, kvs].reshape(B, -1)
+        out = np.stack([mine[b].attend_cached(ql[b:b + 1], kl[b:b + 1], vl[b:b + 1])[0] for b in range(B)])
+        payload = torch.from_numpy(out.astype(np.float32))               # [B, Hl*hd]
+        gathered = torch.empty(world, B, Hl * hd)
+        dist.all_gather_into_tensor(gathered.view(-1), payload.view(-1))  # the layout the bench gathers into
+        got = gathered.permute(1, 0, 2).reshape(B, H * hd).numpy()        # [B, rank-major head blocks] = [B, H*hd]
+        for b in range(B):
+            ref = full[b].attend_cached(q[b:b + 1], k[b:b + 1], v[b:b + 1])[0]
+            assert np.array_equal(got[b], ref), (step, b)                  # the same arithmetic per head: exact
+    dist.destroy_process_group()
+    print("rank", rank, "ok")
+""")
+
+
+def test_two_gloo_ranks_share_a_ragged_batch_by_kv_head(tmp_path):
+    """Batched decode with the kv heads of every sequence divided over the ranks: the per-rank column
+    slices and the [rank][sequence][local heads] gather layout reassemble the unsharded rows exactly."""
+    script = tmp_path / "worker_batched.py"
+    script.write_text(BATCHED_WORKER.format(root=ROOT))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29544", str(script)],
+                       capture_output=True, text=True, env=env, timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("ok") == 2
