@@ -432,6 +432,22 @@ __global__ void __launch_bounds__(RG_THREADS, 2) q8_gemv_ring_kernel(Q8GemvArgs 
         // activations into shared memory (permuted), RMS-normalised if asked (rms_norm.cr:18-37)
         const float4* src = reinterpret_cast<const float4*>(a.x);
         float4* dst = reinterpret_cast<float4*>(xs);
+        if (a.gamma == nullptr && !in_regs) {
+            // a wide row without a norm (the FFN's down projection): eight loads in flight per thread
+            for (int base = threadIdx.x; base < n4; base += 8 * RG_NW * 32) {
+                float4 t[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int d = base + u * RG_NW * 32;
+                    t[u] = d < n4 ? __ldcg(src + source_of(d)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int d = base + u * RG_NW * 32;
+                    if (d < n4) dst[d] = t[u];
+                }
+            }
+        }
         float4 xr[Q8_XREG];
 #pragma unroll
         for (int it = 0; it < Q8_XREG; ++it) {
@@ -474,11 +490,10 @@ __global__ void __launch_bounds__(RG_THREADS, 2) q8_gemv_ring_kernel(Q8GemvArgs 
                 const int d = threadIdx.x + it * RG_NW * 32;
                 if (d < n4) dst[d] = a.gamma != nullptr ? normed(xr[it], gam[it]) : xr[it];
             }
-        } else {
+        } else if (a.gamma != nullptr) {
             for (int d = threadIdx.x; d < n4; d += RG_NW * 32) {
                 const int sidx = source_of(d);
-                const float4 v = __ldcg(src + sidx);
-                dst[d] = a.gamma != nullptr ? normed(v, __ldg(reinterpret_cast<const float4*>(a.gamma) + sidx)) : v;
+                dst[d] = normed(__ldcg(src + sidx), __ldg(reinterpret_cast<const float4*>(a.gamma) + sidx));
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(RG_NW * 32) : "memory");
