@@ -279,6 +279,7 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
         rc = pick_kernel(hs, batch, T, flags, &kern);
         if (rc) return rc;
         p.round_q_tf32 = kern == Kernel::Tensor ? 1 : 0;
+        p.status = ctx->status_dev;
         CU(launch_prep_append(p, s));
         return run_attention(ctx, hs, seqs, batch, T, total_visible, max_visible, ctx->q_rot.p, out, scale, flags, s);
     }

@@ -45,6 +45,7 @@ struct PrepArgs {
     int batch, T;
     HeadShape hs;
     int round_q_tf32;      // round the rotated q to nearest TF32 (it feeds the tensor-core prefill kernel)
+    AttnStatus* status;    // nullable: receives a bounded wait's failure
 };
 
 struct AttnArgs {

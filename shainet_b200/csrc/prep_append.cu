@@ -28,16 +28,22 @@ constexpr int PREP_THREADS = PREP_WARPS * 32;
 //     order, but 32 heads run their chains side by side (one per lane) instead
 //     of one lane working while 31 wait.
 __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
-    extern __shared__ float prep_smem[];
+    extern __shared__ __align__(16) float prep_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int H = a.hs.num_heads, KV = a.hs.num_kv_heads, hd = a.hs.head_dim;
     const int per_row = H + 2 * KV;
     const int half = hd >> 1;
-    const int stride = hd + 1;
-    float* cs = prep_smem;               // [half]
+    // Rows arrive by bulk copies (TMA engine) when they are 16-byte multiples at 16-byte addresses: all of a
+    // token's 24 KB are then in flight at once without holding registers.  Such rows are padded by four floats
+    // (the copies need 16-byte destinations); otherwise by one (conflict-free column walks).
+    const bool vec = (hd & 3) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(a.k_new) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.v_new) & 15u) == 0;
+    const int stride = vec ? hd + 4 : hd + 1;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(prep_smem);   // 16 bytes reserved
+    float* buf = prep_smem + 4;          // [per_row][stride], 16-byte aligned
+    float* cs = buf + (size_t)per_row * stride;   // [half]
     float* sn = cs + half;               // [half]
     float* inv = sn + half;              // [H + KV]
-    float* buf = inv + (H + KV);         // [per_row][hd + 1]
 
     const int r = blockIdx.x;
     const int b = r / a.T, t = r % a.T;
@@ -52,9 +58,7 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
         cs[i] = c_;
         sn[i] = s_;
     }
-    // Stage the token's rows in shared memory.  A warp takes its slots six at a time and issues all of
-    // their 128-bit loads before it uses the first, so that a token costs two round trips to memory
-    // instead of one per head.
+    // Stage the token's rows in shared memory.
     auto slot_src = [&](int slot, const float*& src, const float*& bias) {
         if (slot < H) {
             src = a.q + ((size_t)r * H + slot) * hd;
@@ -67,52 +71,30 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
             bias = a.b_v ? a.b_v + (size_t)(slot - H - KV) * hd : nullptr;
         }
     };
-    constexpr int GROUP = 6;
-    const int hd4 = hd >> 2;
-    const bool vec = (hd & 3) == 0 && hd4 <= 64 && (reinterpret_cast<uintptr_t>(a.q) & 15u) == 0 &&
-                     (reinterpret_cast<uintptr_t>(a.k_new) & 15u) == 0 && (reinterpret_cast<uintptr_t>(a.v_new) & 15u) == 0;
     if (vec) {
-        for (int s0 = warp; s0 < per_row; s0 += PREP_WARPS * GROUP) {
-            float4 x[GROUP][2];
-#pragma unroll
-            for (int g = 0; g < GROUP; ++g) {
-                const int slot = s0 + g * PREP_WARPS;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int d4 = lane + 32 * h;
-                    x[g][h] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (slot < per_row && d4 < hd4) {
-                        const float* src;
-                        const float* bias;
-                        slot_src(slot, src, bias);
-                        x[g][h] = __ldg(reinterpret_cast<const float4*>(src) + d4);
-                    }
-                }
-            }
-#pragma unroll
-            for (int g = 0; g < GROUP; ++g) {
-                const int slot = s0 + g * PREP_WARPS;
-                if (slot >= per_row) break;
+        if (threadIdx.x == 0) {
+            mbar_init(bar, 1);
+            fence_mbar_init();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            mbar_arrive_expect_tx(bar, (uint32_t)per_row * hd * 4);
+            for (int slot = 0; slot < per_row; ++slot) {
                 const float* src;
                 const float* bias;
                 slot_src(slot, src, bias);
+                bulk_g2s(buf + (size_t)slot * stride, src, (uint32_t)hd * 4, bar);
+            }
+        }
+        if (!mbar_wait(bar, 0, a.status, 31)) return;   // bounded; the whole CTA sees the same outcome
+        if (a.b_q != nullptr || a.b_k != nullptr || a.b_v != nullptr) {
+            for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+                const float* src;
+                const float* bias;
+                slot_src(slot, src, bias);
+                if (bias == nullptr) continue;
                 float* row = buf + (size_t)slot * stride;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int d = (lane + 32 * h) * 4;
-                    if (d >= hd) break;
-                    float4 v = x[g][h];
-                    if (bias) {
-                        v.x = __fadd_rn(v.x, bias[d]);
-                        v.y = __fadd_rn(v.y, bias[d + 1]);
-                        v.z = __fadd_rn(v.z, bias[d + 2]);
-                        v.w = __fadd_rn(v.w, bias[d + 3]);
-                    }
-                    row[d] = v.x;
-                    row[d + 1] = v.y;
-                    row[d + 2] = v.z;
-                    row[d + 3] = v.w;
-                }
+                for (int d = lane; d < hd; d += 32) row[d] = __fadd_rn(row[d], bias[d]);
             }
         }
     } else {
@@ -245,7 +227,7 @@ cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s) {
     const long long rows = (long long)a.batch * a.T;
     if (rows == 0) return cudaSuccess;
     const int per_row = a.hs.num_heads + 2 * a.hs.num_kv_heads;
-    const size_t smem = ((size_t)per_row * (a.hs.head_dim + 1) + a.hs.head_dim + a.hs.num_heads + a.hs.num_kv_heads) * sizeof(float);
+    const size_t smem = (4 + (size_t)per_row * (a.hs.head_dim + 4) + a.hs.head_dim + a.hs.num_heads + a.hs.num_kv_heads) * sizeof(float);
     if (smem > 48 * 1024) {
         if (smem > 227 * 1024) return cudaErrorInvalidValue;
         cudaError_t e = cudaFuncSetAttribute(prep_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
