@@ -45,12 +45,12 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 139.3 / 134.26
 
 
-def decode_bytes(wl, L, kv_heads=None):
+def decode_bytes(wl, L, kv_heads=None, elem_bytes=4):
     """Algorithmic HBM bytes of one layer-step at visible length L: K and V read
-    once, the new row written, q read and out written."""
+    once, the new row written (cache elements of elem_bytes), q read and out written (fp32)."""
     KV = wl["KV"] if kv_heads is None else kv_heads
     H = wl["H"] * KV // wl["KV"]
-    return 2 * KV * L * wl["hd"] * 4 + 2 * KV * wl["hd"] * 4 + 2 * H * wl["hd"] * 4
+    return 2 * KV * L * wl["hd"] * elem_bytes + 2 * KV * wl["hd"] * elem_bytes + 2 * H * wl["hd"] * 4
 
 
 def measured_peak():
@@ -241,7 +241,7 @@ BATCHED_WL = dict(name="cfg4: Qwen3-8B attention, 64 sequences in lock step, con
                   H=32, KV=8, hd=128, theta=1e6, batch=64, lo=1024, hi=32768, layers_total=36, steps=16)
 
 
-def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None, layers_resident=None):
+def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None, layers_resident=None, kv_format="f32"):
     """Batched ragged decode on the cfg4 shape: one launch per layer serves all 64 sequences (norm/RoPE/
     append and attention fused, two-level ticket merge).  Over several ranks the kv heads (and their
     query heads) are divided, every rank holds its heads of all 64 sequences, and the head outputs
@@ -265,7 +265,7 @@ def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None
         caches = []
         for b in range(B):
             a = S.LlamaAttention(ctx, Hl, KVl, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn,
-                                 initial_capacity=int(lens[b]) + steps + warm + 8)
+                                 initial_capacity=int(lens[b]) + steps + warm + 8, kv_format=kv_format)
             a.cache.fill_normal(int(lens[b]), 4002 + 100000 * rank + 1000 * l + b)
             caches.append(a)
         layers.append(caches)
@@ -304,14 +304,15 @@ def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None
         ms = float(t.item())
     ms_layer = ms / (steps * len(layers))
     mean_len = float(lens.sum()) + B * (warm + (steps + 1) / 2.0)
-    bytes_layer_rank = 2.0 * KVl * mean_len * hd * 4 + B * (2 * KVl + 2 * Hl) * hd * 4
+    es = 2 if kv_format == "bf16" else 4
+    bytes_layer_rank = 2.0 * KVl * mean_len * hd * es + B * (2 * KVl * es + 2 * Hl * 4) * hd
     for caches in layers:
         for a in caches:
             a.close()
-    check = batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist)
+    check = batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist, kv_format)
     peak, kind = measured_peak()
     gbs = bytes_layer_rank / (ms_layer / 1e3) / 1e9
-    return {"workload": w["name"], "sum_of_context_lengths": int(lens.sum()), "ms_per_layer": ms_layer,
+    return {"workload": w["name"] if es == 4 else w["name"].replace("fp32 KV cache", "bfloat16 KV cache"), "sum_of_context_lengths": int(lens.sum()), "ms_per_layer": ms_layer,
             "tokens_per_s_36_layers": B / (ms_layer * w["layers_total"] / 1e3), "layers_timed": len(layers), "steps": steps,
             "sharding": (f"{world} rank(s) x {KVl} kv head(s) of every sequence"
                          + ("; head outputs all-gathered per layer (NCCL)" if world > 1 else "; no exchange")),
@@ -321,7 +322,7 @@ def batched_block(S, ctx, dev, stream_obj, rank=0, world=1, dist=None, seqs=None
                          "note": "per GPU; the launch time includes the layer's all-gather when ranks > 1"}}
 
 
-def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist):
+def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist, kv_format="f32"):
     """One checked lock-step step of the batched (and, over several ranks, kv-head-sharded and gathered)
     path: 5 short sequences with seeded caches against one CPU oracle per sequence, on rank 0."""
     import torch
@@ -339,7 +340,7 @@ def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist):
     kvs = slice(rank * KVl, (rank + 1) * KVl)
     caches = []
     for kc, vc in full:
-        a = S.LlamaAttention(ctx, Hl, KVl, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        a = S.LlamaAttention(ctx, Hl, KVl, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn, kv_format=kv_format)
         a.cache.import_(kc[kvs], vc[kvs])
         a.cache.reserve(kc.shape[1] + 2)
         caches.append(a)
@@ -365,7 +366,8 @@ def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist):
     from oracle import oracle as O
     worst = 0.0
     for b, (kc, vc) in enumerate(full):
-        o = O.OracleAttention(H, KV, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        o = O.OracleAttention(H, KV, hd, w["theta"], 1e-6, q_norm=qn, k_norm=kn,
+                              kv_rounding="bf16" if kv_format == "bf16" else None)
         o.import_cache(kc, vc)
         ref = o.attend_cached(q[b:b + 1], k[b:b + 1], v[b:b + 1], threads=host_threads())
         worst = max(worst, float(np.abs(got[b:b + 1].astype(np.float64) - ref).max() / np.abs(ref).max()))
@@ -374,15 +376,68 @@ def batched_parity(S, ctx, w, rank, world, dev, stream_obj, dist):
 
 def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
     """The metric's ctx-4k point: BASELINE config 2's attention (LLaMA-3.2-1B: 16 layers, 32 query /
-    8 kv heads, head_dim 64, batch 1, fp32 cache at ctx 4096), one fused launch per layer-step, timed
-    with CUDA events on the launching stream.  The 16 layers' K/V (268 MB) are cycled, which is more
-    than L2 holds, so every launch streams from HBM."""
+    8 kv heads, head_dim 64, batch 1, fp32 cache at ctx 4096).  The 16 layers' K/V (268 MB) are
+    cycled, which is more than L2 holds, so every launch streams from HBM."""
+    return decode_chain_block(S, ctx, dev, stream_obj, WORKLOADS["cfg2"], "f32", steps, warm)
+
+
+def bf16_kv_block(S, ctx, dev, stream_obj):
+    """The opt-in bfloat16 KV cache (no counterpart in the reference, whose rows are fp32; not the
+    headline): the two decode points of the metric with rows rounded to bfloat16 as they are
+    appended, fp32 arithmetic.  Algorithmic bytes count two bytes per cache element.  The ctx-4k
+    point runs three copies of the 16 layers so that the cycled K/V (403 MB) exceed L2."""
+    out = []
+    batched = batched_block(S, ctx, dev, stream_obj, kv_format="bf16")
+    for key, steps, copies in (("cfg5", 24, 1), ("cfg2", 64, 3)):
+        wl = dict(WORKLOADS[key])
+        wl["name"] = wl["name"].replace("fp32 KV cache", "bfloat16 KV cache")
+        res = decode_chain_block(S, ctx, dev, stream_obj, wl, "bf16", steps, 6, copies)
+        res["parity_check"] = format_parity(S, ctx, wl, "bf16")
+        out.append(res)
+    out.append(batched)
+    return out
+
+
+def format_parity(S, ctx, wl, kv_format, ctx_len=2053):
+    """One checked decode step over a cache of the given element format against the CPU oracle with the
+    same row rounding, at a context the oracle finishes in a moment."""
+    from oracle import oracle as O
+    H, KV, hd = wl["H"], wl["KV"], wl["hd"]
+    rng = np.random.default_rng(611)
+    kw = {}
+    if wl["qk_norm"]:
+        kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
+                  k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
+    o = O.OracleAttention(H, KV, hd, wl["theta"], 1e-6, kv_rounding="bf16" if kv_format == "bf16" else None, **kw)
+    g = S.LlamaAttention(ctx, H, KV, hd, wl["theta"], 1e-6, kv_format=kv_format, **kw)
+    kc = rng.standard_normal((KV, ctx_len, hd), dtype=np.float32)
+    vc = rng.standard_normal((KV, ctx_len, hd), dtype=np.float32)
+    o.import_cache(kc, vc)
+    g.cache.import_(kc, vc)
+    q, k, v = (rng.standard_normal((1, n), dtype=np.float32) for n in (H * hd, KV * hd, KV * hd))
+    ref = o.attend_cached(q, k, v, threads=host_threads())
+    got = g.forward_cached(q, k, v)
+    g.close()
+    err = float(np.abs(got.astype(np.float64) - ref).max() / np.abs(ref).max())
+    return {"max_rel_err": err, "tol": 1e-5, "ok": bool(err <= 1e-5), "ctx": ctx_len,
+            "what": "one decode step against the CPU oracle whose cache rows are rounded the same way"}
+
+
+def decode_chain_block(S, ctx, dev, stream_obj, wl, kv_format, steps, warm, copies=1):
+    """Batch-1 decode attention of a whole model's layers (times `copies`), one fused launch per
+    layer-step, timed with CUDA events on the launching stream."""
     import torch
-    wl = WORKLOADS["cfg2"]
-    H, KV, hd, layers, L = wl["H"], wl["KV"], wl["hd"], wl["layers"], wl["ctx"]
+    H, KV, hd, layers, L = wl["H"], wl["KV"], wl["hd"], wl["layers"] * copies, wl["ctx"]
+    es = 2 if kv_format == "bf16" else 4
+    rng = np.random.default_rng(2100)
+    kw = {}
+    if wl["qk_norm"]:
+        kw = dict(q_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32),
+                  k_norm=(1 + 0.02 * rng.standard_normal(hd)).astype(np.float32))
     blocks = []
     for l in range(layers):
-        b = S.LlamaAttention(ctx, H, KV, hd, wl["theta"], 1e-5, initial_capacity=L + steps + warm + 8)
+        b = S.LlamaAttention(ctx, H, KV, hd, wl["theta"], 1e-5, initial_capacity=L + steps + warm + 8,
+                             kv_format=kv_format, **kw)
         b.cache.fill_normal(L, 2101 + l)
         blocks.append(b)
     g = torch.Generator(device=dev)
@@ -416,9 +471,10 @@ def short_context_block(S, ctx, dev, stream_obj, steps=128, warm=8):
     for b in blocks:
         b.close()
     peak, kind = measured_peak()
-    bytes_launch = decode_bytes(wl, L + (steps + 1) / 2.0)
+    bytes_launch = decode_bytes(wl, L + (steps + 1) / 2.0, elem_bytes=es)
     us = ms * 1e3 / (steps * layers)
     gbs = bytes_launch / (us * 1e-6) / 1e9
+    ms /= copies   # a step of the model is one pass over its own layers
     return {"workload": wl["name"], "tokens_per_s": steps / (ms / 1e3), "ms_per_step": ms / steps, "steps": steps,
             "roofline": {"bound": "hbm", "kernel": "attn_decode_fused_kernel", "achieved": gbs, "peak": peak,
                          "peak_kind": kind, "unit": "GB/s", "frac": gbs / peak, "bytes_per_launch": bytes_launch,
@@ -640,6 +696,8 @@ def run_one_block(args):
         res = model_decode_block(S, ctx, dev, steps=args.steps if args.steps != 256 else 96)
     elif args.only == "ctx4k":
         res = short_context_block(S, ctx, dev, tstream)
+    elif args.only == "bf16kv":
+        res = bf16_kv_block(S, ctx, dev, tstream)
     elif args.only == "batched":
         res = batched_block(S, ctx, dev, tstream, seqs=args.batched_seqs, layers_resident=args.batched_layers)
     else:
@@ -899,9 +957,10 @@ def run_ours(args, wl, rank, world, local_rank):
         prefill = prefill_block(S, ctx, dev, tstream)
     if not args.no_prefill:
         batched = batched_block(S, ctx, dev, tstream, rank, world, dist)
-    model = gemv = None
+    model = gemv = bf16kv = None
     if world == 1 and not args.no_prefill and args.workload != "cfg2":
         short_ctx = short_context_block(S, ctx, dev, tstream)
+        bf16kv = bf16_kv_block(S, ctx, dev, tstream)
         model = model_decode_block(S, ctx, dev)
         gemv = gemv_block(S, ctx, dev, tstream)
     parity = parity_check(S, ctx, wl, sp, rank, world, dev, stream, dist, peer, layers * world * pay, epoch[0] + 1)
@@ -955,6 +1014,8 @@ def run_ours(args, wl, rank, world, local_rank):
             line["batched_decode"] = batched
         if short_ctx is not None:
             line["decode_ctx4k"] = short_ctx
+        if bf16kv is not None:
+            line["decode_bf16_kv"] = bf16kv
         if model is not None:
             line["decode_model_cfg2"] = model
         if gemv is not None:
@@ -995,7 +1056,7 @@ def main():
                     help="override 'query_heads,kv_heads' (debugging: e.g. 8,1 on 2 ranks runs the sequence-split path)")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="several ranks: gather head outputs with torch.distributed instead of the kernel's peer stores")
-    ap.add_argument("--only", default=None, choices=["model", "gemv", "ctx4k", "batched", "prefill"],
+    ap.add_argument("--only", default=None, choices=["model", "gemv", "ctx4k", "bf16kv", "batched", "prefill"],
                     help="run one secondary block alone on one GPU and print its JSON object")
     ap.add_argument("--batched-seqs", type=int, default=None, help="--only batched: sequences in the batch (profiling: a small resident case)")
     ap.add_argument("--batched-layers", type=int, default=None, help="--only batched: resident layers")

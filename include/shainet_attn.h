@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define SHAINET_ATTN_VERSION 100
+#define SHAINET_ATTN_VERSION 101
 
 #define SHAINET_ATTN_OK 0
 #define SHAINET_ATTN_E_INVALID (-1)      /* bad argument / shape / null pointer / misaligned pointer */
@@ -92,6 +92,25 @@ int shainet_attn_ctx_timing_read(shainet_attn_ctx* ctx, double* total_ms, int* l
  * RoPE defaults to theta = 10000 as LlamaBlock.new does (:74). */
 int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
                            int head_dim, int initial_capacity);
+/* Element format of the cache rows.  The reference keeps fp32 rows only
+ * (Array(Array(Float32)), llama_block.cr:45-48; float buffers, :50-56), so F32 is what
+ * shainet_attn_kv_create makes and what every parity statement about the reference
+ * refers to.  BF16 has no counterpart in the reference: it is an opt-in that halves the
+ * bytes a decode step streams.  With it the rotated k row and the v row of every new
+ * token are rounded to bfloat16 (round to nearest, ties to even) as they are appended,
+ * and attention - still fp32 arithmetic, fp32 q, fp32 output - runs over the rounded
+ * rows, the new token's own row included.  The result is therefore what the F32 path
+ * gives on a cache whose rows were rounded that way, not what the reference gives on
+ * unrounded rows.  Every entry that takes a cache accepts either format (single-token
+ * decode and batched decode read bfloat16 directly; the other kernels read an fp32 image
+ * of the rows that the context keeps as scratch) except shainet_attn_kv_device_ptrs
+ * and batched decode with a kernel-forcing flag, which answer
+ * SHAINET_ATTN_E_UNSUPPORTED.  kv_export widens exactly; kv_import and kv_fill_normal round. */
+#define SHAINET_ATTN_KV_F32 0
+#define SHAINET_ATTN_KV_BF16 1
+int shainet_attn_kv_create_fmt(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                               int head_dim, int initial_capacity, int format);
+int shainet_attn_kv_format(const shainet_attn_kv* kv);       /* SHAINET_ATTN_KV_*, or negative status */
 int shainet_attn_kv_destroy(shainet_attn_kv* kv);
 int shainet_attn_kv_reset(shainet_attn_kv* kv);              /* clear_cache!: length 0, buffers kept */
 int shainet_attn_kv_len(const shainet_attn_kv* kv);          /* @cache_len, or negative status */
@@ -125,7 +144,7 @@ int shainet_attn_kv_import(shainet_attn_kv* kv, const float* k_host, const float
 /* Fills len positions of K and V with N(0,1) values generated on the device
  * from seed and sets the length (synthetic long contexts for benchmarks). */
 int shainet_attn_kv_fill_normal(shainet_attn_kv* kv, int len, uint64_t seed);
-/* Raw device pointers of the current buffers (invalidated by growth). */
+/* Raw device pointers of the current buffers (invalidated by growth); F32 caches only. */
 int shainet_attn_kv_device_ptrs(shainet_attn_kv* kv, float** k_dev, float** v_dev);
 
 /* ---- the drop-in for attention_heads_gpu (llama_block.cr:407-479) and the

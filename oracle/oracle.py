@@ -41,6 +41,8 @@ def lib():
     L.oracle_block_set_qk_norm.argtypes = [P, F, F]
     L.oracle_block_set_bias.argtypes = [P, F, F, F]
     L.oracle_block_clear.argtypes = [P]
+    L.oracle_block_set_kv_rounding.argtypes = [P, I]
+    L.oracle_round_bf16.argtypes = [F, C.c_size_t, F]
     L.oracle_block_len.argtypes = [P]
     L.oracle_block_len.restype = I
     L.oracle_inv_freq.argtypes = [P, F]
@@ -66,13 +68,21 @@ def lib():
     return L
 
 
+def round_bf16(x) -> np.ndarray:
+    """fp32 -> bfloat16 -> fp32, round to nearest even."""
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().oracle_round_bf16(_fp(x), x.size, _fp(out))
+    return out
+
+
 class OracleAttention:
     """The attention state of the reference's ``LlamaBlock`` (per-kv-head growing
     K/V arrays and ``cache_len``; src/shainet/transformer/llama_block.cr:45-48)
     with its cached and uncached attention between the projections and o_proj."""
 
     def __init__(self, num_heads, num_kv_heads, head_dim, rope_theta=10000.0, eps=1e-6,
-                 rope_freqs=None, q_norm=None, k_norm=None, b_q=None, b_k=None, b_v=None):
+                 rope_freqs=None, q_norm=None, k_norm=None, b_q=None, b_k=None, b_v=None, kv_rounding=None):
         self.L = lib()
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.q_dim, self.kv_dim = num_heads * head_dim, num_kv_heads * head_dim
@@ -80,6 +90,10 @@ class OracleAttention:
         if not self.h:
             raise ValueError("bad head configuration")
         self._keep = []
+        if kv_rounding not in (None, "bf16"):
+            raise ValueError("kv_rounding is None (the reference's fp32 rows) or 'bf16'")
+        if kv_rounding == "bf16":   # not a reference behaviour: the library's opt-in 16-bit cache, restated
+            self.L.oracle_block_set_kv_rounding(self.h, 1)
         if rope_freqs is not None:
             f = _f32(rope_freqs)
             self.L.oracle_block_set_rope_freqs(self.h, _fp(f))

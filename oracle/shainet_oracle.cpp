@@ -51,6 +51,11 @@ struct Block {
     // src/shainet/transformer/llama_block.cr:45-48 — one growing array per kv head
     std::vector<std::vector<float>> k_cache, v_cache;
     int cache_len = 0;
+    // 0: rows are kept as computed (the reference).  1: every row is rounded to bfloat16
+    // as it enters the cache.  Mode 1 has no counterpart in the reference: it states what
+    // the library's opt-in 16-bit cache format is defined to compute, namely the
+    // reference's arithmetic over rows rounded that way.
+    int kv_rounding = 0;
 
     int q_dim() const { return num_heads * head_dim; }
     int kv_dim() const { return num_kv_heads * head_dim; }
@@ -62,6 +67,23 @@ struct Block {
         return (float)(1.0 / std::pow(rope_theta, e));
     }
 };
+
+// fp32 -> bfloat16 -> fp32, round to nearest, ties to even (NaN stays NaN).
+inline float round_bf16(float x) {
+    uint32_t u;
+    std::memcpy(&u, &x, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return x;
+    u += 0x7fffu + ((u >> 16) & 1u);
+    u &= 0xffff0000u;
+    float y;
+    std::memcpy(&y, &u, 4);
+    return y;
+}
+
+inline void round_rows(const Block& b, float* p, size_t n) {
+    if (b.kv_rounding == 1)
+        for (size_t i = 0; i < n; ++i) p[i] = round_bf16(p[i]);
+}
 
 // src/shainet/transformer/llama_block.cr:585-601
 void add_bias(float* m, int rows, int cols, const float* b) {
@@ -245,6 +267,14 @@ void oracle_block_set_bias(void* p, const float* bq, const float* bk, const floa
     if (bv) b->b_v.assign(bv, bv + b->kv_dim());
 }
 
+// mode 0 = the reference's fp32 rows; 1 = rows rounded to bfloat16 on entry (not a
+// reference behaviour, see Block::kv_rounding).  Affects rows appended or imported later.
+void oracle_block_set_kv_rounding(void* p, int mode) { ((Block*)p)->kv_rounding = mode == 1 ? 1 : 0; }
+
+void oracle_round_bf16(const float* x, size_t n, float* out) {
+    for (size_t i = 0; i < n; ++i) out[i] = round_bf16(x[i]);
+}
+
 // src/shainet/transformer/llama_block.cr:116-122
 void oracle_block_clear(void* p) {
     Block* b = (Block*)p;
@@ -268,6 +298,8 @@ void oracle_block_import(void* p, const float* k, const float* v, int len) {
     for (int h = 0; h < b->num_kv_heads; ++h) {
         b->k_cache[h].assign(k + h * per, k + (h + 1) * per);
         b->v_cache[h].assign(v + h * per, v + (h + 1) * per);
+        round_rows(*b, b->k_cache[h].data(), per);
+        round_rows(*b, b->v_cache[h].data(), per);
     }
     b->cache_len = len;
 }
@@ -308,8 +340,10 @@ void oracle_block_attend_cached(void* p, const float* q_in, const float* k_in, c
         for (int t = 0; t < new_tokens; ++t) {
             std::fill(rotated.begin(), rotated.end(), 0.0f);
             rope_row(*b, k.data() + (size_t)t * kvd + kv_col, start_pos + t, rotated.data());
+            round_rows(*b, rotated.data(), rotated.size());
             b->k_cache[kv_h].insert(b->k_cache[kv_h].end(), rotated.begin(), rotated.end());
-            const float* vr = v.data() + (size_t)t * kvd + kv_col;
+            float* vr = v.data() + (size_t)t * kvd + kv_col;
+            round_rows(*b, vr, hd);
             b->v_cache[kv_h].insert(b->v_cache[kv_h].end(), vr, vr + hd);
         }
     }

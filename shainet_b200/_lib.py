@@ -30,6 +30,8 @@ SIGNATURES = {
     "shainet_attn_ctx_timing_enable": (C.c_int, [_P, C.c_int]),
     "shainet_attn_ctx_timing_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "shainet_attn_kv_create": (C.c_int, [_P, C.POINTER(_P), C.c_int, C.c_int, C.c_int, C.c_int]),
+    "shainet_attn_kv_create_fmt": (C.c_int, [_P, C.POINTER(_P), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "shainet_attn_kv_format": (C.c_int, [_P]),
     "shainet_attn_kv_destroy": (C.c_int, [_P]),
     "shainet_attn_kv_reset": (C.c_int, [_P]),
     "shainet_attn_kv_len": (C.c_int, [_P]),

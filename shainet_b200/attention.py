@@ -126,14 +126,30 @@ class AttnContext:
             self.h = None
 
 
+KV_FORMATS = {"f32": 0, "bf16": 1}
+
+
 class KVCache:
-    def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int, head_dim: int, initial_capacity: int = 0):
+    """One block's device KV cache.  ``kv_format`` "f32" is the reference's layout
+    (llama_block.cr:45-56); "bf16" is this library's opt-in that rounds the rows to
+    bfloat16 as they are appended (no counterpart in the reference)."""
+
+    def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int, head_dim: int, initial_capacity: int = 0,
+                 kv_format: str = "f32"):
         self.ctx, self.L = ctx, ctx.L
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.q_dim, self.kv_dim = num_heads * head_dim, num_kv_heads * head_dim
+        if kv_format not in KV_FORMATS:
+            raise ValueError(f"kv_format must be one of {sorted(KV_FORMATS)}")
         h = C.c_void_p()
-        check(self.L.shainet_attn_kv_create(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim, initial_capacity))
+        check(self.L.shainet_attn_kv_create_fmt(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim, initial_capacity,
+                                                KV_FORMATS[kv_format]))
         self.h = h
+
+    @property
+    def kv_format(self) -> str:
+        code = check(self.L.shainet_attn_kv_format(self.h))
+        return {v: k for k, v in KV_FORMATS.items()}[code]
 
     def close(self):
         if getattr(self, "h", None):
@@ -203,10 +219,10 @@ class LlamaAttention:
 
     def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int | None = None, head_dim: int = 64,
                  rope_theta: float = 10000.0, eps: float = 1e-6, rope_freqs=None, q_norm=None, k_norm=None,
-                 b_q=None, b_k=None, b_v=None, initial_capacity: int = 0):
+                 b_q=None, b_k=None, b_v=None, initial_capacity: int = 0, kv_format: str = "f32"):
         num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
         self.ctx = ctx
-        self.cache = KVCache(ctx, num_heads, num_kv_heads, head_dim, initial_capacity)
+        self.cache = KVCache(ctx, num_heads, num_kv_heads, head_dim, initial_capacity, kv_format)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.q_dim, self.kv_dim = self.cache.q_dim, self.cache.kv_dim
         self.scale = default_scale(head_dim)

@@ -66,7 +66,8 @@ int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
     const long long want = std::max<long long>(256, std::max<long long>(total_len, 2ll * kv->cap));
     if (want > 0x7fffffffll) return fail(SHAINET_ATTN_E_INVALID, "cache capacity overflow");
     const int new_cap = (int)want;
-    const size_t bytes = (size_t)kv->hs.num_kv_heads * new_cap * kv->hs.head_dim * sizeof(float);
+    const size_t es = (size_t)kv->es;
+    const size_t bytes = (size_t)kv->hs.num_kv_heads * new_cap * kv->hs.head_dim * es;
     float *nk = nullptr, *nv = nullptr;
     cudaError_t e = cudaMalloc(&nk, bytes);
     if (e != cudaSuccess) return fail_cuda(e, "cudaMalloc(k cache)");
@@ -80,9 +81,9 @@ int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
     e = cudaMemsetAsync(nk, 0, bytes, s);
     if (e == cudaSuccess) e = cudaMemsetAsync(nv, 0, bytes, s);
     if (e == cudaSuccess && kv->k && kv->len > 0) {
-        const size_t row_bytes = (size_t)kv->len * kv->hs.head_dim * sizeof(float);
-        const size_t src_pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
-        const size_t dst_pitch = (size_t)new_cap * kv->hs.head_dim * sizeof(float);
+        const size_t row_bytes = (size_t)kv->len * kv->hs.head_dim * es;
+        const size_t src_pitch = (size_t)kv->cap * kv->hs.head_dim * es;
+        const size_t dst_pitch = (size_t)new_cap * kv->hs.head_dim * es;
         e = cudaMemcpy2DAsync(nk, dst_pitch, kv->k, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s);
         if (e == cudaSuccess)
             e = cudaMemcpy2DAsync(nv, dst_pitch, kv->v, src_pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToDevice, s);
@@ -157,8 +158,8 @@ int pick_kernel(const HeadShape& hs, int batch, int T, unsigned flags, Kernel* o
 
 // Rows of cache per split so that about one CTA lands on every SM.
 void plan_splits(int sm_count, const HeadShape& hs, int rows, long long total_visible, int max_visible,
-                 int waves, int* chunk_rows, int* max_splits) {
-    const int tw = splitk_tile_rows(hs);
+                 int waves, int* chunk_rows, int* max_splits, int kv_elem_bytes = 4) {
+    const int tw = splitk_tile_rows(hs, kv_elem_bytes);
     const long long ctas = std::max<long long>(1, (long long)sm_count * splitk_ctas_per_sm(hs) * waves);
     long long chunk = (total_visible * hs.num_kv_heads + ctas - 1) / ctas;
     const long long min_chunk = 4ll * tw;  // one tile per consumer warp
@@ -255,6 +256,8 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
         ctx->gather_armed = false;
         return fail(SHAINET_ATTN_E_UNSUPPORTED, "peer delivery is done by the fused decode kernel only (one new token, head_dim 64/128)");
     }
+    if (!fused && par->es != 4 && seqs.many != nullptr)
+        return fail(SHAINET_ATTN_E_UNSUPPORTED, "batched decode over bfloat16 caches is served by the fused decode kernel only");
     if (!fused) {
         ctx->last_fused = false;
         rc = grow(ctx->q_rot, (size_t)batch * T * hs.num_heads * hs.head_dim, s);
@@ -279,8 +282,25 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
         rc = pick_kernel(hs, batch, T, flags, &kern);
         if (rc) return rc;
         p.round_q_tf32 = kern == Kernel::Tensor ? 1 : 0;
+        p.kv_elem_bytes = par->es;
         p.status = ctx->status_dev;
         CU(launch_prep_append(p, s));
+        if (par->es != 4) {
+            // These attention kernels read fp32 rows.  A bfloat16 cache is widened (exactly) into
+            // a scratch image first; the capacity of the image is a whole number of the
+            // tensor-core kernel's 128-row tiles, and it never holds anything but finite values.
+            const int cap_s = (max_visible + 127) / 128 * 128;
+            const size_t per = (size_t)hs.num_kv_heads * cap_s * hs.head_dim;
+            float* before = ctx->kv_f32.p;
+            rc = grow(ctx->kv_f32, 2 * per, s);
+            if (rc) return rc;
+            if (ctx->kv_f32.p != before) CU(cudaMemsetAsync(ctx->kv_f32.p, 0, ctx->kv_f32.cap * sizeof(float), s));
+            float* wk = ctx->kv_f32.p;
+            float* wv = wk + per;
+            CU(launch_kv_convert(seqs.one.k, par->es, seqs.one.capacity, wk, 4, cap_s, hs.num_kv_heads, hs.head_dim, 0, max_visible, s));
+            CU(launch_kv_convert(seqs.one.v, par->es, seqs.one.capacity, wv, 4, cap_s, hs.num_kv_heads, hs.head_dim, 0, max_visible, s));
+            seqs.one = SeqDesc{wk, wv, seqs.one.start, cap_s};
+        }
         return run_attention(ctx, hs, seqs, batch, T, total_visible, max_visible, ctx->q_rot.p, out, scale, flags, s);
     }
     FusedArgs f{};
@@ -300,7 +320,7 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     f.hs = hs;
     f.scale = scale;
     f.status = ctx->status_dev;
-    plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits);
+    plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits, par->es);
     f.max_groups = fused_merge_groups(f.max_splits);
     // A single sequence whose grid is fully resident merges through {value, epoch} words
     // (8 bytes per partial float) polled by the merging CTAs; batched decode keeps float
@@ -348,6 +368,7 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     ctx->rows_rewound = false;
     f.pos_delta = pos_delta;
     f.no_append = no_append;
+    f.kv_elem_bytes = par->es;
     f.lse_out = ctx->lse_out;
     f.gather.world = 0;
     if (ctx->gather_armed) {
@@ -488,7 +509,7 @@ int shainet_attn_ctx_destroy(shainet_attn_ctx* c) {
     if (c->live_caches != 0) return fail(SHAINET_ATTN_E_STATE, "%d caches still alive", c->live_caches);
     DeviceGuard g(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    for (DevBuf* b : {&c->q_rot, &c->part, &c->part_words, &c->dev_in, &c->dev_out})
+    for (DevBuf* b : {&c->q_rot, &c->part, &c->part_words, &c->dev_in, &c->dev_out, &c->kv_f32})
         if (b->p) cudaFree(b->p);
     if (c->pin_in) cudaFreeHost(c->pin_in);
     if (c->pin_out) cudaFreeHost(c->pin_out);
@@ -544,13 +565,25 @@ int shainet_attn_ctx_timing_read(shainet_attn_ctx* c, double* total_ms, int* lau
 
 size_t shainet_attn_ctx_scratch_bytes(shainet_attn_ctx* c) {
     if (!c) return 0;
-    return (c->q_rot.cap + c->part.cap + c->part_words.cap + c->dev_in.cap + c->dev_out.cap) * sizeof(float);
+    return (c->q_rot.cap + c->part.cap + c->part_words.cap + c->dev_in.cap + c->dev_out.cap + c->kv_f32.cap) * sizeof(float);
 }
 
 int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
                            int head_dim, int initial_capacity) {
+    return shainet_attn_kv_create_fmt(ctx, out, num_heads, num_kv_heads, head_dim, initial_capacity, SHAINET_ATTN_KV_F32);
+}
+
+int shainet_attn_kv_format(const shainet_attn_kv* kv) {
+    if (!kv) return fail(SHAINET_ATTN_E_INVALID, "null cache");
+    return kv->es == 2 ? SHAINET_ATTN_KV_BF16 : SHAINET_ATTN_KV_F32;
+}
+
+int shainet_attn_kv_create_fmt(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                               int head_dim, int initial_capacity, int format) {
     if (!ctx || !out) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
     *out = nullptr;
+    if (format != SHAINET_ATTN_KV_F32 && format != SHAINET_ATTN_KV_BF16)
+        return fail(SHAINET_ATTN_E_INVALID, "unknown cache format %d", format);
     // LlamaBlock.new's checks (llama_block.cr:80-89)
     if (num_kv_heads <= 0 || num_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail(SHAINET_ATTN_E_INVALID, "num_heads must be divisible by num_kv_heads");
@@ -563,6 +596,7 @@ int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num
     if (!kv) return fail(SHAINET_ATTN_E_NOMEM, "out of host memory");
     kv->ctx = ctx;
     kv->hs = HeadShape{num_heads, num_kv_heads, head_dim};
+    kv->es = format == SHAINET_ATTN_KV_BF16 ? 2 : 4;
     ctx->live_caches++;
     int rc = shainet_attn_kv_set_rope_theta(kv, 10000.0);
     if (rc == SHAINET_ATTN_OK && initial_capacity > 0) rc = kv_ensure(kv, initial_capacity, ctx->stream);
@@ -662,8 +696,25 @@ int shainet_attn_kv_export(shainet_attn_kv* kv, float* k_host, float* v_host, in
     if (len < 0 || len > kv->len) return fail(SHAINET_ATTN_E_STATE, "export of %d rows from a cache of %d", len, kv->len);
     if (len == 0) return SHAINET_ATTN_OK;
     DeviceGuard g(kv->ctx->device);
-    CU(cudaStreamSynchronize(kv->ctx->stream));
+    cudaStream_t s = kv->ctx->stream;
+    CU(cudaStreamSynchronize(s));
     const size_t row_bytes = (size_t)len * kv->hs.head_dim * sizeof(float);
+    if (kv->es != 4) {
+        // widened (exactly) on the device, one tensor at a time, through the context's fp32 image
+        const size_t per = (size_t)kv->hs.num_kv_heads * len * kv->hs.head_dim;
+        float* before = kv->ctx->kv_f32.p;
+        int rc = grow(kv->ctx->kv_f32, per, s);
+        if (rc) return rc;
+        if (kv->ctx->kv_f32.p != before) CU(cudaMemsetAsync(kv->ctx->kv_f32.p, 0, kv->ctx->kv_f32.cap * sizeof(float), s));
+        float* host[2] = {k_host, v_host};
+        const float* dev[2] = {kv->k, kv->v};
+        for (int t = 0; t < 2; ++t) {
+            CU(launch_kv_convert(dev[t], kv->es, kv->cap, kv->ctx->kv_f32.p, 4, len, kv->hs.num_kv_heads, kv->hs.head_dim, 0, len, s));
+            CU(cudaMemcpyAsync(host[t], kv->ctx->kv_f32.p, per * sizeof(float), cudaMemcpyDeviceToHost, s));
+            CU(cudaStreamSynchronize(s));
+        }
+        return SHAINET_ATTN_OK;
+    }
     const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
     CU(cudaMemcpy2D(k_host, row_bytes, kv->k, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
     CU(cudaMemcpy2D(v_host, row_bytes, kv->v, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
@@ -677,7 +728,22 @@ int shainet_attn_kv_import(shainet_attn_kv* kv, const float* k_host, const float
     kv->len = 0;
     int rc = kv_ensure(kv, len, kv->ctx->stream);
     if (rc) return rc;
-    if (len > 0) {
+    if (len > 0 && kv->es != 4) {
+        // uploaded as fp32, one tensor at a time, and rounded to bfloat16 (nearest even) on the device
+        cudaStream_t s = kv->ctx->stream;
+        const size_t per = (size_t)kv->hs.num_kv_heads * len * kv->hs.head_dim;
+        float* before = kv->ctx->kv_f32.p;
+        rc = grow(kv->ctx->kv_f32, per, s);
+        if (rc) return rc;
+        if (kv->ctx->kv_f32.p != before) CU(cudaMemsetAsync(kv->ctx->kv_f32.p, 0, kv->ctx->kv_f32.cap * sizeof(float), s));
+        const float* host[2] = {k_host, v_host};
+        float* dev[2] = {kv->k, kv->v};
+        for (int t = 0; t < 2; ++t) {
+            CU(cudaMemcpyAsync(kv->ctx->kv_f32.p, host[t], per * sizeof(float), cudaMemcpyHostToDevice, s));
+            CU(launch_kv_convert(kv->ctx->kv_f32.p, 4, len, dev[t], kv->es, kv->cap, kv->hs.num_kv_heads, kv->hs.head_dim, 0, len, s));
+            CU(cudaStreamSynchronize(s));
+        }
+    } else if (len > 0) {
         CU(cudaStreamSynchronize(kv->ctx->stream));
         const size_t row_bytes = (size_t)len * kv->hs.head_dim * sizeof(float);
         const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
@@ -695,8 +761,8 @@ int shainet_attn_kv_fill_normal(shainet_attn_kv* kv, int len, uint64_t seed) {
     kv->len = 0;
     int rc = kv_ensure(kv, len, kv->ctx->stream);
     if (rc) return rc;
-    CU(launch_fill_normal(kv->k, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed, kv->ctx->stream));
-    CU(launch_fill_normal(kv->v, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed + 1, kv->ctx->stream));
+    CU(launch_fill_normal(kv->k, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed, kv->es, kv->ctx->stream));
+    CU(launch_fill_normal(kv->v, kv->hs.num_kv_heads, kv->cap, kv->hs.head_dim, len, 2 * seed + 1, kv->es, kv->ctx->stream));
     CU(cudaStreamSynchronize(kv->ctx->stream));
     kv->len = len;
     return SHAINET_ATTN_OK;
@@ -704,6 +770,7 @@ int shainet_attn_kv_fill_normal(shainet_attn_kv* kv, int len, uint64_t seed) {
 
 int shainet_attn_kv_device_ptrs(shainet_attn_kv* kv, float** k_dev, float** v_dev) {
     if (!kv || !k_dev || !v_dev) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    if (kv->es != 4) return fail(SHAINET_ATTN_E_UNSUPPORTED, "the rows of a bfloat16 cache are not fp32: use shainet_attn_kv_export");
     *k_dev = kv->k;
     *v_dev = kv->v;
     return SHAINET_ATTN_OK;
@@ -965,6 +1032,7 @@ int shainet_attn_forward_batched_dev(shainet_attn_ctx* ctx, shainet_attn_kv* con
         if (kv->hs.num_heads != first->hs.num_heads || kv->hs.num_kv_heads != first->hs.num_kv_heads ||
             kv->hs.head_dim != first->hs.head_dim)
             return fail(SHAINET_ATTN_E_INVALID, "cache %d has a different head shape", b);
+        if (kv->es != first->es) return fail(SHAINET_ATTN_E_INVALID, "cache %d has a different element format", b);
         for (int c = 0; c < b; ++c)
             if (kvs[c] == kv) return fail(SHAINET_ATTN_E_INVALID, "cache %d appears twice in the batch", b);
         if (kv->len == 0x7fffffff) return fail(SHAINET_ATTN_E_INVALID, "cache length overflow");

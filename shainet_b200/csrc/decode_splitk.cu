@@ -33,6 +33,7 @@
 //
 // All waits are bounded (see mbar_wait); a timed-out wait records a status
 // word and the kernel unwinds.
+#include <cuda_bf16.h>
 #include <math.h>
 #include <stdio.h>
 #include <atomic>
@@ -77,6 +78,30 @@ __device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
 
 __device__ __forceinline__ ulonglong2 lds128x2(const void* p) { return *reinterpret_cast<const ulonglong2*>(p); }
 
+// Four consecutive cache elements, starting at element `elem` of a shared-memory tile, as
+// two packed fp32 pairs.  ES = 4: fp32 rows, one 16-byte load.  ES = 2: bfloat16 rows, one
+// 8-byte load; a bfloat16 is the upper half of the fp32 of the same value, so each pair
+// costs a shift and a mask.
+template <int ES>
+__device__ __forceinline__ ulonglong2 lds_kv4(const float* tile, size_t elem) {
+    if constexpr (ES == 4) {
+        return lds128x2(tile + elem);
+    } else {
+        const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(tile) + elem);
+        ulonglong2 r;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(r.x) : "r"(w.x << 16), "r"(w.x & 0xffff0000u));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(r.y) : "r"(w.y << 16), "r"(w.y & 0xffff0000u));
+        return r;
+    }
+}
+
+// The value a cache of element size ES keeps for x.
+template <int ES>
+__device__ __forceinline__ float kv_rounded(float x) {
+    if constexpr (ES == 4) return x;
+    else return __bfloat162float(__float2bfloat16_rn(x));
+}
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -95,16 +120,17 @@ struct SKDefault {
     static constexpr int CTAS_PER_SM = BIG ? 1 : 2;
 };
 
-template <int HD, int G, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
+template <int HD, int G, int ES_ = 4, int TW_ = SKDefault<HD, G>::TW, int NW_ = SKDefault<HD, G>::NW,
           int SMEM_KB_ = SKDefault<HD, G>::SMEM_KB, int CTAS_ = SKDefault<HD, G>::CTAS_PER_SM>
 struct SK {
+    static constexpr int ES = ES_;                     // bytes per cache element: 4 (fp32) or 2 (bfloat16)
     static constexpr int NW = NW_;                     // consumer warps
     static constexpr int CPL = HD / 64;                // 16-byte chunks per lane per K row
     static constexpr int R = 16 / G;                   // rows per half-warp per batch
     static constexpr int BR = 2 * R;                   // rows per batch
     static constexpr int TW = TW_;                     // rows per warp tile
     static constexpr int NB = TW / BR;                 // batches per tile
-    static constexpr int TILE_FLOATS = TW * HD;        // per tensor
+    static constexpr int TILE_FLOATS = TW * HD * ES / 4;   // per tensor, in 4-byte units
     static constexpr int STAGE_FLOATS = 2 * TILE_FLOATS;
     static constexpr int RPI = 128 / HD;               // V rows covered by one warp-wide 128-bit load
     static constexpr int WARP_SCRATCH = 2 * 2 * (32 + 16); // two buffers of (p,p)[BR*G = 32] + (alpha,alpha)[G <= 16], as floats
@@ -125,11 +151,18 @@ struct SK {
     static constexpr int MERGE_FLOATS = NW * G * (HD + 2);
     static constexpr size_t SMEM_BYTES = (size_t)NS * STAGE_FLOATS * 4 + FIXED_BYTES;
     static_assert(HD == 64 || HD == 128, "head_dim");
+    static_assert(ES == 4 || ES == 2, "cache element size");
     static_assert(G == 1 || G == 2 || G == 4 || G == 8 || G == 16, "group size");
     static_assert(TW % BR == 0, "a warp tile is a whole number of batches");
     static_assert(NS >= NW, "ring shorter than the number of consumer warps");
     static_assert(MERGE_FLOATS <= NS * STAGE_FLOATS, "merge area must fit in the ring");
 };
+
+// bfloat16 caches: a warp tile of twice the rows, so that a bulk copy moves as many bytes
+// as with fp32 rows and twice the batches overlap inside a tile (batched decode on the
+// Qwen3-8B shape: 0.49 ms per layer against 0.77 ms with the fp32 kernel's row count).
+template <int HD, int G>
+using SKB = SK<HD, G, 2, 2 * SKDefault<HD, G>::TW>;
 
 // Carve-up of the dynamic shared memory, common to both kernels.
 template <class C>
@@ -208,10 +241,10 @@ __device__ __forceinline__ void score_batch(const float* ks, int base, int hw, i
     for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
 #pragma unroll
     for (int rr = 0; rr < C::R; ++rr) {
-        const float* krow = ks + (size_t)(base + hw * C::R + rr) * HD;
+        const size_t krow = (size_t)(base + hw * C::R + rr) * HD;
 #pragma unroll
         for (int c = 0; c < C::CPL; ++c) {
-            const ulonglong2 kk = lds128x2(krow + (c * 16 + i16) * 4);
+            const ulonglong2 kk = lds_kv4<C::ES>(ks, krow + (c * 16 + i16) * 4);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
@@ -271,7 +304,7 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
         for (int rr = 0; rr < C::BR; rr += C::RPI) {
             const int rb = rr + (C::RPI == 2 ? hw : 0);
             const int col = (C::RPI == 2 ? i16 : lane) * 4;
-            const ulonglong2 vv = lds128x2(vs + (size_t)(base + rb) * HD + col);
+            const ulonglong2 vv = lds_kv4<C::ES>(vs, (size_t)(base + rb) * HD + col);
             const f32x2* prow = ps + rb * G;
             if constexpr (G >= 2) {
 #pragma unroll
@@ -291,8 +324,8 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
     }
 }
 
-// One warp tile: `nrows` valid rows of K (ks) and V (vs) in shared memory.
-template <int HD, int G, class C>
+// One warp tile: `nrows` valid rows of K (ks) and V (vs) in shared memory, elements of ES bytes.
+template <int HD, int G, class C, int ES>
 __device__ __forceinline__ void consume_tile(const float* ks, const float* vs, int nrows, const ulonglong2 (&q)[G][C::CPL],
                                              WarpState<G>& st, f32x2* ps, f32x2* as, int lane, float scale, int nbatches) {
     const int i16 = lane & 15, hw = lane >> 4;
@@ -308,10 +341,10 @@ __device__ __forceinline__ void consume_tile(const float* ks, const float* vs, i
         for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
 #pragma unroll
         for (int rr = 0; rr < C::R; ++rr) {
-            const float* krow = ks + (size_t)(base + hw * C::R + rr) * HD;
+            const size_t krow = (size_t)(base + hw * C::R + rr) * HD;
 #pragma unroll
             for (int c = 0; c < C::CPL; ++c) {
-                const ulonglong2 kk = lds128x2(krow + (c * 16 + i16) * 4);
+                const ulonglong2 kk = lds_kv4<ES>(ks, krow + (c * 16 + i16) * 4);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
@@ -358,7 +391,7 @@ __device__ __forceinline__ void consume_tile(const float* ks, const float* vs, i
             if (base + rr >= nrows) break;  // warp-uniform
             if (row < nrows) {
                 const int col = (C::RPI == 2 ? i16 : lane) * 4;
-                const ulonglong2 vv = lds128x2(vs + (size_t)row * HD + col);
+                const ulonglong2 vv = lds_kv4<ES>(vs, (size_t)row * HD + col);
                 const f32x2* prow = ps + (row - base) * G;
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
@@ -448,7 +481,7 @@ __device__ __forceinline__ bool produce_tiles(Smem<C>& sm, const float* kbase, c
         const int s = i % C::NS;
         if (i >= C::NS && !mbar_wait(&sm.empty_bar[s], ((i / C::NS) - 1) & 1, status, 1)) return false;
         const int nrows = min(C::TW, rows - i * C::TW);
-        const uint32_t bytes = (uint32_t)nrows * HD * 4;
+        const uint32_t bytes = (uint32_t)nrows * HD * C::ES;
         float* ks = sm.stages + (size_t)s * C::STAGE_FLOATS;
         float* vs = ks + C::TILE_FLOATS;
         mbar_arrive_expect_tx(&sm.full_bar[s], 2 * bytes);
@@ -473,7 +506,7 @@ __device__ __forceinline__ void consume_slice(Smem<C>& sm, int ntiles, int rows,
             consume_full_tile<HD, G, C>(ks, vs, q, st, ps, lane, scale);
         } else {
             __syncwarp();
-            consume_tile<HD, G, C>(ks, vs, nrows, q, st, ps, as, lane, scale, C::NB);
+            consume_tile<HD, G, C, C::ES>(ks, vs, nrows, q, st, ps, as, lane, scale, C::NB);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty_bar[s]);
@@ -497,6 +530,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_splitk_kernel
     const int row1 = min(row0 + a.chunk_rows, visible);
     const int rows = row1 - row0;
     const int ntiles = (rows + C::TW - 1) / C::TW;
+    static_assert(C::ES == 4, "the plain split-K kernel reads fp32 caches");
     const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
     const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -833,8 +867,10 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
     const int safe_end = start - a.unsafe_tail;
     const int n_safe = min(ntiles, row0 + rows <= safe_end ? ntiles : max(0, (safe_end - row0) / C::TW));
     const int n_early = a.inputs_ready ? n_safe : min(n_safe, C::NS);
-    const float* kbase = sd.k + ((size_t)kv_h * sd.capacity + row0) * HD;
-    const float* vbase = sd.v + ((size_t)kv_h * sd.capacity + row0) * HD;
+    // element size C::ES: a bfloat16 cache is addressed through the same (float-typed) pointers
+    const size_t slice_off = ((size_t)kv_h * sd.capacity + row0) * HD * C::ES;
+    const float* kbase = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(sd.k) + slice_off);
+    const float* vbase = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(sd.v) + slice_off);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     init_barriers(sm);
 
@@ -948,12 +984,23 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
                     x[n][k + PL] = __fadd_rn(__fmul_rn(x1, rc[k]), __fmul_rn(x0, rs[k]));
                 }
             }
+            if (it >= G) {  // the new row is attended to as the cache will hold it
+#pragma unroll
+                for (int c = 0; c < 2 * PL; ++c) x[n][c] = kv_rounded<C::ES>(x[n][c]);
+            }
 #pragma unroll
             for (int c = 0; c < 2 * PL; ++c) row[lane + 32 * c] = x[n][c];
             if (it >= G) {  // append to the cache
-                float* dst = (it == G ? sd.k : sd.v) + ((size_t)kv_h * sd.capacity + start) * HD;
+                const size_t e0 = ((size_t)kv_h * sd.capacity + start) * HD;
+                if constexpr (C::ES == 4) {
+                    float* dst = (it == G ? sd.k : sd.v) + e0;
 #pragma unroll
-                for (int c = 0; c < 2 * PL; ++c) dst[lane + 32 * c] = x[n][c];
+                    for (int c = 0; c < 2 * PL; ++c) dst[lane + 32 * c] = x[n][c];
+                } else {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(it == G ? sd.k : sd.v) + e0;
+#pragma unroll
+                    for (int c = 0; c < 2 * PL; ++c) dst[lane + 32 * c] = __float2bfloat16_rn(x[n][c]);
+                }
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(C::NW * 32) : "memory");  // consumers only: qs/xk/xv complete
@@ -963,7 +1010,7 @@ __global__ void __launch_bounds__(C::THREADS, C::CTAS_PER_SM) attn_decode_fused_
         if (owns_new && warp == (ntiles % C::NW)) {
             // the new token's own row, from shared memory (one valid row)
             f32x2* ps = reinterpret_cast<f32x2*>(sm.warp_scratch + warp * C::WARP_SCRATCH);
-            consume_tile<HD, G, C>(sm.xk, sm.xv, 1, q, st, ps, ps + 32, lane, a.scale, 1);
+            consume_tile<HD, G, C, 4>(sm.xk, sm.xv, 1, q, st, ps, ps + 32, lane, a.scale, 1);
         }
         finish_warp<HD, G, C>(st);
     }
@@ -1292,14 +1339,15 @@ bool splitk_supported(const HeadShape& hs) {
     return (hs.head_dim == 64 || hs.head_dim == 128) && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16);
 }
 
-int splitk_tile_rows(const HeadShape& hs) {
+int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes) {
     const int g = hs.num_heads / hs.num_kv_heads;
     const int br = 2 * (16 / g);
-    return br > 8 ? br : 8;  // SKDefault::TW
+    const int tw = br > 8 ? br : 8;          // SKDefault::TW
+    return kv_elem_bytes == 2 ? 2 * tw : tw;  // SKB
 }
 
 int splitk_ctas_per_sm(const HeadShape& hs) {
-    return 2 * splitk_tile_rows(hs) * hs.head_dim * 4 > 16 * 1024 ? 1 : 2;  // SKDefault::CTAS_PER_SM
+    return 2 * splitk_tile_rows(hs, 4) * hs.head_dim * 4 > 16 * 1024 ? 1 : 2;  // SKDefault::CTAS_PER_SM
 }
 
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits) {
@@ -1317,6 +1365,14 @@ cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s) {
 
 cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s) {
     if (a.batch == 0) return cudaSuccess;
+    if (a.kv_elem_bytes == 2) {
+        if (a.hs.head_dim == 64)
+            return dispatch_g(a, [&](auto g) { return launch_fused<64, decltype(g)::value, SKB<64, decltype(g)::value>>(a, s); });
+        if (a.hs.head_dim == 128)
+            return dispatch_g(a, [&](auto g) { return launch_fused<128, decltype(g)::value, SKB<128, decltype(g)::value>>(a, s); });
+        return cudaErrorInvalidValue;
+    }
+    if (a.kv_elem_bytes != 4) return cudaErrorInvalidValue;
     if (a.hs.head_dim == 64) return dispatch_g(a, [&](auto g) { return launch_fused<64, decltype(g)::value>(a, s); });
     if (a.hs.head_dim == 128) return dispatch_g(a, [&](auto g) { return launch_fused<128, decltype(g)::value>(a, s); });
     return cudaErrorInvalidValue;
@@ -1437,7 +1493,7 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
     a.scale = scale;
     a.status = nullptr;
     const int visible = start_pos + 1;
-    const int tw = splitk_tile_rows(hs);
+    const int tw = splitk_tile_rows(hs, 4);
     const long long ctas = (long long)nd.sm_count * splitk_ctas_per_sm(hs);
     long long chunk = ((long long)visible * hs.num_kv_heads + ctas - 1) / ctas;
     if (chunk < 4ll * tw) chunk = 4ll * tw;

@@ -28,6 +28,7 @@ struct shainet_attn_ctx {
     int sm_count = 148;
     cudaStream_t stream = nullptr;
     shainet::DevBuf q_rot, part, part_words, dev_in, dev_out;
+    shainet::DevBuf kv_f32;             // fp32 image of a bfloat16 cache's rows, for the kernels that read fp32 caches only
     shainet::DevBuf act[6];             // activations of the block / decoder entries (see decoder.cu)   // part_words: {value, epoch} partials of single-sequence decode
     float* pin_in = nullptr;
     size_t pin_in_cap = 0;
@@ -69,8 +70,9 @@ struct shainet_attn_ctx {
 struct shainet_attn_kv {
     shainet_attn_ctx* ctx = nullptr;
     shainet::HeadShape hs{};
-    float* k = nullptr;
+    float* k = nullptr;         // [num_kv_heads, cap, head_dim] elements of `es` bytes (bfloat16 behind a float pointer when es == 2)
     float* v = nullptr;
+    int es = 4;                 // bytes per cache element: 4 = fp32, 2 = bfloat16
     int cap = 0;
     int len = 0;
     float* inv_freq = nullptr;  // device, head_dim/2

@@ -6,8 +6,10 @@
 
 namespace shainet {
 
-// One sequence's device KV cache, [num_kv_heads, capacity, head_dim] fp32 per
-// tensor, and the number of positions held BEFORE the rows of this call.
+// One sequence's device KV cache, [num_kv_heads, capacity, head_dim] per tensor, and
+// the number of positions held BEFORE the rows of this call.  Elements are fp32, or
+// bfloat16 for a cache created in that format: the launch arguments then say so
+// (kv_elem_bytes = 2) and the kernels reinterpret these pointers.
 struct SeqDesc {
     float* k;
     float* v;
@@ -45,6 +47,7 @@ struct PrepArgs {
     int batch, T;
     HeadShape hs;
     int round_q_tf32;      // round the rotated q to nearest TF32 (it feeds the tensor-core prefill kernel)
+    int kv_elem_bytes;     // 4: fp32 cache rows; 2: rows rounded to bfloat16 (nearest even) as they are appended
     AttnStatus* status;    // nullable: receives a bounded wait's failure
 };
 
@@ -111,6 +114,7 @@ struct FusedArgs {
     int inputs_ready;      // caller vouches that q/k_new/v_new do not come from the previous grid
     int pos_delta;         // RoPE position of the new token minus the rows already cached (0 unless the sequence is split over ranks)
     int no_append;         // attend over the cached rows only: k_new/v_new are not used, nothing is appended
+    int kv_elem_bytes;     // 4: fp32 cache; 2: bfloat16 cache (the new row is rounded before it is stored and attended to)
     GatherTarget gather;   // peer delivery of the merged result (world == 0: none)
     float* lse_out;        // nullable [batch, num_heads]: max + ln(sum) of every row's softmax, for merging partial results
     AttnStatus* status;
@@ -125,7 +129,7 @@ cudaError_t launch_attn_generic(const AttnArgs& a, cudaStream_t s);
 
 // Split-K flash-decode for head_dim in {64,128} and group size in {1,2,4,8,16}.
 bool splitk_supported(const HeadShape& hs);
-int splitk_tile_rows(const HeadShape& hs);
+int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes);   // rows per warp tile for fp32 (4) or bfloat16 (2) caches
 int splitk_ctas_per_sm(const HeadShape& hs);
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits);
 int fused_merge_groups(int max_splits);
@@ -156,9 +160,15 @@ cudaError_t launch_gather_merge(const unsigned long long* words, int world, int 
 cudaError_t launch_gather_wait(const unsigned long long* words, float* data, long long count, unsigned epoch,
                                unsigned long long limit_ns, AttnStatus* status, cudaStream_t s);
 
-// Standard-normal fill of `len` positions per kv head (benchmark caches).
+// Standard-normal fill of `len` positions per kv head (benchmark caches); elem_bytes 2 stores
+// the same values rounded to bfloat16.
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
-                               unsigned long long seed, cudaStream_t s);
+                               unsigned long long seed, int elem_bytes, cudaStream_t s);
+
+// Rows [row0, row0 + rows) of every kv head copied between two caches of possibly different
+// element sizes (4 = fp32, 2 = bfloat16; fp32 -> bfloat16 rounds to nearest even) and capacities.
+cudaError_t launch_kv_convert(const void* src, int src_elem_bytes, int src_capacity, void* dst, int dst_elem_bytes,
+                              int dst_capacity, int num_kv_heads, int head_dim, int row0, int rows, cudaStream_t s);
 
 // y[M, N] = x[M, K] . dequant(q[N, K], scales[N, ceil(K/32)]) with optional fused pieces:
 // gamma != null: x is RMS-normalised first (f64 sum and scaling, weight gamma[K], eps);

@@ -12,6 +12,8 @@
 // unfused fp32 operations (the Crystal build does not contract a*b+c), so the
 // cache contents differ from the host path only by the ulp-level difference
 // between the device's and libm's cosf/sinf.
+#include <cuda_bf16.h>
+
 #include "kernels.h"
 
 namespace shainet {
@@ -126,13 +128,22 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
     for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
         const float* row = buf + (size_t)slot * stride;
         if (slot >= H + KV) {
-            float* dst = sd.v + ((size_t)(slot - H - KV) * sd.capacity + pos) * hd;
-            for (int d = lane; d < hd; d += 32) dst[d] = row[d];
+            const size_t e0 = ((size_t)(slot - H - KV) * sd.capacity + pos) * hd;
+            if (a.kv_elem_bytes == 2) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(sd.v) + e0;
+                for (int d = lane; d < hd; d += 32) dst[d] = __float2bfloat16_rn(row[d]);
+            } else {
+                float* dst = sd.v + e0;
+                for (int d = lane; d < hd; d += 32) dst[d] = row[d];
+            }
             continue;
         }
         const bool is_q = slot < H;
         const float* w = is_q ? a.q_norm : a.k_norm;
-        float* dst = is_q ? a.q_rot + ((size_t)r * H + slot) * hd : sd.k + ((size_t)(slot - H) * sd.capacity + pos) * hd;
+        const size_t k0 = is_q ? 0 : ((size_t)(slot - H) * sd.capacity + pos) * hd;
+        const bool k16 = !is_q && a.kv_elem_bytes == 2;   // bfloat16 cache: rotated k rows are rounded to nearest even
+        float* dst = is_q ? a.q_rot + ((size_t)r * H + slot) * hd : sd.k + k0;
+        __nv_bfloat16* dst16 = reinterpret_cast<__nv_bfloat16*>(sd.k) + k0;
         const float iv = normed ? inv[slot] : 1.0f;
         for (int i = lane; i < half; i += 32) {
             float x0 = row[i], x1 = row[i + half];
@@ -151,8 +162,13 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
                 y0 = __uint_as_float(u0);
                 y1 = __uint_as_float(u1);
             }
-            dst[i] = y0;
-            dst[i + half] = y1;
+            if (k16) {
+                dst16[i] = __float2bfloat16_rn(y0);
+                dst16[i + half] = __float2bfloat16_rn(y1);
+            } else {
+                dst[i] = y0;
+                dst[i + half] = y1;
+            }
         }
     }
 }
@@ -198,7 +214,7 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
 }
 
 __global__ void fill_normal_kernel(float* base, int num_kv_heads, int capacity, int hd, int len,
-                                   unsigned long long seed) {
+                                   unsigned long long seed, int elem_bytes) {
     const long long per_head = (long long)len * hd;
     const long long pairs = ((long long)num_kv_heads * per_head + 1) / 2;
     for (long long pidx = (long long)blockIdx.x * blockDim.x + threadIdx.x; pidx < pairs;
@@ -215,13 +231,55 @@ __global__ void fill_normal_kernel(float* base, int num_kv_heads, int capacity, 
             const long long e = 2 * pidx + k;
             if (e < (long long)num_kv_heads * per_head) {
                 const long long h = e / per_head, rem = e - h * per_head;
-                base[h * (long long)capacity * hd + rem] = z[k];
+                const long long at = h * (long long)capacity * hd + rem;
+                if (elem_bytes == 2) reinterpret_cast<__nv_bfloat16*>(base)[at] = __float2bfloat16_rn(z[k]);
+                else base[at] = z[k];
             }
         }
     }
 }
 
+// Rows [row0, row0 + rows) of every kv head, two elements per thread and step (head_dim is even).
+__global__ void kv_convert_kernel(const void* src, int src_es, long long src_pitch, void* dst, int dst_es,
+                                  long long dst_pitch, int num_kv_heads, long long row_elems0, long long elems) {
+    const long long pairs_per_head = elems / 2;
+    const long long total = pairs_per_head * num_kv_heads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long h = i / pairs_per_head, e = row_elems0 + 2 * (i - h * pairs_per_head);
+        float2 v;
+        if (src_es == 4) {
+            v = *reinterpret_cast<const float2*>(static_cast<const float*>(src) + h * src_pitch + e);
+        } else {
+            const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(static_cast<const __nv_bfloat16*>(src) + h * src_pitch + e);
+            v = __bfloat1622float2(b);
+        }
+        if (dst_es == 4) {
+            *reinterpret_cast<float2*>(static_cast<float*>(dst) + h * dst_pitch + e) = v;
+        } else {
+            __nv_bfloat162 b;
+            b.x = __float2bfloat16_rn(v.x);
+            b.y = __float2bfloat16_rn(v.y);
+            *reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(dst) + h * dst_pitch + e) = b;
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_kv_convert(const void* src, int src_elem_bytes, int src_capacity, void* dst, int dst_elem_bytes,
+                              int dst_capacity, int num_kv_heads, int head_dim, int row0, int rows, cudaStream_t s) {
+    if (rows <= 0 || num_kv_heads <= 0) return cudaSuccess;
+    if ((src_elem_bytes != 4 && src_elem_bytes != 2) || (dst_elem_bytes != 4 && dst_elem_bytes != 2) || (head_dim & 1))
+        return cudaErrorInvalidValue;
+    const long long elems = (long long)rows * head_dim;
+    const long long total = elems / 2 * num_kv_heads;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    kv_convert_kernel<<<(unsigned)blocks, 256, 0, s>>>(src, src_elem_bytes, (long long)src_capacity * head_dim, dst,
+                                                        dst_elem_bytes, (long long)dst_capacity * head_dim, num_kv_heads,
+                                                        (long long)row0 * head_dim, elems);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s) {
     const long long rows = (long long)a.batch * a.T;
@@ -255,12 +313,12 @@ cudaError_t launch_ref_append(const float* staging, float* kc, float* vc, int ne
 }
 
 cudaError_t launch_fill_normal(float* base, int num_kv_heads, int capacity, int head_dim, int len,
-                               unsigned long long seed, cudaStream_t s) {
+                               unsigned long long seed, int elem_bytes, cudaStream_t s) {
     const long long pairs = ((long long)num_kv_heads * len * head_dim + 1) / 2;
     if (pairs == 0) return cudaSuccess;
     long long blocks = (pairs + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    fill_normal_kernel<<<(unsigned)blocks, 256, 0, s>>>(base, num_kv_heads, capacity, head_dim, len, seed);
+    fill_normal_kernel<<<(unsigned)blocks, 256, 0, s>>>(base, num_kv_heads, capacity, head_dim, len, seed, elem_bytes);
     return cudaGetLastError();
 }
 

@@ -217,3 +217,43 @@ def test_swiglu_activation_bias_and_greedy():
     assert O.greedy(np.array([1.0, 5.0, 5.0, np.inf, np.nan, -2.0], np.float32)) == 1
     assert O.greedy(np.array([np.nan, np.inf, -np.inf], np.float32)) == 0
     assert O.greedy(np.array([-3.0, -1.0, -2.0], np.float32)) == 1
+
+
+def test_bf16_row_rounding_mode_is_the_plain_oracle_over_rounded_rows():
+    """kv_rounding="bf16" (the library's opt-in cache format restated; not a reference behaviour):
+    rounding is to nearest even, bit-identical to torch's, and attention in that mode equals the
+    unrounded oracle attending over the rounded rows."""
+    import torch
+    from oracle import oracle as O
+    rng = np.random.default_rng(31)
+    x = (rng.standard_normal(200000) * 4).astype(np.float32)
+    x[:3] = [1.00390625, 1.01171875, -1.00390625]
+    r = O.round_bf16(x)
+    assert np.array_equal(r, torch.from_numpy(x).to(torch.bfloat16).float().numpy())
+    assert list(r[:3]) == [1.0, 1.015625, -1.0]
+    H, KV, hd = 8, 2, 32
+    qn = (1 + 0.02 * rng.standard_normal(hd)).astype(np.float32)
+    a = O.OracleAttention(H, KV, hd, 10000.0, 1e-6, q_norm=qn, k_norm=qn, kv_rounding="bf16")
+    b = O.OracleAttention(H, KV, hd, 10000.0, 1e-6, q_norm=qn, k_norm=qn)
+    f = lambda *s: rng.standard_normal(s).astype(np.float32)
+    q, k, v = f(40, H * hd), f(40, KV * hd), f(40, KV * hd)
+    a.attend_cached(q, k, v)
+    b.attend_cached(q, k, v)
+    ka, va = a.export_cache(); kb, vb = b.export_cache()
+    assert np.array_equal(ka, O.round_bf16(kb)) and np.array_equal(va, O.round_bf16(vb))
+    q1, k1, v1 = f(1, H * hd), f(1, KV * hd), f(1, KV * hd)
+    ya = a.attend_cached(q1, k1, v1)
+    ka, va = a.export_cache()
+    # mode 1 restarted from its own (representable) rows reproduces the step bit for bit; mode 0 from the
+    # same rows differs only through the new token's unrounded row
+    d = O.OracleAttention(H, KV, hd, 10000.0, 1e-6, q_norm=qn, k_norm=qn)
+    d.import_cache(ka[:, :40], va[:, :40])
+    e = O.OracleAttention(H, KV, hd, 10000.0, 1e-6, q_norm=qn, k_norm=qn, kv_rounding="bf16")
+    e.import_cache(ka[:, :40], va[:, :40])
+    assert np.array_equal(e.export_cache()[0], ka[:, :40])             # importing representable rows changes nothing
+    yd = d.attend_cached(q1, k1, v1)
+    ye = e.attend_cached(q1, k1, v1)
+    assert np.array_equal(ya, ye)
+    kd = d.export_cache()[0]
+    assert np.array_equal(O.round_bf16(kd[:, 40]), ka[:, 40])
+    assert not np.array_equal(yd, ye) and np.abs(yd - ye).max() < 0.05  # rounding the new row is visible, and small

@@ -123,7 +123,7 @@ def test_symbol_compatible_gemm_q8_f32_against_the_reference_kernel():
         assert e <= 1e-6, e
 
 
-def _make_block(ctx, rng, d, H, KV, hd, ffn, theta, eps, qk_norm=False):
+def _make_block(ctx, rng, d, H, KV, hd, ffn, theta, eps, qk_norm=False, kv_format="f32"):
     """The same random block on both sides: (oracle block, library block, things to close)."""
     import shainet_b200 as S
     from oracle import oracle as O
@@ -138,8 +138,8 @@ def _make_block(ctx, rng, d, H, KV, hd, ffn, theta, eps, qk_norm=False):
         shapes.update(gate=(d, ffn), up=(d, ffn), down=(ffn, d))
     ow = {k: O.OracleQ8(_w(rng, *s)) for k, s in shapes.items()}
     gw = {k: S.Q8Weight.from_quantized(ctx, w.q, w.scales) for k, w in ow.items()}
-    oa = O.OracleAttention(H, KV, hd, theta, eps, **kw)
-    ga = S.LlamaAttention(ctx, H, KV, hd, theta, eps, **kw)
+    oa = O.OracleAttention(H, KV, hd, theta, eps, kv_rounding="bf16" if kv_format == "bf16" else None, **kw)
+    ga = S.LlamaAttention(ctx, H, KV, hd, theta, eps, kv_format=kv_format, **kw)
     ob = O.OracleQ8Block(oa, eps, norm1, ow["wq"], ow["wk"], ow["wv"], ow["wo"], norm2 if ffn else None,
                          ow.get("gate"), ow.get("up"), ow.get("down"))
     gb = S.LlamaBlock(ctx, ga, d, eps, norm1, gw["wq"], gw["wk"], gw["wv"], gw["wo"], norm2 if ffn else None,
@@ -165,6 +165,20 @@ def test_block_forward_cached_against_the_oracle(ctx, name, d, H, KV, hd, ffn, t
         e = rel_err(got, ref)
         assert e <= BLOCK_TOL, (name, T, e)
     assert gb.attn.cache_len == 8 == ob.attn.cache_len
+    for o in owned:
+        o.close()
+
+
+def test_block_over_a_bf16_cache(ctx):
+    """The same chain with the opt-in bfloat16 KV cache: the block's attention reads 16-bit rows (fp32
+    image for the prefill rows, the fused kernel directly for single tokens); the oracle rounds its
+    cache rows the same way."""
+    rng = np.random.default_rng(1897)
+    ob, gb, owned = _make_block(ctx, rng, 2048, 32, 8, 64, 8192, 5e5, 1e-5, False, kv_format="bf16")
+    for T in (40, 1, 1, 1):
+        x = rng.standard_normal((T, 2048)).astype(np.float32)
+        e = rel_err(gb.forward_cached(x), ob.forward_cached(x))
+        assert e <= BLOCK_TOL, (T, e)
     for o in owned:
         o.close()
 
