@@ -699,7 +699,8 @@ def run_one_block(args):
     elif args.only == "bf16kv":
         res = bf16_kv_block(S, ctx, dev, tstream)
     elif args.only == "batched":
-        res = batched_block(S, ctx, dev, tstream, seqs=args.batched_seqs, layers_resident=args.batched_layers)
+        res = batched_block(S, ctx, dev, tstream, seqs=args.batched_seqs, layers_resident=args.batched_layers,
+                            kv_format=args.kv_format)
     else:
         res = prefill_block(S, ctx, dev, tstream)
     ctx.close()
@@ -1059,6 +1060,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["model", "gemv", "ctx4k", "bf16kv", "batched", "prefill"],
                     help="run one secondary block alone on one GPU and print its JSON object")
     ap.add_argument("--batched-seqs", type=int, default=None, help="--only batched: sequences in the batch (profiling: a small resident case)")
+    ap.add_argument("--kv-format", default="f32", choices=["f32", "bf16"], help="--only batched: element format of the caches")
     ap.add_argument("--batched-layers", type=int, default=None, help="--only batched: resident layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill (cfg3 shape) block of the JSON line")
