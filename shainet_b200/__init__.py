@@ -6,4 +6,4 @@ interface and, around it, of the Q8_0 weights, the whole block and the token loo
 loudly if it has not been built."""
 from . import sharding  # noqa: F401
 from .attention import (AttnContext, Decoder, KVCache, LlamaAttention, LlamaBlock, Q8Weight, ShainetAttnError, default_scale, device_count,  # noqa: F401
-                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE)
+                        forward_batched_dev, F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE, F_TENSOR_1CTA)

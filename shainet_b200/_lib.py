@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libshainet_attn.so")
 
 OK = 0
 E_INVALID, E_CUDA, E_NOMEM, E_UNSUPPORTED, E_DEVICE_WAIT, E_STATE = -1, -2, -3, -4, -5, -6
-F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE = 1, 2, 4, 8, 16, 32
+F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE, F_TENSOR_1CTA = 1, 2, 4, 8, 16, 32, 64
 
 _F = C.POINTER(C.c_float)
 _P = C.c_void_p

@@ -15,7 +15,8 @@ import math
 import numpy as np
 
 from . import _lib
-from ._lib import F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE, ShainetAttnError, check  # noqa: F401
+from ._lib import (F_GENERIC, F_SPLITK, F_TENSOR, F_UNFUSED, F_INPUTS_READY, F_TICKET_MERGE, F_TENSOR_1CTA,  # noqa: F401
+                   ShainetAttnError, check)
 
 
 def _fp(a: np.ndarray):

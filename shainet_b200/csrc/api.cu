@@ -209,6 +209,7 @@ int run_attention_untimed(shainet_attn_ctx* ctx, const HeadShape& hs, SeqRef seq
     a.hs = hs;
     a.scale = scale;
     a.status = ctx->status_dev;
+    a.prefill_one_cta = (flags & SHAINET_ATTN_F_TENSOR_1CTA) ? 1 : 0;
     if (kern == Kernel::Generic) {
         if (hs.head_dim > 256) return fail(SHAINET_ATTN_E_UNSUPPORTED, "head_dim %d > 256", hs.head_dim);
         CU(launch_attn_generic(a, s));

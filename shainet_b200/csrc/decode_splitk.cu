@@ -78,22 +78,30 @@ __device__ __forceinline__ f32x2 fmul2(f32x2 a, f32x2 b) {
 
 __device__ __forceinline__ ulonglong2 lds128x2(const void* p) { return *reinterpret_cast<const ulonglong2*>(p); }
 
-// Four consecutive cache elements, starting at element `elem` of a shared-memory tile, as
-// two packed fp32 pairs.  ES = 4: fp32 rows, one 16-byte load.  ES = 2: bfloat16 rows, one
-// 8-byte load; a bfloat16 is the upper half of the fp32 of the same value, so each pair
-// costs a shift and a mask.
+// Four consecutive cache elements of a shared-memory tile, `off` elements into the row that starts at
+// element `row0`, as two packed fp32 pairs.  ES = 4: fp32 rows, one 16-byte load.  ES = 2: bfloat16 rows,
+// one 8-byte load; a bfloat16 is the upper half of the fp32 of the same value, so each pair costs a shift
+// and a mask.  The fp32 form keeps the row pointer as a pointer and the bfloat16 form sums the indices first:
+// each is the grouping the compiler turns into the loop without spills for that element size (the other way
+// round the group-size-8 fp32 instance spills 88 bytes per thread and a launch takes 1 us longer).
 template <int ES>
-__device__ __forceinline__ ulonglong2 lds_kv4(const float* tile, size_t elem) {
-    if constexpr (ES == 4) {
-        return lds128x2(tile + elem);
-    } else {
-        const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(tile) + elem);
-        ulonglong2 r;
-        asm("mov.b64 %0, {%1, %2};" : "=l"(r.x) : "r"(w.x << 16), "r"(w.x & 0xffff0000u));
-        asm("mov.b64 %0, {%1, %2};" : "=l"(r.y) : "r"(w.y << 16), "r"(w.y & 0xffff0000u));
-        return r;
+struct KvRow {
+    const float* row;   // ES = 4
+    const float* tile;  // ES = 2
+    size_t row0;
+    __device__ __forceinline__ KvRow(const float* t, size_t r0) : row(t + r0), tile(t), row0(r0) {}
+    __device__ __forceinline__ ulonglong2 at(int off) const {
+        if constexpr (ES == 4) {
+            return lds128x2(row + off);
+        } else {
+            const uint2 w = *reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(tile) + (row0 + off));
+            ulonglong2 r;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(r.x) : "r"(w.x << 16), "r"(w.x & 0xffff0000u));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(r.y) : "r"(w.y << 16), "r"(w.y & 0xffff0000u));
+            return r;
+        }
     }
-}
+};
 
 // The value a cache of element size ES keeps for x.
 template <int ES>
@@ -241,10 +249,10 @@ __device__ __forceinline__ void score_batch(const float* ks, int base, int hw, i
     for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
 #pragma unroll
     for (int rr = 0; rr < C::R; ++rr) {
-        const size_t krow = (size_t)(base + hw * C::R + rr) * HD;
+        const KvRow<C::ES> krow(ks, (size_t)(base + hw * C::R + rr) * HD);
 #pragma unroll
         for (int c = 0; c < C::CPL; ++c) {
-            const ulonglong2 kk = lds_kv4<C::ES>(ks, krow + (c * 16 + i16) * 4);
+            const ulonglong2 kk = krow.at((c * 16 + i16) * 4);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
@@ -304,7 +312,7 @@ __device__ __forceinline__ void consume_full_tile(const float* ks, const float* 
         for (int rr = 0; rr < C::BR; rr += C::RPI) {
             const int rb = rr + (C::RPI == 2 ? hw : 0);
             const int col = (C::RPI == 2 ? i16 : lane) * 4;
-            const ulonglong2 vv = lds_kv4<C::ES>(vs, (size_t)(base + rb) * HD + col);
+            const ulonglong2 vv = KvRow<C::ES>(vs, (size_t)(base + rb) * HD).at(col);
             const f32x2* prow = ps + rb * G;
             if constexpr (G >= 2) {
 #pragma unroll
@@ -341,10 +349,10 @@ __device__ __forceinline__ void consume_tile(const float* ks, const float* vs, i
         for (int k = 0; k < 16; ++k) acc2[k] = 0ull;
 #pragma unroll
         for (int rr = 0; rr < C::R; ++rr) {
-            const size_t krow = (size_t)(base + hw * C::R + rr) * HD;
+            const KvRow<ES> krow(ks, (size_t)(base + hw * C::R + rr) * HD);
 #pragma unroll
             for (int c = 0; c < C::CPL; ++c) {
-                const ulonglong2 kk = lds_kv4<ES>(ks, krow + (c * 16 + i16) * 4);
+                const ulonglong2 kk = krow.at((c * 16 + i16) * 4);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     acc2[rr * G + g] = ffma2(q[g][c].x, kk.x, acc2[rr * G + g]);
@@ -391,7 +399,7 @@ __device__ __forceinline__ void consume_tile(const float* ks, const float* vs, i
             if (base + rr >= nrows) break;  // warp-uniform
             if (row < nrows) {
                 const int col = (C::RPI == 2 ? i16 : lane) * 4;
-                const ulonglong2 vv = lds_kv4<ES>(vs, (size_t)row * HD + col);
+                const ulonglong2 vv = KvRow<ES>(vs, (size_t)row * HD).at(col);
                 const f32x2* prow = ps + (row - base) * G;
 #pragma unroll
                 for (int g = 0; g < G; ++g) {

@@ -63,6 +63,7 @@ struct AttnArgs {
     float* part_ml;        // [rows, num_heads, max_splits, 2]
     int chunk_rows;        // cache rows per split (multiple of the warp tile)
     int max_splits;        // grid.x
+    int prefill_one_cta;   // tensor-core prefill: never pair CTAs
     AttnStatus* status;
 };
 

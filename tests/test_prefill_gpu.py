@@ -96,3 +96,25 @@ def test_prefill_pairs_row_tiles_when_the_group_size_is_odd(ctx, H, KV, hd, T):
     got = g.forward_cached(q, k, v, S.F_TENSOR)
     assert rel_err(got, ref) <= PREFILL_TOL, rel_err(got, ref)
     g.close()
+
+
+@pytest.mark.parametrize("shape,T", [(Q8B, 700), (L1B, 384), (Q30, 257)], ids=["qwen3_8b_700", "llama1b_384", "qwen3_30b_257"])
+def test_cluster_pair_kernel_and_single_cta_kernel_against_the_oracle(ctx, shape, T):
+    """Even group sizes run on a cluster of two CTAs (two query heads of one kv head, one tensor-core tile of 256 rows,
+    128-position steps); SHAINET_ATTN_F_TENSOR_1CTA keeps the one-CTA kernel (two tiles per CTA, 64-position steps).
+    Both against the oracle, a first chunk and a second one over it; the two kernels also agree with each other
+    far inside the tolerance (same TF32 products, different summation order)."""
+    import shainet_b200 as S
+    rng = np.random.default_rng(3010)
+    o, g = make_pair(ctx, shape, rng)
+    _, g1 = make_pair(ctx, shape, np.random.default_rng(3010))
+    for n in (T, 130):
+        q, k, v = qkv(rng, shape, n)
+        ref = o.attend_cached(q, k, v, threads=8)
+        pair = g.forward_cached(q, k, v, S.F_TENSOR)
+        single = g1.forward_cached(q, k, v, S.F_TENSOR | S.F_TENSOR_1CTA)
+        assert rel_err(pair, ref) <= PREFILL_TOL, (n, rel_err(pair, ref))
+        assert rel_err(single, ref) <= PREFILL_TOL, (n, rel_err(single, ref))
+        assert rel_err(pair, single) <= PREFILL_TOL / 2
+        assert not np.array_equal(pair, single)        # two different kernels did run
+    g.close(); g1.close()
