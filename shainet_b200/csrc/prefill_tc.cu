@@ -668,13 +668,17 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 tc_commit_pair(smem_u32(bar));
                 tc_commit_pair(map_to_cta(smem_u32(bar), 1u));
             };
+            // A descriptor differs from the one of the tile's first bytes only in its address field (bits 0-13, in
+            // units of 16 bytes; every address here is below 256 KB): built once, then one 64-bit add per MMA by this
+            // single issuing thread.
+            const uint64_t q_desc0 = smem_desc_sw128(q_addr, 16, 1024);
             auto scores = [&](int j) {
-                const uint32_t k_addr = k_addr0 + (j % KS) * C::K_BYTES;
+                const uint64_t k_desc0 = smem_desc_sw128(k_addr0 + (j % KS) * C::K_BYTES, 16, 1024);
                 const uint32_t d = tmem + C::TMEM_S + (j % SB) * C::BN;
 #pragma unroll
                 for (int kk = 0; kk < HD / 8; ++kk) {
-                    const uint64_t ad = smem_desc_sw128(q_addr + (kk >> 2) * (C::BM * 128) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = smem_desc_sw128(k_addr + (kk >> 2) * (C::K_ROWS * 128) + (kk & 3) * 32, 16, 1024);
+                    const uint64_t ad = q_desc0 + (uint64_t)(((kk >> 2) * (C::BM * 128) + (kk & 3) * 32) >> 4);
+                    const uint64_t bd = k_desc0 + (uint64_t)(((kk >> 2) * (C::K_ROWS * 128) + (kk & 3) * 32) >> 4);
                     mma_ss_tf32_pair(d, ad, bd, idesc_qk, kk > 0);
                 }
                 commit(&s_full[j % SB]);
@@ -700,11 +704,10 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_
                 tc_fence_after();
                 const uint32_t d = tmem + C::TMEM_O;
                 const uint32_t p = tmem + C::TMEM_S + (j % SB) * C::BN;
+                const uint64_t v_desc0 = smem_desc(v_addr0 + sv * C::V_BYTES, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
 #pragma unroll
-                for (int kk = 0; kk < C::BN / 8; ++kk) {
-                    const uint64_t bd = smem_desc(v_addr0 + sv * C::V_BYTES + kk * 1024, C::BN * 128, 512, LAYOUT_SW128_BASE32B);
-                    mma_ts_tf32_pair(d, p + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < C::BN / 8; ++kk)
+                    mma_ts_tf32_pair(d, p + kk * 8, v_desc0 + (uint64_t)(kk * 1024 >> 4), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 commit(o_done);
                 commit(&v_empty[sv]);
             }
