@@ -118,3 +118,24 @@ def test_cluster_pair_kernel_and_single_cta_kernel_against_the_oracle(ctx, shape
         assert rel_err(pair, single) <= PREFILL_TOL / 2
         assert not np.array_equal(pair, single)        # two different kernels did run
     g.close(); g1.close()
+
+
+@pytest.mark.parametrize("H,KV,hd,T,pre", [(4, 2, 128, 130, 0), (16, 1, 64, 300, 45), (8, 4, 64, 129, 128), (16, 2, 128, 257, 3)],
+                         ids=["g2_hd128", "g16_hd64_over_45", "g2_hd64_over_128", "g8_hd128_over_3"])
+def test_cluster_pair_kernel_group_sizes_and_ragged_edges(ctx, H, KV, hd, T, pre):
+    """Every even group size goes to the pair kernel: group sizes 2, 8 and 16, both head dims, row counts one past a
+    tile, and existing cache lengths that leave the first 128-position step ragged."""
+    import shainet_b200 as S
+    rng = np.random.default_rng(3011)
+    shape = dict(H=H, KV=KV, hd=hd, theta=10000.0, qk_norm=(hd == 128))
+    o, g = make_pair(ctx, shape, rng)
+    if pre:
+        q, k, v = qkv(rng, shape, pre)
+        o.attend_cached(q, k, v); g.forward_cached(q, k, v, S.F_GENERIC)
+    q, k, v = qkv(rng, shape, T)
+    ref = o.attend_cached(q, k, v, threads=8)
+    got = g.forward_cached(q, k, v, S.F_TENSOR)
+    assert rel_err(got, ref) <= PREFILL_TOL, rel_err(got, ref)
+    per_row = np.abs(got - ref).max(axis=1) / np.abs(ref).max(axis=1)
+    assert per_row.max() <= 4 * PREFILL_TOL, (float(per_row.max()), int(per_row.argmax()))
+    g.close()
