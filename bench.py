@@ -924,12 +924,19 @@ def run_ours(args, wl, rank, world, local_rank):
 
     ho_full = torch.empty(layers, (H * hd) if split else (world * qd), dtype=torch.float32).pin_memory() if world > 1 else None
 
+    # the argument lists of the per-layer calls, built once: the pointers into the pinned buffers do not change, and
+    # building them (tensor views, casts) per call would put several microseconds of Python into every layer
+    host_calls = None
+    if world == 1:
+        host_calls = [[(ctx.h, b.cache.h, C.cast(hq[vi, l].data_ptr(), FP), C.cast(hk[vi, l].data_ptr(), FP),
+                        C.cast(hv[vi, l].data_ptr(), FP), C.cast(ho[l].data_ptr(), FP), 1, C.c_float(b.scale), 0)
+                       for l, b in enumerate(blocks)] for vi in range(NV)]
+
     def host_step(i):
         vi = i % NV
         if world == 1:
-            for l, b in enumerate(blocks):
-                rc = fwd_host(ctx.h, b.cache.h, C.cast(hq[vi, l].data_ptr(), FP), C.cast(hk[vi, l].data_ptr(), FP),
-                              C.cast(hv[vi, l].data_ptr(), FP), C.cast(ho[l].data_ptr(), FP), 1, b.scale, 0)
+            for call in host_calls[vi]:
+                rc = fwd_host(*call)
                 if rc:
                     S.check(rc)
             return
