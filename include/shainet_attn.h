@@ -55,7 +55,7 @@ extern "C" {
  * tickets even where the flag-polling merge would be chosen (testing). */
 #define SHAINET_ATTN_F_TICKET_MERGE 32u
 /* Tensor-core prefill with one CTA per two query tiles even where a pair of CTAs (cluster of two, cta_group::2)
- * would be chosen, i.e. for even group sizes (measurement and testing; the pair is the faster one). */
+ * would be chosen, i.e. at head_dim 128 with an even group size (measurement and testing; the pair is the faster one). */
 #define SHAINET_ATTN_F_TENSOR_1CTA 64u
 
 typedef struct shainet_attn_ctx shainet_attn_ctx;

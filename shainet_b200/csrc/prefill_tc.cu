@@ -8,10 +8,10 @@
 // overflows Int32 at 32 x 8192 x 8192, src/shainet/transformer/llama_block.cr:418)
 // and never touches a tensor core.
 //
-// Two kernels.  With an even group size (every GQA model) a cluster of two CTAs
+// Two kernels.  With head_dim 128 and an even group size a cluster of two CTAs
 // works as one tensor core (cta_group::2) on two query heads of one kv head:
-// attn_prefill_pair_kernel, further down.  Otherwise (one query head per kv
-// head) attn_prefill_tc2_kernel: one CTA owns two tiles of 128 query rows that
+// attn_prefill_pair_kernel, further down.  Otherwise (head_dim 64, or one query
+// head per kv head) attn_prefill_tc2_kernel: one CTA owns two tiles of 128 query rows that
 // see the same K/V tiles and walks the visible cache positions in tiles of 64:
 //
 //   S  = Q K^T      tcgen05.mma kind::tf32, A and B from shared memory (K-major),
@@ -941,8 +941,10 @@ cudaError_t launch_pf_pair128(const AttnArgs& a, cudaStream_t s) {
 
 template <int HD>
 cudaError_t launch_pf_any(const AttnArgs& a, cudaStream_t s) {
-    // even group size: two query heads of one kv head per pair of CTAs; otherwise the single-CTA kernel
-    if ((a.hs.num_heads / a.hs.num_kv_heads) % 2 == 0 && !a.prefill_one_cta) return launch_pf_pair128<HD>(a, s);
+    // even group size and head_dim 128: two query heads of one kv head per pair of CTAs; otherwise the one-CTA kernel
+    // (at head_dim 64 a step's exponentials take as long as its MMAs in either kernel and the pair's hand-over is pure
+    // cost: 0.266 against 0.254 ms for 4096 tokens of the LLaMA-3.2-1B shape, 0.872 against 0.809 ms for 8192)
+    if (HD == 128 && (a.hs.num_heads / a.hs.num_kv_heads) % 2 == 0 && !a.prefill_one_cta) return launch_pf_pair128<HD>(a, s);
     return launch_pf<HD>(a, s);
 }
 
