@@ -114,6 +114,16 @@ int shainet_attn_kv_create(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num
 int shainet_attn_kv_create_fmt(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
                                int head_dim, int initial_capacity, int format);
 int shainet_attn_kv_format(const shainet_attn_kv* kv);       /* SHAINET_ATTN_KV_*, or negative status */
+/* A cache that grows without moving (no counterpart in the reference, whose ensure_gpu_cache!, llama_block.cr:497-520,
+ * allocates max(256, need, 2 x old) rows and uploads the whole cache again).  Device ADDRESSES for max_capacity rows
+ * per kv head (rounded up so that a kv head's range is a whole number of pages) are reserved at creation; physical
+ * memory is mapped behind them, page by page (the driver's granularity, 2 MB), as rows are appended, reserved or
+ * imported.  Growth therefore copies nothing and invalidates nothing: kv_device_ptrs stay valid for the cache's life,
+ * kv_capacity is the reserved row count from the start, and memory in use follows the length, not a doubling policy.
+ * Every entry accepts such a cache (to the kernels it is an ordinary cache of that capacity); appending past
+ * max_capacity answers SHAINET_ATTN_E_INVALID, a driver without virtual memory management SHAINET_ATTN_E_UNSUPPORTED. */
+int shainet_attn_kv_create_reserved(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                                    int head_dim, int max_capacity, int format);
 int shainet_attn_kv_destroy(shainet_attn_kv* kv);
 int shainet_attn_kv_reset(shainet_attn_kv* kv);              /* clear_cache!: length 0, buffers kept */
 int shainet_attn_kv_len(const shainet_attn_kv* kv);          /* @cache_len, or negative status */

@@ -32,6 +32,7 @@ SIGNATURES = {
     "shainet_attn_kv_create": (C.c_int, [_P, C.POINTER(_P), C.c_int, C.c_int, C.c_int, C.c_int]),
     "shainet_attn_kv_create_fmt": (C.c_int, [_P, C.POINTER(_P), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "shainet_attn_kv_format": (C.c_int, [_P]),
+    "shainet_attn_kv_create_reserved": (C.c_int, [_P, C.POINTER(_P), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "shainet_attn_kv_destroy": (C.c_int, [_P]),
     "shainet_attn_kv_reset": (C.c_int, [_P]),
     "shainet_attn_kv_len": (C.c_int, [_P]),

@@ -136,16 +136,24 @@ class KVCache:
     bfloat16 as they are appended (no counterpart in the reference)."""
 
     def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int, head_dim: int, initial_capacity: int = 0,
-                 kv_format: str = "f32"):
+                 kv_format: str = "f32", reserve_capacity: int = 0):
         self.ctx, self.L = ctx, ctx.L
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.q_dim, self.kv_dim = num_heads * head_dim, num_kv_heads * head_dim
         if kv_format not in KV_FORMATS:
             raise ValueError(f"kv_format must be one of {sorted(KV_FORMATS)}")
         h = C.c_void_p()
-        check(self.L.shainet_attn_kv_create_fmt(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim, initial_capacity,
-                                                KV_FORMATS[kv_format]))
-        self.h = h
+        if reserve_capacity:
+            # addresses for reserve_capacity rows, memory mapped behind them as the cache fills (no copy on growth)
+            check(self.L.shainet_attn_kv_create_reserved(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim,
+                                                         reserve_capacity, KV_FORMATS[kv_format]))
+            self.h = h
+            if initial_capacity:
+                self.reserve(initial_capacity)
+        else:
+            check(self.L.shainet_attn_kv_create_fmt(ctx.h, C.byref(h), num_heads, num_kv_heads, head_dim, initial_capacity,
+                                                    KV_FORMATS[kv_format]))
+            self.h = h
 
     @property
     def kv_format(self) -> str:
@@ -220,10 +228,10 @@ class LlamaAttention:
 
     def __init__(self, ctx: AttnContext, num_heads: int, num_kv_heads: int | None = None, head_dim: int = 64,
                  rope_theta: float = 10000.0, eps: float = 1e-6, rope_freqs=None, q_norm=None, k_norm=None,
-                 b_q=None, b_k=None, b_v=None, initial_capacity: int = 0, kv_format: str = "f32"):
+                 b_q=None, b_k=None, b_v=None, initial_capacity: int = 0, kv_format: str = "f32", reserve_capacity: int = 0):
         num_kv_heads = num_heads if num_kv_heads is None else num_kv_heads
         self.ctx = ctx
-        self.cache = KVCache(ctx, num_heads, num_kv_heads, head_dim, initial_capacity, kv_format)
+        self.cache = KVCache(ctx, num_heads, num_kv_heads, head_dim, initial_capacity, kv_format, reserve_capacity)
         self.num_heads, self.num_kv_heads, self.head_dim = num_heads, num_kv_heads, head_dim
         self.q_dim, self.kv_dim = self.cache.q_dim, self.cache.kv_dim
         self.scale = default_scale(head_dim)

@@ -25,6 +25,8 @@ module SHAInet
     fun kv_create_fmt = shainet_attn_kv_create_fmt(ctx : Ctx, out_kv : Kv*, num_heads : Int32, num_kv_heads : Int32,
                                                    head_dim : Int32, initial_capacity : Int32, format : Int32) : Int32
     fun kv_format = shainet_attn_kv_format(kv : Kv) : Int32
+    fun kv_create_reserved = shainet_attn_kv_create_reserved(ctx : Ctx, out_kv : Kv*, num_heads : Int32, num_kv_heads : Int32,
+                                                             head_dim : Int32, max_capacity : Int32, format : Int32) : Int32
     fun kv_destroy = shainet_attn_kv_destroy(kv : Kv) : Int32
     fun kv_reset = shainet_attn_kv_reset(kv : Kv) : Int32
     fun kv_truncate = shainet_attn_kv_truncate(kv : Kv, len : Int32) : Int32

@@ -1,5 +1,6 @@
 // Host side of libshainet_attn: contexts, KV caches, kernel selection and the
 // C ABI declared in include/shainet_attn.h.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdarg.h>
@@ -59,9 +60,88 @@ int grow_pinned(float*& p, size_t& cap, size_t floats) {
     return SHAINET_ATTN_OK;
 }
 
+// ---- virtual-memory management (driver API, looked up once) for caches that grow without moving ----
+struct VmmApi {
+    CUresult (*address_reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+    CUresult (*address_free)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+    CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+    CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+    CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*set_access)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+    CUresult (*granularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+    bool ok = false;
+};
+
+const VmmApi& vmm_api() {
+    static VmmApi api = [] {
+        VmmApi a;
+        auto get = [](const char* name, void** fn) {
+            cudaDriverEntryPointQueryResult q;
+            return cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess && *fn;
+        };
+        a.ok = get("cuMemAddressReserve", (void**)&a.address_reserve) && get("cuMemAddressFree", (void**)&a.address_free) &&
+               get("cuMemCreate", (void**)&a.create) && get("cuMemRelease", (void**)&a.release) && get("cuMemMap", (void**)&a.map) &&
+               get("cuMemUnmap", (void**)&a.unmap) && get("cuMemSetAccess", (void**)&a.set_access) &&
+               get("cuMemGetAllocationGranularity", (void**)&a.granularity);
+        cudaGetLastError();
+        return a;
+    }();
+    return api;
+}
+
+CUmemAllocationProp vmm_prop(int device) {
+    CUmemAllocationProp p{};
+    p.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    p.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    p.location.id = device;
+    return p;
+}
+
+// Maps (and zeroes) pages behind every kv head of both tensors until `rows` rows of each are backed.
+int kv_map_rows(shainet_attn_kv* kv, int rows, cudaStream_t s) {
+    const VmmApi& api = vmm_api();
+    const size_t row_bytes = (size_t)kv->hs.head_dim * kv->es;
+    const size_t head_stride = (size_t)kv->cap * row_bytes;
+    const size_t need = ((size_t)rows * row_bytes + kv->page_bytes - 1) / kv->page_bytes;
+    if (need <= kv->pages_per_head) return SHAINET_ATTN_OK;
+    const CUmemAllocationProp prop = vmm_prop(kv->ctx->device);
+    CUmemAccessDesc acc{};
+    acc.location = prop.location;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    const size_t first = kv->pages_per_head * kv->page_bytes, bytes = (need - kv->pages_per_head) * kv->page_bytes;
+    for (float* base : {kv->k, kv->v}) {
+        for (int h = 0; h < kv->hs.num_kv_heads; ++h) {
+            const CUdeviceptr at = (CUdeviceptr)base + (size_t)h * head_stride + first;
+            CUmemGenericAllocationHandle hd;
+            CUresult r = api.create(&hd, bytes, &prop, 0);
+            if (r != CUDA_SUCCESS)
+                return fail(r == CUDA_ERROR_OUT_OF_MEMORY ? SHAINET_ATTN_E_NOMEM : SHAINET_ATTN_E_CUDA, "cuMemCreate of %zu bytes failed (%d)", bytes, (int)r);
+            r = api.map(at, bytes, 0, hd, 0);
+            if (r == CUDA_SUCCESS) r = api.set_access(at, bytes, &acc, 1);
+            if (r != CUDA_SUCCESS) {
+                api.release(hd);
+                return fail(SHAINET_ATTN_E_CUDA, "mapping %zu bytes of cache failed (%d)", bytes, (int)r);
+            }
+            kv->mappings.push_back({(unsigned long long)at, (unsigned long long)bytes, (unsigned long long)hd});
+            // rows past the appended length are read (and masked) by the tensor-core prefill kernel: they start at zero
+            CU(cudaMemsetAsync((void*)at, 0, bytes, s));
+        }
+    }
+    CU(cudaStreamSynchronize(s));
+    kv->pages_per_head = need;
+    return SHAINET_ATTN_OK;
+}
+
 // Capacity policy of ensure_gpu_cache! (llama_block.cr:500): max(256, need, 2*old),
 // but the live rows move device-to-device instead of being re-uploaded.
 int kv_ensure(shainet_attn_kv* kv, int total_len, cudaStream_t s) {
+    if (kv->reserved) {
+        if (total_len > kv->cap)
+            return fail(SHAINET_ATTN_E_INVALID, "%d rows exceed the %d this cache reserved addresses for", total_len, kv->cap);
+        // whole 128-row tiles of the prefill kernel are always backed
+        return kv_map_rows(kv, std::min(kv->cap, (total_len + 127) / 128 * 128), s);
+    }
     if (kv->cap >= total_len && kv->k) return SHAINET_ATTN_OK;
     const long long want = std::max<long long>(256, std::max<long long>(total_len, 2ll * kv->cap));
     if (want > 0x7fffffffll) return fail(SHAINET_ATTN_E_INVALID, "cache capacity overflow");
@@ -611,10 +691,72 @@ int shainet_attn_kv_create_fmt(shainet_attn_ctx* ctx, shainet_attn_kv** out, int
     return SHAINET_ATTN_OK;
 }
 
+int shainet_attn_kv_create_reserved(shainet_attn_ctx* ctx, shainet_attn_kv** out, int num_heads, int num_kv_heads,
+                                    int head_dim, int max_capacity, int format) {
+    if (!out) return fail(SHAINET_ATTN_E_INVALID, "null pointer");
+    *out = nullptr;
+    if (max_capacity <= 0) return fail(SHAINET_ATTN_E_INVALID, "the reserved capacity must be positive");
+    const VmmApi& api = vmm_api();
+    if (!api.ok) return fail(SHAINET_ATTN_E_UNSUPPORTED, "the driver does not offer virtual memory management");
+    shainet_attn_kv* kv = nullptr;
+    int rc = shainet_attn_kv_create_fmt(ctx, &kv, num_heads, num_kv_heads, head_dim, 0, format);
+    if (rc) return rc;
+    DeviceGuard g(ctx->device);
+    const CUmemAllocationProp prop = vmm_prop(ctx->device);
+    size_t gran = 0;
+    CUresult r = api.granularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM);
+    if (r != CUDA_SUCCESS || gran == 0) {
+        shainet_attn_kv_destroy(kv);
+        return fail(SHAINET_ATTN_E_CUDA, "cuMemGetAllocationGranularity failed (%d)", (int)r);
+    }
+    // every kv head's range starts on a page: round the capacity up until its bytes are a whole number of pages
+    const size_t row_bytes = (size_t)head_dim * kv->es;
+    size_t a = gran, b = row_bytes;
+    while (b) {
+        const size_t t = a % b;
+        a = b;
+        b = t;
+    }
+    const size_t rows_unit = gran / a;   // smallest row count whose bytes are a multiple of the granularity
+    const size_t cap = ((size_t)max_capacity + rows_unit - 1) / rows_unit * rows_unit;
+    if (cap > 0x7fffffffull) {
+        shainet_attn_kv_destroy(kv);
+        return fail(SHAINET_ATTN_E_INVALID, "reserved capacity overflow");
+    }
+    const size_t total = cap * row_bytes * num_kv_heads;
+    CUdeviceptr pk = 0, pv = 0;
+    r = api.address_reserve(&pk, total, gran, 0, 0);
+    if (r == CUDA_SUCCESS) r = api.address_reserve(&pv, total, gran, 0, 0);
+    if (r != CUDA_SUCCESS) {
+        if (pk) api.address_free(pk, total);
+        shainet_attn_kv_destroy(kv);
+        return fail(SHAINET_ATTN_E_NOMEM, "reserving %zu bytes of device addresses failed (%d)", total, (int)r);
+    }
+    kv->reserved = true;
+    kv->page_bytes = gran;
+    kv->cap = (int)cap;
+    kv->k = reinterpret_cast<float*>(pk);
+    kv->v = reinterpret_cast<float*>(pv);
+    *out = kv;
+    return SHAINET_ATTN_OK;
+}
+
 int shainet_attn_kv_destroy(shainet_attn_kv* kv) {
     if (!kv) return SHAINET_ATTN_OK;
     DeviceGuard g(kv->ctx->device);
     cudaStreamSynchronize(kv->ctx->stream);
+    if (kv->reserved) {
+        const VmmApi& api = vmm_api();
+        const size_t total = (size_t)kv->cap * kv->hs.head_dim * kv->es * kv->hs.num_kv_heads;
+        for (const shainet_attn_kv::Mapping& m : kv->mappings) {
+            api.unmap((CUdeviceptr)m.at, (size_t)m.bytes);
+            api.release((CUmemGenericAllocationHandle)m.handle);
+        }
+        kv->mappings.clear();
+        if (kv->k) api.address_free((CUdeviceptr)kv->k, total);
+        if (kv->v) api.address_free((CUdeviceptr)kv->v, total);
+        kv->k = kv->v = nullptr;
+    }
     for (float* p : {kv->k, kv->v, kv->inv_freq, kv->q_norm, kv->k_norm, kv->b_q, kv->b_k, kv->b_v})
         if (p) cudaFree(p);
     cudaGetLastError();
@@ -717,6 +859,14 @@ int shainet_attn_kv_export(shainet_attn_kv* kv, float* k_host, float* v_host, in
         return SHAINET_ATTN_OK;
     }
     const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
+    if (kv->reserved) {
+        // a pitched copy would be checked over the unmapped addresses between the kv heads: one copy per head
+        for (int h = 0; h < kv->hs.num_kv_heads; ++h) {
+            CU(cudaMemcpy(reinterpret_cast<char*>(k_host) + h * row_bytes, reinterpret_cast<const char*>(kv->k) + h * pitch, row_bytes, cudaMemcpyDeviceToHost));
+            CU(cudaMemcpy(reinterpret_cast<char*>(v_host) + h * row_bytes, reinterpret_cast<const char*>(kv->v) + h * pitch, row_bytes, cudaMemcpyDeviceToHost));
+        }
+        return SHAINET_ATTN_OK;
+    }
     CU(cudaMemcpy2D(k_host, row_bytes, kv->k, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
     CU(cudaMemcpy2D(v_host, row_bytes, kv->v, pitch, row_bytes, kv->hs.num_kv_heads, cudaMemcpyDeviceToHost));
     return SHAINET_ATTN_OK;
@@ -748,8 +898,15 @@ int shainet_attn_kv_import(shainet_attn_kv* kv, const float* k_host, const float
         CU(cudaStreamSynchronize(kv->ctx->stream));
         const size_t row_bytes = (size_t)len * kv->hs.head_dim * sizeof(float);
         const size_t pitch = (size_t)kv->cap * kv->hs.head_dim * sizeof(float);
-        CU(cudaMemcpy2D(kv->k, pitch, k_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
-        CU(cudaMemcpy2D(kv->v, pitch, v_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
+        if (kv->reserved) {
+            for (int h = 0; h < kv->hs.num_kv_heads; ++h) {
+                CU(cudaMemcpy(reinterpret_cast<char*>(kv->k) + h * pitch, reinterpret_cast<const char*>(k_host) + h * row_bytes, row_bytes, cudaMemcpyHostToDevice));
+                CU(cudaMemcpy(reinterpret_cast<char*>(kv->v) + h * pitch, reinterpret_cast<const char*>(v_host) + h * row_bytes, row_bytes, cudaMemcpyHostToDevice));
+            }
+        } else {
+            CU(cudaMemcpy2D(kv->k, pitch, k_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
+            CU(cudaMemcpy2D(kv->v, pitch, v_host, row_bytes, row_bytes, kv->hs.num_kv_heads, cudaMemcpyHostToDevice));
+        }
     }
     kv->len = len;
     return SHAINET_ATTN_OK;

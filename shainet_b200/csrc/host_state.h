@@ -73,6 +73,15 @@ struct shainet_attn_kv {
     float* k = nullptr;         // [num_kv_heads, cap, head_dim] elements of `es` bytes (bfloat16 behind a float pointer when es == 2)
     float* v = nullptr;
     int es = 4;                 // bytes per cache element: 4 = fp32, 2 = bfloat16
+    // Reserved-address cache (kv_create_reserved): k and v are virtual address ranges of cap rows per kv head, reserved
+    // once; physical pages are mapped behind the rows in use.  cap then never changes and rows never move.
+    bool reserved = false;
+    size_t page_bytes = 0;      // mapping granularity
+    size_t pages_per_head = 0;  // pages mapped (and zeroed) behind every kv head of k and of v
+    struct Mapping {
+        unsigned long long at, bytes, handle;       // device address, size, CUmemGenericAllocationHandle
+    };
+    std::vector<Mapping> mappings;
     int cap = 0;
     int len = 0;
     float* inv_freq = nullptr;  // device, head_dim/2

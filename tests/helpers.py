@@ -34,13 +34,14 @@ def make_pair(ctx, shape, rng, eps=1e-6, **extra):
     kw = dict(extra)
     cap = kw.pop("initial_capacity", 0)
     fmt = kw.pop("kv_format", "f32")   # "bf16": the library's opt-in 16-bit cache against the oracle's rounded rows
+    reserve = kw.pop("reserve_capacity", 0)   # addresses reserved up front, memory mapped as the cache fills
     if shape.get("qk_norm"):
         kw.setdefault("q_norm", norm_weights(rng, shape["hd"]))
         kw.setdefault("k_norm", norm_weights(rng, shape["hd"]))
     o = O.OracleAttention(shape["H"], shape["KV"], shape["hd"], shape["theta"], eps,
                           kv_rounding="bf16" if fmt == "bf16" else None, **kw)
     g = S.LlamaAttention(ctx, shape["H"], shape["KV"], shape["hd"], shape["theta"], eps, initial_capacity=cap,
-                         kv_format=fmt, **kw)
+                         kv_format=fmt, reserve_capacity=reserve, **kw)
     return o, g
 
 
