@@ -173,6 +173,133 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_append_kernel(PrepArgs a) {
     }
 }
 
+// The same kernel for head_dim 64 and 128 with rows that arrive by bulk copies (16-byte aligned inputs): the loops are
+// unrolled, a lane's cos/sin and norm weights stay in registers over all of the token's heads, and the sequential sums
+// read four floats per load.  Arithmetic and its order are those of the kernel above; it only issues a third of the
+// instructions (the general kernel is bound by its instruction count, not by memory).
+template <int HD>
+__global__ void __launch_bounds__(PREP_THREADS) prep_append_hd_kernel(PrepArgs a) {
+    extern __shared__ __align__(16) float prep_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int H = a.hs.num_heads, KV = a.hs.num_kv_heads;
+    const int per_row = H + 2 * KV;
+    constexpr int HALF = HD / 2, STRIDE = HD + 4, PL = HALF / 32;   // rotation pairs per lane
+    uint64_t* bar = reinterpret_cast<uint64_t*>(prep_smem);   // 16 bytes reserved
+    float* buf = prep_smem + 4;          // [per_row][STRIDE], 16-byte aligned
+    float* inv = buf + (size_t)per_row * STRIDE;   // [H + KV]
+
+    const int r = blockIdx.x;
+    const int b = r / a.T, t = r % a.T;
+    const SeqDesc sd = a.seqs.many ? a.seqs.many[b] : a.seqs.one;
+    const int pos = sd.start + t;
+    const float fpos = (float)pos;
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(bar, (uint32_t)per_row * HD * 4);
+        for (int slot = 0; slot < per_row; ++slot) {
+            const float* src = slot < H ? a.q + ((size_t)r * H + slot) * HD
+                             : slot < H + KV ? a.k_new + ((size_t)r * KV + (slot - H)) * HD
+                                             : a.v_new + ((size_t)r * KV + (slot - H - KV)) * HD;
+            bulk_g2s(buf + (size_t)slot * STRIDE, src, (uint32_t)HD * 4, bar);
+        }
+    }
+    // this lane's rotation pairs (i, i + HALF), i = lane + 32 k: angle, norm weights
+    float cs[PL], sn[PL], wq0[PL], wq1[PL], wk0[PL], wk1[PL];
+#pragma unroll
+    for (int k = 0; k < PL; ++k) {
+        const int i = lane + 32 * k;
+        sincosf(__fmul_rn(fpos, a.inv_freq[i]), &sn[k], &cs[k]);
+        wq0[k] = a.q_norm ? a.q_norm[i] : 1.0f;
+        wq1[k] = a.q_norm ? a.q_norm[i + HALF] : 1.0f;
+        wk0[k] = a.k_norm ? a.k_norm[i] : 1.0f;
+        wk1[k] = a.k_norm ? a.k_norm[i + HALF] : 1.0f;
+    }
+    if (!mbar_wait(bar, 0, a.status, 31)) return;   // bounded; the whole CTA sees the same outcome
+    if (a.b_q != nullptr || a.b_k != nullptr || a.b_v != nullptr) {
+        for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+            const float* bias = slot < H ? (a.b_q ? a.b_q + (size_t)slot * HD : nullptr)
+                              : slot < H + KV ? (a.b_k ? a.b_k + (size_t)(slot - H) * HD : nullptr)
+                                              : (a.b_v ? a.b_v + (size_t)(slot - H - KV) * HD : nullptr);
+            if (bias == nullptr) continue;
+            float* row = buf + (size_t)slot * STRIDE;
+#pragma unroll
+            for (int d = lane; d < HD; d += 32) row[d] = __fadd_rn(row[d], bias[d]);
+        }
+        __syncthreads();
+    }
+    const bool normed = a.q_norm != nullptr || a.k_norm != nullptr;
+    if (normed) {
+        for (int slot = threadIdx.x; slot < H + KV; slot += PREP_THREADS) {
+            // sequential fp32 sum in ascending d, as the host loop does; four floats per load
+            const float4* row = reinterpret_cast<const float4*>(buf + (size_t)slot * STRIDE);
+            float ss = 0.0f;
+#pragma unroll
+            for (int d4 = 0; d4 < HD / 4; ++d4) {
+                const float4 v = row[d4];
+                ss = __fadd_rn(ss, __fmul_rn(v.x, v.x));
+                ss = __fadd_rn(ss, __fmul_rn(v.y, v.y));
+                ss = __fadd_rn(ss, __fmul_rn(v.z, v.z));
+                ss = __fadd_rn(ss, __fmul_rn(v.w, v.w));
+            }
+            const float mean = __fdiv_rn(ss, (float)HD);
+            inv[slot] = (float)(1.0 / sqrt((double)mean + a.eps));
+        }
+        __syncthreads();
+    }
+    for (int slot = warp; slot < per_row; slot += PREP_WARPS) {
+        const float* row = buf + (size_t)slot * STRIDE;
+        if (slot >= H + KV) {
+            const size_t e0 = ((size_t)(slot - H - KV) * sd.capacity + pos) * HD;
+            if (a.kv_elem_bytes == 2) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(sd.v) + e0;
+#pragma unroll
+                for (int d = lane; d < HD; d += 32) dst[d] = __float2bfloat16_rn(row[d]);
+            } else {
+                float* dst = sd.v + e0;
+#pragma unroll
+                for (int d = lane; d < HD; d += 32) dst[d] = row[d];
+            }
+            continue;
+        }
+        const bool is_q = slot < H;
+        const bool has_w = (is_q ? a.q_norm : a.k_norm) != nullptr;
+        const size_t k0 = is_q ? 0 : ((size_t)(slot - H) * sd.capacity + pos) * HD;
+        const bool k16 = !is_q && a.kv_elem_bytes == 2;
+        float* dst = is_q ? a.q_rot + ((size_t)r * H + slot) * HD : sd.k + k0;
+        __nv_bfloat16* dst16 = reinterpret_cast<__nv_bfloat16*>(sd.k) + k0;
+        const float iv = normed ? inv[slot] : 1.0f;
+#pragma unroll
+        for (int k = 0; k < PL; ++k) {
+            const int i = lane + 32 * k;
+            float x0 = row[i], x1 = row[i + HALF];
+            if (has_w) {
+                x0 = __fmul_rn(__fmul_rn(x0, iv), is_q ? wq0[k] : wk0[k]);
+                x1 = __fmul_rn(__fmul_rn(x1, iv), is_q ? wq1[k] : wk1[k]);
+            }
+            float y0 = __fsub_rn(__fmul_rn(x0, cs[k]), __fmul_rn(x1, sn[k]));
+            float y1 = __fadd_rn(__fmul_rn(x1, cs[k]), __fmul_rn(x0, sn[k]));
+            if (a.round_q_tf32 && is_q) {
+                unsigned u0, u1;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u0) : "f"(y0));
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u1) : "f"(y1));
+                y0 = __uint_as_float(u0);
+                y1 = __uint_as_float(u1);
+            }
+            if (k16) {
+                dst16[i] = __float2bfloat16_rn(y0);
+                dst16[i + HALF] = __float2bfloat16_rn(y1);
+            } else {
+                dst[i] = y0;
+                dst[i + HALF] = y1;
+            }
+        }
+    }
+}
+
 // Scatter of already-rotated staging rows, the reference kernel's contract:
 // staging = K chunks [kv_head][t][d] followed by V chunks in the same layout.
 __global__ void ref_append_kernel(const float4* __restrict__ staging, float* __restrict__ kc, float* __restrict__ vc,
@@ -291,7 +418,10 @@ cudaError_t launch_prep_append(const PrepArgs& a, cudaStream_t s) {
         cudaError_t e = cudaFuncSetAttribute(prep_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    prep_append_kernel<<<(unsigned)rows, PREP_THREADS, smem, s>>>(a);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) & 15u) == 0;
+    if (aligned && smem <= 48 * 1024 && a.hs.head_dim == 128) prep_append_hd_kernel<128><<<(unsigned)rows, PREP_THREADS, smem, s>>>(a);
+    else if (aligned && smem <= 48 * 1024 && a.hs.head_dim == 64) prep_append_hd_kernel<64><<<(unsigned)rows, PREP_THREADS, smem, s>>>(a);
+    else prep_append_kernel<<<(unsigned)rows, PREP_THREADS, smem, s>>>(a);
     return cudaGetLastError();
 }
 
