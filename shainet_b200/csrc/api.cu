@@ -238,8 +238,8 @@ int pick_kernel(const HeadShape& hs, int batch, int T, unsigned flags, Kernel* o
 
 // Rows of cache per split so that about one CTA lands on every SM.
 void plan_splits(int sm_count, const HeadShape& hs, int rows, long long total_visible, int max_visible,
-                 int waves, int* chunk_rows, int* max_splits, int kv_elem_bytes = 4) {
-    const int tw = splitk_tile_rows(hs, kv_elem_bytes);
+                 int waves, int* chunk_rows, int* max_splits, int kv_elem_bytes = 4, bool batched = false) {
+    const int tw = splitk_tile_rows(hs, kv_elem_bytes, batched);
     const long long ctas = std::max<long long>(1, (long long)sm_count * splitk_ctas_per_sm(hs) * waves);
     long long chunk = (total_visible * hs.num_kv_heads + ctas - 1) / ctas;
     const long long min_chunk = 4ll * tw;  // one tile per consumer warp
@@ -401,7 +401,8 @@ int run_step(shainet_attn_ctx* ctx, const shainet_attn_kv* par, SeqRef seqs, int
     f.hs = hs;
     f.scale = scale;
     f.status = ctx->status_dev;
-    plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits, par->es);
+    plan_splits(ctx->sm_count, hs, batch, total_visible, max_visible, batch > 1 ? 4 : 1, &f.chunk_rows, &f.max_splits, par->es,
+                seqs.many != nullptr);
     f.max_groups = fused_merge_groups(f.max_splits);
     // A single sequence whose grid is fully resident merges through {value, epoch} words
     // (8 bytes per partial float) polled by the merging CTAs; batched decode keeps float

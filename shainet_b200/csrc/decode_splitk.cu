@@ -168,9 +168,12 @@ struct SK {
 
 // bfloat16 caches: a warp tile of twice the rows, so that a bulk copy moves as many bytes
 // as with fp32 rows and twice the batches overlap inside a tile (batched decode on the
-// Qwen3-8B shape: 0.49 ms per layer against 0.77 ms with the fp32 kernel's row count).
-template <int HD, int G>
-using SKB = SK<HD, G, 2, 2 * SKDefault<HD, G>::TW>;
+// Qwen3-8B shape: 0.49 ms per layer against 0.77 ms with the fp32 kernel's row count); three
+// times the rows for batched decode at group sizes 4 and up (0.43 ms; a single sequence, whose
+// CTAs have few tiles each, is slower with them: 29.6 against 27.0 us on the Qwen3-30B-A3B shape).
+template <int HD, int G, int MUL>
+using SKB = SK<HD, G, 2, MUL * SKDefault<HD, G>::TW>;
+constexpr int skb_mul(int g, bool batched) { return batched && g >= 4 ? 3 : 2; }
 
 // Carve-up of the dynamic shared memory, common to both kernels.
 template <class C>
@@ -1347,15 +1350,15 @@ bool splitk_supported(const HeadShape& hs) {
     return (hs.head_dim == 64 || hs.head_dim == 128) && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16);
 }
 
-int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes) {
+int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes, bool batched) {
     const int g = hs.num_heads / hs.num_kv_heads;
     const int br = 2 * (16 / g);
     const int tw = br > 8 ? br : 8;          // SKDefault::TW
-    return kv_elem_bytes == 2 ? 2 * tw : tw;  // SKB
+    return kv_elem_bytes == 2 ? skb_mul(g, batched) * tw : tw;  // SKB
 }
 
 int splitk_ctas_per_sm(const HeadShape& hs) {
-    return 2 * splitk_tile_rows(hs, 4) * hs.head_dim * 4 > 16 * 1024 ? 1 : 2;  // SKDefault::CTAS_PER_SM
+    return 2 * splitk_tile_rows(hs, 4, false) * hs.head_dim * 4 > 16 * 1024 ? 1 : 2;  // SKDefault::CTAS_PER_SM
 }
 
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits) {
@@ -1374,10 +1377,17 @@ cudaError_t launch_attn_splitk(const AttnArgs& a, cudaStream_t s) {
 cudaError_t launch_decode_fused(const FusedArgs& a, cudaStream_t s) {
     if (a.batch == 0) return cudaSuccess;
     if (a.kv_elem_bytes == 2) {
-        if (a.hs.head_dim == 64)
-            return dispatch_g(a, [&](auto g) { return launch_fused<64, decltype(g)::value, SKB<64, decltype(g)::value>>(a, s); });
-        if (a.hs.head_dim == 128)
-            return dispatch_g(a, [&](auto g) { return launch_fused<128, decltype(g)::value, SKB<128, decltype(g)::value>>(a, s); });
+        const bool batched = a.seqs.many != nullptr;   // the planner made the slices for this tile size (splitk_tile_rows)
+        auto go = [&](auto hd) {
+            constexpr int HD = decltype(hd)::value;
+            return dispatch_g(a, [&](auto g) {
+                constexpr int G = decltype(g)::value;
+                if (batched) return launch_fused<HD, G, SKB<HD, G, skb_mul(G, true)>>(a, s);
+                return launch_fused<HD, G, SKB<HD, G, skb_mul(G, false)>>(a, s);
+            });
+        };
+        if (a.hs.head_dim == 64) return go(std::integral_constant<int, 64>{});
+        if (a.hs.head_dim == 128) return go(std::integral_constant<int, 128>{});
         return cudaErrorInvalidValue;
     }
     if (a.kv_elem_bytes != 4) return cudaErrorInvalidValue;
@@ -1501,7 +1511,7 @@ extern "C" int shainet_attn_decode_noalloc(const float* q_dev, const float* k_ca
     a.scale = scale;
     a.status = nullptr;
     const int visible = start_pos + 1;
-    const int tw = splitk_tile_rows(hs, 4);
+    const int tw = splitk_tile_rows(hs, 4, false);
     const long long ctas = (long long)nd.sm_count * splitk_ctas_per_sm(hs);
     long long chunk = ((long long)visible * hs.num_kv_heads + ctas - 1) / ctas;
     if (chunk < 4ll * tw) chunk = 4ll * tw;

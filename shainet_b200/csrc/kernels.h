@@ -130,7 +130,7 @@ cudaError_t launch_attn_generic(const AttnArgs& a, cudaStream_t s);
 
 // Split-K flash-decode for head_dim in {64,128} and group size in {1,2,4,8,16}.
 bool splitk_supported(const HeadShape& hs);
-int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes);   // rows per warp tile for fp32 (4) or bfloat16 (2) caches
+int splitk_tile_rows(const HeadShape& hs, int kv_elem_bytes, bool batched);   // rows per warp tile: fp32 (4) or bfloat16 (2) caches, one sequence or a batch
 int splitk_ctas_per_sm(const HeadShape& hs);
 size_t splitk_scratch_floats(const HeadShape& hs, int rows, int max_splits);
 int fused_merge_groups(int max_splits);
