@@ -59,9 +59,12 @@ def test_prefill_at_the_benchmarked_length(ctx, chunks):
     g.close()
 
 
-def test_batched_ragged_decode_at_the_benchmarked_batch(ctx):
+@pytest.mark.parametrize("kv_format", ["f32", "bf16"])
+def test_batched_ragged_decode_at_the_benchmarked_batch(ctx, kv_format):
     """64 sequences, lengths floor(exp(U(ln 1024, ln 32768))) from seed 4001 (the
-    benchmark's draw), caches N(0,1), two lock-step steps against 64 oracles."""
+    benchmark's draw), caches N(0,1), two lock-step steps against 64 oracles; also with the
+    opt-in bfloat16 rows (24-row warp tiles in the batched launch) against oracles that round
+    their rows the same way."""
     import torch
     import shainet_b200 as S
     from oracle import oracle as O
@@ -77,9 +80,10 @@ def test_batched_ragged_decode_at_the_benchmarked_batch(ctx):
         L = int(lens[b])
         kc = rng.standard_normal((KV, L, hd), dtype=np.float32)
         vc = rng.standard_normal((KV, L, hd), dtype=np.float32)
-        o = O.OracleAttention(H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        o = O.OracleAttention(H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn,
+                              kv_rounding="bf16" if kv_format == "bf16" else None)
         o.import_cache(kc, vc)
-        g = S.LlamaAttention(ctx, H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn)
+        g = S.LlamaAttention(ctx, H, KV, hd, shape["theta"], 1e-6, q_norm=qn, k_norm=kn, kv_format=kv_format)
         g.cache.import_(kc, vc)
         g.cache.reserve(L + 4)
         oracles.append(o); caches.append(g)
